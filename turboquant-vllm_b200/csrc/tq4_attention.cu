@@ -1,0 +1,670 @@
+// Paged TQ4 attention: planning + query rotation, the fp32 CUDA-core streaming kernel,
+// the split merge + un-rotation kernel, and the C entry points.
+#include <math_constants.h>
+
+#include "tq4_attention.cuh"
+
+namespace tq4 {
+
+// ======================================================================================
+// 1. Prologue: q_rot = q * Pi^T for every (row, head), and (last block) the tile plan.
+// ======================================================================================
+template <int D>
+__host__ __device__ constexpr int qrot_vecs() { return D <= 128 ? 16 : 8; }  // (row, head) vectors per block
+
+__device__ void build_plan(const AttnArgs& a) {
+  // One block.  Per row: visible key range, tiles; then two exclusive scans.
+  const AttnShape& sh = a.sh;
+  const AttnPlan& p = a.plan;
+  __shared__ int s_part[1024];
+  __shared__ int s_total;
+  const int rows = sh.rows;
+  const int per = (rows + blockDim.x - 1) / blockDim.x;
+  const int r_lo = min(rows, (int)threadIdx.x * per), r_hi = min(rows, r_lo + per);
+
+  int local = 0;
+  for (int r = r_lo; r < r_hi; ++r) {
+    const int gr = r + sh.row_offset;
+    int seq, start = 0, end = 0;
+    if (a.query_start_loc == nullptr) {
+      seq = gr;
+      if (seq < sh.num_seqs) {
+        const int len = max(0, a.seq_lens[seq]);
+        end = len;
+        start = a.sliding_window > 0 ? max(0, len - a.sliding_window) : 0;
+      } else {
+        seq = 0;
+      }
+    } else {
+      // largest i with qsl[i] <= gr
+      int lo = 0, hi = sh.num_seqs;  // qsl has num_seqs + 1 entries
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (a.query_start_loc[mid] <= gr) lo = mid; else hi = mid - 1;
+      }
+      seq = lo;
+      if (seq < sh.num_seqs && gr < a.query_start_loc[sh.num_seqs]) {
+        const int q0 = a.query_start_loc[seq], q1 = a.query_start_loc[seq + 1];
+        const int len = max(0, a.seq_lens[seq]);
+        const int pos = len - (q1 - q0) + (gr - q0);
+        end = a.causal ? pos + 1 : len;
+        end = max(0, min(end, len));
+        start = a.sliding_window > 0 ? max(0, pos + 1 - a.sliding_window) : 0;
+        start = min(start, end);
+      } else {
+        seq = 0;
+      }
+    }
+    p.kv_start[r] = start;
+    p.kv_end[r] = end;
+    p.row_seq[r] = seq;
+    const int nt = end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
+    p.tile_prefix[r] = nt;  // raw count for now
+    local += nt;
+  }
+  auto block_exclusive_scan = [&](int mine) -> int {
+    s_part[threadIdx.x] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int i = 0; i < (int)blockDim.x; ++i) {
+        const int v = s_part[i];
+        s_part[i] = run;
+        run += v;
+      }
+      s_total = run;
+    }
+    __syncthreads();
+    const int base = s_part[threadIdx.x];
+    __syncthreads();
+    return base;
+  };
+  int run = block_exclusive_scan(local);
+  for (int r = r_lo; r < r_hi; ++r) {
+    const int nt = p.tile_prefix[r];
+    p.tile_prefix[r] = run;
+    run += nt;
+  }
+  const int total = s_total;
+  const int tps = max(1, (total + sh.ctas - 1) / sh.ctas);
+  if (threadIdx.x == 0) {
+    p.tile_prefix[rows] = total;
+    p.scalars[0] = total;
+    p.scalars[1] = tps;
+  }
+  __syncthreads();
+  local = 0;
+  for (int r = r_lo; r < r_hi; ++r) {
+    const int b = p.tile_prefix[r];
+    const int e = p.tile_prefix[r + 1];
+    const int n = e > b ? (e - 1) / tps - b / tps + 1 : 0;
+    p.slot_base[r] = n;
+    local += n;
+  }
+  __syncthreads();
+  run = block_exclusive_scan(local);
+  for (int r = r_lo; r < r_hi; ++r) {
+    const int n = p.slot_base[r];
+    p.slot_base[r] = run;
+    run += n;
+  }
+  if (threadIdx.x == 0) p.slot_base[rows] = s_total;
+}
+
+template <int D>
+__global__ void __launch_bounds__(D) qrot_plan_kernel(const AttnArgs a) {
+  if (blockIdx.x == gridDim.x - 1) {  // the planning block (blockDim.x == D threads)
+    build_plan(a);
+    return;
+  }
+  constexpr int kQrotVecs = qrot_vecs<D>();
+  __shared__ float s_pi[D][33];
+  __shared__ float s_q[kQrotVecs][D];
+  const AttnShape& sh = a.sh;
+  const int64_t n_vec = (int64_t)sh.rows * sh.Hq;
+  const int64_t v0 = (int64_t)blockIdx.x * kQrotVecs;
+  const int j = threadIdx.x;
+#pragma unroll 1
+  for (int v = 0; v < kQrotVecs; ++v) {
+    const int64_t vec = v0 + v;
+    float x = 0.f;
+    if (vec < n_vec) {
+      const int64_t row = vec / sh.Hq + sh.row_offset;
+      const int h = (int)(vec % sh.Hq);
+      x = load_as_float(a.q, a.q_dtype, row * a.q_token_stride + h * a.q_head_stride + j);
+    }
+    s_q[v][j] = x;
+  }
+  float acc[kQrotVecs];
+#pragma unroll
+  for (int v = 0; v < kQrotVecs; ++v) acc[v] = 0.f;
+  const int warp = j >> 5, lane = j & 31;
+  for (int d0 = 0; d0 < D; d0 += 32) {
+    __syncthreads();
+    // stage Pi[:, d0:d0+32] (row jj, 32 consecutive floats per warp-load)
+    for (int jj = warp; jj < D; jj += D / 32) s_pi[jj][lane] = a.rotation[(size_t)jj * D + d0 + lane];
+    __syncthreads();
+#pragma unroll 8
+    for (int dd = 0; dd < 32; ++dd) {
+      const float pv = s_pi[j][dd];
+#pragma unroll
+      for (int v = 0; v < kQrotVecs; ++v) acc[v] = fmaf(s_q[v][d0 + dd], pv, acc[v]);
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < kQrotVecs; ++v) {
+    const int64_t vec = v0 + v;
+    if (vec < n_vec) a.plan.q_rot[vec * D + j] = acc[v];
+  }
+}
+
+// ======================================================================================
+// 2. fp32 CUDA-core streaming kernel (any supported head_dim, any group size).
+// ======================================================================================
+template <int D, int GC>
+struct Fp32Cfg {
+  static constexpr int REPS = (D + 127) / 128;  // 4-dim groups per lane in the V phase
+  static constexpr int KW = D / 16;             // 32-bit words of K per lane (half a row)
+  static constexpr size_t smem_per_warp =
+      (size_t)GC * D * 4 + kTileTokens * GC * 4 + kTileTokens * 8;
+};
+
+template <int D, int GC>
+__global__ void __launch_bounds__(kMaxWarpsPerCta * 32)
+attention_fp32_kernel(const AttnArgs a) {
+  using Cfg = Fp32Cfg<D, GC>;
+  constexpr int REPS = Cfg::REPS, KW = Cfg::KW, HALF = D / 2;
+  const AttnShape& sh = a.sh;
+  const AttnPlan& p = a.plan;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float lut_k[TQ4_MAX_CENTROIDS], lut_v[TQ4_MAX_CENTROIDS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned char* wbase = smem_raw + warp * Cfg::smem_per_warp;
+  float* s_q = reinterpret_cast<float*>(wbase);                       // [GC][D]
+  float* s_p = s_q + GC * D;                                          // [16][GC]  p * vnorm
+  int64_t* s_row = reinterpret_cast<int64_t*>(s_p + kTileTokens * GC);  // [16] row byte offset, -1 = masked
+
+  if (threadIdx.x < TQ4_MAX_CENTROIDS) {
+    lut_k[threadIdx.x] = threadIdx.x < a.n_k_centroids ? a.k_centroids[threadIdx.x] : 0.f;
+    lut_v[threadIdx.x] = threadIdx.x < a.n_v_centroids ? a.v_centroids[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+
+  const int c = blockIdx.x % sh.ctas, slice = blockIdx.x / sh.ctas;
+  const int vh = slice * sh.HPC + warp % sh.HPC, ts = warp / sh.HPC;
+  const int kvh = vh / sh.NCH, chunk = vh % sh.NCH;
+  const int qh0 = kvh * sh.G + chunk * sh.GC;
+  const int gcount = min(sh.GC, sh.G - chunk * sh.GC);
+  const int total = p.scalars[0], tps = p.scalars[1];
+  const int t_begin = c * tps, t_end = min(total, t_begin + tps);
+  if (t_begin >= t_end) return;
+  const RowLayout lay = row_layout(sh.Hkv, D);
+
+  // first row r with tile_prefix[r] <= t_begin < tile_prefix[r+1]
+  int r;
+  {
+    int lo = 0, hi = sh.rows - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.tile_prefix[mid] <= t_begin) lo = mid; else hi = mid - 1;
+    }
+    r = lo;
+    while (p.tile_prefix[r + 1] <= t_begin) ++r;  // skip rows without tiles
+  }
+  const int tok = lane & 15, half = lane >> 4;
+
+  int t = t_begin;
+  while (t < t_end) {
+    const int row_t0 = p.tile_prefix[r], row_t1 = p.tile_prefix[r + 1];
+    const int seg_end = min(row_t1, t_end);
+    const int kv_start = p.kv_start[r], kv_end = p.kv_end[r];
+    const int32_t* bt = a.block_table + (int64_t)p.row_seq[r] * a.bt_stride;
+    const int tile0 = kv_start / kTileTokens;  // absolute tile index of the row's first tile
+
+    // q of this row's heads -> smem
+    __syncwarp();
+    for (int i = lane; i < GC * D; i += 32) {
+      const int g = i / D, d = i - g * D;
+      s_q[i] = g < gcount ? p.q_rot[((int64_t)r * sh.Hq + qh0 + g) * D + d] : 0.f;
+    }
+    __syncwarp();
+
+    float m[GC], l[GC], acc[GC][REPS][4];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      m[g] = -CUDART_INF_F;
+      l[g] = 0.f;
+#pragma unroll
+      for (int rep = 0; rep < REPS; ++rep)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[g][rep][e] = 0.f;
+    }
+
+    for (int tt = t + ts; tt < seg_end; tt += sh.TPC) {
+      const int pos = (tile0 + (tt - row_t0)) * kTileTokens + tok;
+      // ---- K phase: lane = (half, token) -------------------------------------------------
+      int64_t row_off = -1;
+      if (pos >= kv_start && pos < kv_end) {
+        const int blk = bt[pos / a.block_size];
+        if (blk < 0 || blk >= a.num_blocks) {
+          if (a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+        } else {
+          row_off = (int64_t)blk * a.cache_block_stride +
+                    (int64_t)(pos % a.block_size) * a.cache_token_stride;
+        }
+      }
+      float dot[GC];
+#pragma unroll
+      for (int g = 0; g < GC; ++g) dot[g] = 0.f;
+      float knorm = 0.f, vnorm = 0.f;
+      if (row_off >= 0) {
+        const uint8_t* rowp = a.cache + row_off;
+        const uint32_t* kw = reinterpret_cast<const uint32_t*>(rowp + lay.k_idx + kvh * HALF + half * (HALF / 2));
+        knorm = *reinterpret_cast<const float*>(rowp + lay.k_norm + kvh * 4);
+        vnorm = *reinterpret_cast<const float*>(rowp + lay.v_norm + kvh * 4);
+        const int dbase = half * HALF;
+#pragma unroll
+        for (int w = 0; w < KW; ++w) {
+          const uint32_t word = kw[w];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const uint32_t byte = (word >> (8 * b)) & 0xFFu;
+            const float ce = lut_k[byte >> 4], co = lut_k[byte & 0xFu];
+            const int d = dbase + w * 8 + b * 2;
+#pragma unroll
+            for (int g = 0; g < GC; ++g) {
+              dot[g] = fmaf(s_q[g * D + d], ce, dot[g]);
+              dot[g] = fmaf(s_q[g * D + d + 1], co, dot[g]);
+            }
+          }
+        }
+      }
+      if (half == 0) s_row[tok] = row_off;
+      float pw[GC];
+#pragma unroll
+      for (int g = 0; g < GC; ++g) {
+        float s = dot[g] + __shfl_xor_sync(0xffffffffu, dot[g], 16);
+        s = row_off >= 0 ? s * knorm * a.scale_log2e : -CUDART_INF_F;
+        float mt = s;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+        const float m_new = fmaxf(m[g], mt);
+        const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
+        const float alpha = exp2f(m[g] - m_use);
+        const float pr = exp2f(s - m_use);
+        m[g] = m_new;
+        l[g] = l[g] * alpha + (half == 0 ? pr : 0.f);
+        pw[g] = pr * vnorm;
+#pragma unroll
+        for (int rep = 0; rep < REPS; ++rep)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[g][rep][e] *= alpha;
+      }
+      if (half == 0) {
+#pragma unroll
+        for (int g = 0; g < GC; ++g) s_p[tok * GC + g] = pw[g];
+      }
+      __syncwarp();
+      // ---- V phase: lane = 4 consecutive dims per rep -----------------------------------
+#pragma unroll 4
+      for (int tk = 0; tk < kTileTokens; ++tk) {
+        const int64_t ro = s_row[tk];
+        if (ro < 0) continue;
+        const uint8_t* vrow = a.cache + ro + lay.v_idx + kvh * HALF;
+#pragma unroll
+        for (int rep = 0; rep < REPS; ++rep) {
+          const int byte0 = 2 * (lane + 32 * rep);
+          if (byte0 < HALF) {
+            const uint32_t hv = *reinterpret_cast<const uint16_t*>(vrow + byte0);
+            const float c0 = lut_v[(hv >> 4) & 0xFu], c1 = lut_v[hv & 0xFu];
+            const float c2 = lut_v[(hv >> 12) & 0xFu], c3 = lut_v[(hv >> 8) & 0xFu];
+#pragma unroll
+            for (int g = 0; g < GC; ++g) {
+              const float w = s_p[tk * GC + g];
+              acc[g][rep][0] = fmaf(w, c0, acc[g][rep][0]);
+              acc[g][rep][1] = fmaf(w, c1, acc[g][rep][1]);
+              acc[g][rep][2] = fmaf(w, c2, acc[g][rep][2]);
+              acc[g][rep][3] = fmaf(w, c3, acc[g][rep][3]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+
+    // ---- write this warp's partial for the segment ---------------------------------------
+    const int slot = p.slot_base[r] + (c - row_t0 / tps);
+    const int64_t pidx = (int64_t)slot * sh.TPC + ts;
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      if (g < gcount) {
+        const float lsum = warp_sum(l[g]);
+        const int64_t hidx = pidx * sh.Hq + qh0 + g;
+        if (lane == 0) {
+          p.part_m[hidx] = m[g];
+          p.part_l[hidx] = lsum;
+        }
+#pragma unroll
+        for (int rep = 0; rep < REPS; ++rep) {
+          const int d = 4 * (lane + 32 * rep);
+          if (d < D)
+            *reinterpret_cast<float4*>(p.part_o + hidx * D + d) =
+                make_float4(acc[g][rep][0], acc[g][rep][1], acc[g][rep][2], acc[g][rep][3]);
+        }
+      }
+    }
+    t = seg_end;
+    if (t < t_end) {
+      ++r;
+      while (p.tile_prefix[r + 1] <= t) ++r;
+    }
+  }
+}
+
+template <int D, int GC>
+int launch_fp32_t(const AttnArgs& a, cudaStream_t st) {
+  using Cfg = Fp32Cfg<D, GC>;
+  const size_t smem = Cfg::smem_per_warp * kMaxWarpsPerCta;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attention_fp32_kernel<D, GC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return TQ4_ERR_CUDA;
+    attr_set = true;
+  }
+  const int warps = a.sh.HPC * a.sh.TPC;
+  attention_fp32_kernel<D, GC><<<a.sh.ctas * a.sh.n_slices, warps * 32, smem, st>>>(a);
+  TQ4_CHECK_LAUNCH();
+  return TQ4_OK;
+}
+
+template <int D>
+int launch_fp32_d(const AttnArgs& a, cudaStream_t st) {
+  const int gc = a.sh.GC;
+  if (gc <= 1) return launch_fp32_t<D, 1>(a, st);
+  if (gc <= 2) return launch_fp32_t<D, 2>(a, st);
+  if (gc <= 4) return launch_fp32_t<D, 4>(a, st);
+  return launch_fp32_t<D, 8>(a, st);
+}
+
+int launch_attention_fp32(const AttnArgs& a, cudaStream_t st) {
+  switch (a.sh.D) {
+    case 64: return launch_fp32_d<64>(a, st);
+    case 96: return launch_fp32_d<96>(a, st);
+    case 128: return launch_fp32_d<128>(a, st);
+    case 256: return launch_fp32_d<256>(a, st);
+  }
+  return TQ4_ERR_UNSUPPORTED;
+}
+
+// ======================================================================================
+// 3. Merge the partials of a row, normalise, un-rotate, store.
+//    Also serves tq4_combine_partials (cross-GPU shards) through the "dense" mode.
+// ======================================================================================
+constexpr int kCombHeads = 8;
+
+struct CombineArgs {
+  // sparse mode (plan != null): slots of row r are slot_base[r]..slot_base[r+1], x TPC
+  const int* slot_base;
+  int TPC;
+  const float* part_o;
+  const float* part_m;
+  const float* part_l;
+  // dense mode (slot_base == null): `world` parts, part index w*rows + r; part_m holds natural-log
+  // LSE and part_o is already normalised
+  int world;
+  int rows, row_offset, Hq;
+  const float* rotation;
+  void* out;
+  int out_dtype;
+  int64_t out_token_stride, out_head_stride;
+  float* lse_out;
+  int out_rotated;
+};
+
+template <int D>
+__global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
+  __shared__ float s_o[kCombHeads][D];
+  const int r = blockIdx.x, h0 = blockIdx.y * kCombHeads, d = threadIdx.x;
+  const int nh = min(kCombHeads, a.Hq - h0);
+  constexpr float kLn2 = 0.6931471805599453f, kLog2e = 1.4426950408889634f;
+  for (int hh = 0; hh < nh; ++hh) {
+    const int h = h0 + hh;
+    float M = -CUDART_INF_F, L = 0.f, o = 0.f;
+    if (a.slot_base != nullptr) {
+      const int64_t p0 = (int64_t)a.slot_base[r] * a.TPC, p1 = (int64_t)a.slot_base[r + 1] * a.TPC;
+      for (int64_t pi = p0; pi < p1; ++pi) M = fmaxf(M, a.part_m[pi * a.Hq + h]);
+      const float m_use = M == -CUDART_INF_F ? 0.f : M;
+      for (int64_t pi = p0; pi < p1; ++pi) {
+        const float w = exp2f(a.part_m[pi * a.Hq + h] - m_use);
+        if (w > 0.f) {
+          L = fmaf(a.part_l[pi * a.Hq + h], w, L);
+          o = fmaf(a.part_o[(pi * a.Hq + h) * D + d], w, o);
+        }
+      }
+      M = m_use;
+    } else {
+      for (int w = 0; w < a.world; ++w)
+        M = fmaxf(M, a.part_m[((int64_t)w * a.rows + r) * a.Hq + h] * kLog2e);
+      const float m_use = M == -CUDART_INF_F ? 0.f : M;
+      for (int w = 0; w < a.world; ++w) {
+        const int64_t pi = (int64_t)w * a.rows + r;
+        const float wt = exp2f(a.part_m[pi * a.Hq + h] * kLog2e - m_use);
+        if (wt > 0.f) {
+          L += wt;
+          o = fmaf(a.part_o[(pi * a.Hq + h) * D + d], wt, o);
+        }
+      }
+      M = m_use;
+    }
+    s_o[hh][d] = L > 0.f ? o / L : 0.f;
+    if (d == 0 && a.lse_out)
+      a.lse_out[(int64_t)(r + a.row_offset) * a.Hq + h] = L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
+  }
+  __syncthreads();
+  float acc[kCombHeads];
+  if (a.out_rotated) {
+#pragma unroll
+    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = hh < nh ? s_o[hh][d] : 0.f;
+  } else {
+#pragma unroll
+    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = 0.f;
+#pragma unroll 4
+    for (int j = 0; j < D; ++j) {
+      const float pv = __ldg(a.rotation + (size_t)j * D + d);
+#pragma unroll
+      for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh][j], pv, acc[hh]);
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < kCombHeads; ++hh)
+    if (hh < nh)
+      store_from_float(a.out, a.out_dtype,
+                       (int64_t)(r + a.row_offset) * a.out_token_stride +
+                           (int64_t)(h0 + hh) * a.out_head_stride + d,
+                       acc[hh]);
+}
+
+int launch_combine(const CombineArgs& c, int D, cudaStream_t st) {
+  if (c.rows == 0) return TQ4_OK;
+  dim3 grid(c.rows, (c.Hq + kCombHeads - 1) / kCombHeads);
+  switch (D) {
+    case 64: combine_kernel<64><<<grid, 64, 0, st>>>(c); break;
+    case 96: combine_kernel<96><<<grid, 96, 0, st>>>(c); break;
+    case 128: combine_kernel<128><<<grid, 128, 0, st>>>(c); break;
+    case 256: combine_kernel<256><<<grid, 256, 0, st>>>(c); break;
+    default: return TQ4_ERR_UNSUPPORTED;
+  }
+  TQ4_CHECK_LAUNCH();
+  return TQ4_OK;
+}
+
+int launch_qrot_plan(const AttnArgs& a, cudaStream_t st) {
+  const int64_t n_vec = (int64_t)a.sh.rows * a.sh.Hq;
+  const int vecs = a.sh.D <= 128 ? 16 : 8;
+  const unsigned grid = (unsigned)((n_vec + vecs - 1) / vecs) + 1;
+  switch (a.sh.D) {
+    case 64: qrot_plan_kernel<64><<<grid, 64, 0, st>>>(a); break;
+    case 96: qrot_plan_kernel<96><<<grid, 96, 0, st>>>(a); break;
+    case 128: qrot_plan_kernel<128><<<grid, 128, 0, st>>>(a); break;
+    case 256: qrot_plan_kernel<256><<<grid, 256, 0, st>>>(a); break;
+    default: return TQ4_ERR_UNSUPPORTED;
+  }
+  TQ4_CHECK_LAUNCH();
+  return TQ4_OK;
+}
+
+}  // namespace tq4
+
+// ======================================================================================
+// C entry points
+// ======================================================================================
+extern "C" const char* tq4_version(void) { return "tq4-sm100a 0.1"; }
+
+extern "C" const char* tq4_status_string(int status) {
+  switch (status) {
+    case TQ4_OK: return "ok";
+    case TQ4_ERR_INVALID_ARG: return "invalid argument (null/misaligned pointer or bad size)";
+    case TQ4_ERR_UNSUPPORTED: return "unsupported head_dim / head grouping / dtype";
+    case TQ4_ERR_CUDA: return "CUDA runtime error at launch";
+    case TQ4_ERR_WORKSPACE: return "workspace too small";
+  }
+  return "unknown status";
+}
+
+extern "C" size_t tq4_attention_workspace_bytes(int64_t max_query_rows, int num_q_heads,
+                                                int num_kv_heads, int head_dim) {
+  tq4::AttnShape sh{};
+  if (max_query_rows <= 0 || !tq4::make_shape(sh, num_q_heads, num_kv_heads, head_dim)) return 0;
+  const int64_t rows = max_query_rows < tq4::kMaxRowsPerLaunch ? max_query_rows : tq4::kMaxRowsPerLaunch;
+  tq4::AttnPlan p;
+  return tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, sh.TPC);
+}
+
+extern "C" int tq4_paged_attention(
+    const void* q, int q_dtype, int64_t num_rows, int num_seqs, int num_q_heads, int num_kv_heads,
+    int head_dim, int64_t q_token_stride, int64_t q_head_stride, const uint8_t* cache,
+    int64_t cache_block_stride, int64_t cache_token_stride, int64_t num_blocks, int block_size,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+    const int32_t* query_start_loc, const float* k_centroids, int n_k_centroids,
+    const float* v_centroids, int n_v_centroids, const float* rotation, float sm_scale, int causal,
+    int sliding_window, void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
+    float* lse_out, int out_rotated, void* workspace, size_t workspace_bytes, int mode,
+    int* err_flag, void* stream) {
+  using namespace tq4;
+  if (num_rows < 0 || num_seqs < 0 || block_size <= 0 || num_blocks < 0) return TQ4_ERR_INVALID_ARG;
+  if (!supported_head_dim(head_dim)) return TQ4_ERR_UNSUPPORTED;
+  if (q_dtype < 0 || q_dtype > 2 || out_dtype < 0 || out_dtype > 2) return TQ4_ERR_UNSUPPORTED;
+  if (n_k_centroids <= 0 || n_k_centroids > TQ4_MAX_CENTROIDS || n_v_centroids <= 0 ||
+      n_v_centroids > TQ4_MAX_CENTROIDS)
+    return TQ4_ERR_UNSUPPORTED;
+  AttnArgs a{};
+  if (!make_shape(a.sh, num_q_heads, num_kv_heads, head_dim)) return TQ4_ERR_UNSUPPORTED;
+  if (num_rows == 0) return TQ4_OK;
+  if (!q || !cache || !block_table || !seq_lens || !k_centroids || !v_centroids || !rotation ||
+      !out || !workspace)
+    return TQ4_ERR_INVALID_ARG;
+  if (((uintptr_t)cache & 3) || (cache_token_stride & 3) || (cache_block_stride & 3) ||
+      ((uintptr_t)workspace & 15) ||
+      cache_token_stride < row_data_bytes(num_kv_heads, head_dim))
+    return TQ4_ERR_INVALID_ARG;
+  if (query_start_loc == nullptr && num_rows > num_seqs) return TQ4_ERR_INVALID_ARG;
+  const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
+  if (workspace_bytes < carve_plan(a.plan, nullptr, rows_cap, num_q_heads, head_dim, a.sh.TPC))
+    return TQ4_ERR_WORKSPACE;
+  carve_plan(a.plan, workspace, rows_cap, num_q_heads, head_dim, a.sh.TPC);
+
+  a.sh.num_seqs = num_seqs;
+  a.q = q;
+  a.q_dtype = q_dtype;
+  a.q_token_stride = q_token_stride;
+  a.q_head_stride = q_head_stride;
+  a.cache = cache;
+  a.cache_block_stride = cache_block_stride;
+  a.cache_token_stride = cache_token_stride;
+  a.num_blocks = num_blocks;
+  a.block_size = block_size;
+  a.block_table = block_table;
+  a.bt_stride = bt_stride;
+  a.seq_lens = seq_lens;
+  a.query_start_loc = query_start_loc;
+  a.k_centroids = k_centroids;
+  a.v_centroids = v_centroids;
+  a.n_k_centroids = n_k_centroids;
+  a.n_v_centroids = n_v_centroids;
+  a.rotation = rotation;
+  a.scale_log2e = sm_scale * 1.4426950408889634f;
+  a.causal = causal;
+  a.sliding_window = sliding_window > 0 ? sliding_window : 0;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.out_token_stride = out_token_stride;
+  a.out_head_stride = out_head_stride;
+  a.lse_out = lse_out;
+  a.out_rotated = out_rotated;
+  a.err_flag = err_flag;
+
+  const bool use_mma = mode == 2 || (mode == 0 && attention_mma_supported(a.sh, block_size));
+  if (mode == 2 && !attention_mma_supported(a.sh, block_size)) return TQ4_ERR_UNSUPPORTED;
+  const int sms = sm_count();
+  int ctas = (use_mma ? 2 : 4) * sms / a.sh.n_slices;
+  if (ctas < 1) ctas = 1;
+  if (ctas > kMaxCtasPerSlice) ctas = kMaxCtasPerSlice;
+  a.sh.ctas = ctas;
+  cudaStream_t st = (cudaStream_t)stream;
+
+  for (int64_t r0 = 0; r0 < num_rows; r0 += kMaxRowsPerLaunch) {
+    a.sh.rows = (int)((num_rows - r0) < kMaxRowsPerLaunch ? (num_rows - r0) : kMaxRowsPerLaunch);
+    a.sh.row_offset = (int)r0;
+    int rc = launch_qrot_plan(a, st);
+    if (rc != TQ4_OK) return rc;
+    rc = use_mma ? launch_attention_mma(a, st) : launch_attention_fp32(a, st);
+    if (rc != TQ4_OK) return rc;
+    CombineArgs c{};
+    c.slot_base = a.plan.slot_base;
+    c.TPC = a.sh.TPC;
+    c.part_o = a.plan.part_o;
+    c.part_m = a.plan.part_m;
+    c.part_l = a.plan.part_l;
+    c.rows = a.sh.rows;
+    c.row_offset = a.sh.row_offset;
+    c.Hq = num_q_heads;
+    c.rotation = rotation;
+    c.out = out;
+    c.out_dtype = out_dtype;
+    c.out_token_stride = out_token_stride;
+    c.out_head_stride = out_head_stride;
+    c.lse_out = lse_out;
+    c.out_rotated = out_rotated;
+    rc = launch_combine(c, head_dim, st);
+    if (rc != TQ4_OK) return rc;
+  }
+  return TQ4_OK;
+}
+
+extern "C" int tq4_combine_partials(const float* parts_o, const float* parts_lse, int world,
+                                    int64_t num_rows, int num_q_heads, int head_dim,
+                                    const float* rotation, void* out, int out_dtype,
+                                    int64_t out_token_stride, int64_t out_head_stride,
+                                    void* stream) {
+  using namespace tq4;
+  if (world <= 0 || num_rows < 0 || num_q_heads <= 0) return TQ4_ERR_INVALID_ARG;
+  if (!supported_head_dim(head_dim) || out_dtype < 0 || out_dtype > 2) return TQ4_ERR_UNSUPPORTED;
+  if (num_rows == 0) return TQ4_OK;
+  if (!parts_o || !parts_lse || !rotation || !out) return TQ4_ERR_INVALID_ARG;
+  if (num_rows > 0x7fffffff) return TQ4_ERR_INVALID_ARG;
+  CombineArgs c{};
+  c.slot_base = nullptr;
+  c.world = world;
+  c.part_o = parts_o;
+  c.part_m = parts_lse;
+  c.rows = (int)num_rows;
+  c.row_offset = 0;
+  c.Hq = num_q_heads;
+  c.rotation = rotation;
+  c.out = out;
+  c.out_dtype = out_dtype;
+  c.out_token_stride = out_token_stride;
+  c.out_head_stride = out_head_stride;
+  return launch_combine(c, head_dim, (cudaStream_t)stream);
+}

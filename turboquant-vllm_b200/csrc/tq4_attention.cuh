@@ -1,0 +1,121 @@
+// Shared plan / argument structures of the paged TQ4 attention kernels.
+//
+// Work decomposition (CUDA-graph safe: the grid depends on shapes only, everything that
+// depends on seq_lens is computed on the device):
+//   * a query ROW r (one query token, all its heads) sees keys [kv_start[r], kv_end[r]);
+//   * the keys of a row are cut into 16-token TILES on absolute 16-token boundaries;
+//   * all tiles of all rows form one stream, cut into `ctas` equal contiguous SPANS; CTA c
+//     works on span c, so load balance is independent of the length distribution;
+//   * inside a CTA, warp (ts, vh) handles virtual head vh and every TPC-th tile (phase ts);
+//   * a (row, CTA) intersection is a SEGMENT; every warp writes one partial (m, l, O) per
+//     segment into slot slot_base[r] + (c - first_cta(r)), sub-slot ts;
+//   * the combine kernel merges the slots of a row, normalises and un-rotates.
+#pragma once
+#include "tq4_common.cuh"
+
+namespace tq4 {
+
+constexpr int kTileTokens = 16;
+constexpr int kMaxWarpsPerCta = 8;
+constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace sizing
+constexpr int kMaxRowsPerLaunch = 4096;    // larger query batches are processed in pieces
+
+struct AttnPlan {
+  float* q_rot;      // [rows][Hq][D] fp32, q * Pi^T
+  int* kv_start;     // [rows]
+  int* kv_end;       // [rows]
+  int* row_seq;      // [rows]   block-table row of the sequence that owns the query row
+  int* tile_prefix;  // [rows+1] exclusive prefix sum of tiles per row
+  int* slot_base;    // [rows+1] exclusive prefix sum of segments per row
+  int* scalars;      // [0] total tiles, [1] tiles per span
+  float* part_o;     // [slots][TPC][Hq][D]  un-normalised, rotated space
+  float* part_m;     // [slots][TPC][Hq]     running max (log2 domain), -inf if empty
+  float* part_l;     // [slots][TPC][Hq]     running sum
+};
+
+struct AttnShape {
+  int rows;       // query rows in this launch
+  int row_offset; // index of the first row of this launch within the whole call
+  int num_seqs, Hq, Hkv, D, G;  // G = Hq / Hkv
+  int GC;         // q heads per virtual head (<= 8)
+  int NCH;        // virtual heads per KV head = ceil(G / GC)
+  int HPC;        // virtual heads per CTA
+  int TPC;        // tile phases per CTA (warps per virtual head)
+  int n_slices;   // VH / HPC
+  int ctas;       // CTAs per slice
+};
+
+struct AttnArgs {
+  AttnPlan plan;
+  AttnShape sh;
+  const void* q;
+  int q_dtype;
+  int64_t q_token_stride, q_head_stride;
+  const uint8_t* cache;
+  int64_t cache_block_stride, cache_token_stride, num_blocks;
+  int block_size;
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* seq_lens;
+  const int32_t* query_start_loc;  // nullptr = decode
+  const float* k_centroids;
+  const float* v_centroids;
+  int n_k_centroids, n_v_centroids;
+  const float* rotation;
+  float scale_log2e;  // sm_scale * log2(e)
+  int causal, sliding_window;
+  void* out;
+  int out_dtype;
+  int64_t out_token_stride, out_head_stride;
+  float* lse_out;
+  int out_rotated;
+  int* err_flag;
+};
+
+inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+// Split Hq query heads over warps: a VIRTUAL head is one KV head plus up to 8 of its query
+// heads; a CTA holds HPC virtual heads x TPC tile phases = at most 8 warps.
+inline bool make_shape(AttnShape& s, int Hq, int Hkv, int D) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return false;
+  s.Hq = Hq; s.Hkv = Hkv; s.D = D; s.G = Hq / Hkv;
+  s.NCH = (s.G + 7) / 8;
+  s.GC = (s.G + s.NCH - 1) / s.NCH;
+  const int vh = Hkv * s.NCH;
+  s.HPC = 1;
+  for (int c = kMaxWarpsPerCta; c >= 1; --c)
+    if (vh % c == 0) { s.HPC = c; break; }
+  s.TPC = kMaxWarpsPerCta / s.HPC;
+  s.n_slices = vh / s.HPC;
+  return true;
+}
+
+// Carve the workspace.  Returns the number of bytes used.
+inline size_t carve_plan(AttnPlan& p, void* ws, int64_t rows, int Hq, int D, int TPC) {
+  const int64_t slots = rows + kMaxCtasPerSlice;
+  unsigned char* b = reinterpret_cast<unsigned char*>(ws);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    unsigned char* q = b ? b + off : nullptr;
+    off += align16(bytes);
+    return q;
+  };
+  p.q_rot = reinterpret_cast<float*>(take((size_t)rows * Hq * D * 4));
+  p.kv_start = reinterpret_cast<int*>(take((size_t)rows * 4));
+  p.kv_end = reinterpret_cast<int*>(take((size_t)rows * 4));
+  p.row_seq = reinterpret_cast<int*>(take((size_t)rows * 4));
+  p.tile_prefix = reinterpret_cast<int*>(take((size_t)(rows + 1) * 4));
+  p.slot_base = reinterpret_cast<int*>(take((size_t)(rows + 1) * 4));
+  p.scalars = reinterpret_cast<int*>(take(64));
+  p.part_o = reinterpret_cast<float*>(take((size_t)slots * TPC * Hq * D * 4));
+  p.part_m = reinterpret_cast<float*>(take((size_t)slots * TPC * Hq * 4));
+  p.part_l = reinterpret_cast<float*>(take((size_t)slots * TPC * Hq * 4));
+  return off;
+}
+
+// Launchers implemented in tq4_attention.cu / tq4_decode_mma.cu.
+int launch_attention_fp32(const AttnArgs& a, cudaStream_t st);
+int launch_attention_mma(const AttnArgs& a, cudaStream_t st);  // returns TQ4_ERR_UNSUPPORTED if shape not covered
+bool attention_mma_supported(const AttnShape& sh, int block_size);
+
+}  // namespace tq4

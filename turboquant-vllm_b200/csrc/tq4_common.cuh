@@ -1,0 +1,104 @@
+// Shared device/host helpers for the TQ4 sm_100a kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tq4.h"
+
+#define TQ4_MAX_BOUNDARIES 15
+#define TQ4_MAX_CENTROIDS 16
+
+#define TQ4_CHECK_LAUNCH()                                   \
+  do {                                                       \
+    cudaError_t e__ = cudaGetLastError();                    \
+    if (e__ != cudaSuccess) return (int)TQ4_ERR_CUDA;        \
+  } while (0)
+
+namespace tq4 {
+
+__host__ __device__ inline bool supported_head_dim(int d) {
+  return d == 64 || d == 96 || d == 128 || d == 256;
+}
+
+// Bytes of one token row that carry data: [K_idx|K_norm|V_idx|V_norm].
+__host__ __device__ inline int row_data_bytes(int num_kv_heads, int head_dim) {
+  return num_kv_heads * (head_dim + 8);
+}
+
+struct RowLayout {
+  int k_idx, k_norm, v_idx, v_norm;  // byte offsets of the four regions in a token row
+};
+__host__ __device__ inline RowLayout row_layout(int num_kv_heads, int head_dim) {
+  RowLayout r;
+  r.k_idx = 0;
+  r.k_norm = num_kv_heads * (head_dim / 2);
+  r.v_idx = r.k_norm + num_kv_heads * 4;
+  r.v_norm = r.v_idx + num_kv_heads * (head_dim / 2);
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Load one element of a typed tensor chosen at run time (cold paths only).
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+  if (dtype == TQ4_F32) return reinterpret_cast<const float*>(p)[i];
+  if (dtype == TQ4_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void store_from_float(void* p, int dtype, int64_t i, float v) {
+  if (dtype == TQ4_F32) reinterpret_cast<float*>(p)[i] = v;
+  else if (dtype == TQ4_F16) reinterpret_cast<__half*>(p)[i] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// idx = #{b : b < y}: the tie rule of torch.bucketize(right=False).  NaN compares false -> 0.
+__device__ __forceinline__ int bucketize(float y, const float* __restrict__ b, int nb) {
+  int idx = 0;
+#pragma unroll
+  for (int i = 0; i < TQ4_MAX_BOUNDARIES; ++i)
+    if (i < nb) idx += (y > b[i]) ? 1 : 0;
+  return idx;
+}
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace tq4

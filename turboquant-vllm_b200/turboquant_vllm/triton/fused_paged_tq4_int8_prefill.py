@@ -1,0 +1,4 @@
+"""Alias of the reference module path ``turboquant_vllm.triton.fused_paged_tq4_int8_prefill``."""
+from turboquant_vllm.kernels.ops import fused_paged_tq4_int8_prefill
+
+__all__ = ["fused_paged_tq4_int8_prefill"]
