@@ -1,0 +1,200 @@
+"""GPU parity: compress (rows) and the fused paged cache write, through the C ABI."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tq4_oracle as O
+from tests.helpers import Prims, build_paged_case, index_mismatch, t, ulp_diff
+
+pytestmark = pytest.mark.gpu
+
+MAX_INDEX_MISMATCH = 1e-4  # end-to-end index mismatch bound
+MAX_NORM_ULP = 4           # fp32 norm: reduction order differs from torch's CPU reduction
+
+
+@pytest.fixture(scope="module")
+def ops(cuda_lib):
+    from turboquant_vllm.kernels import ops as _ops
+
+    return _ops
+
+
+@pytest.mark.parametrize("d", [64, 96, 128, 256])
+def test_pack_rotated_bit_exact(ops, golden, d):
+    """Given the reference's own rotated rows, the packed bytes are bit-exact."""
+    g = golden("compress.npz")
+    p = Prims(d).cuda()
+    packed = ops.tq4_pack_rotated(t(g[f"rotated_{d}"]).cuda(), p["kb"])
+    assert np.array_equal(packed.cpu().numpy(), g[f"packed_{d}"].reshape(-1, d // 2))
+
+
+@pytest.mark.parametrize("d", [64, 96, 128, 256])
+def test_compress_golden_bf16(ops, golden, d):
+    g = golden("compress.npz")
+    p = Prims(d).cuda()
+    x = t(g[f"x_{d}"]).bfloat16().cuda()
+    packed, norms = ops.tq4_compress(x, p["even"], p["odd"], p["kb"])
+    assert packed.shape == (24, 4, d // 2) and packed.dtype == torch.uint8
+    assert norms.shape == (24, 4, 1) and norms.dtype == torch.float32
+    assert index_mismatch(packed, t(g[f"packed_{d}"])) <= MAX_INDEX_MISMATCH
+    ref_n = t(g[f"norms_{d}"])
+    assert ulp_diff(norms, ref_n).max() <= MAX_NORM_ULP
+    # the all-zero vector: norm 0, every index 7 (tie at boundary 0.0 resolved like bucketize)
+    assert norms[5, 2, 0].item() == 0.0
+    assert torch.all(packed[5, 2] == 0x77)
+
+
+def test_compress_fp32_input_and_3bit(ops, golden):
+    g = golden("compress.npz")
+    p = Prims(128, 3, 3).cuda()
+    packed, norms = ops.tq4_compress(t(g["x_f32_128"]).cuda(), p["even"], p["odd"], p["kb"])
+    assert index_mismatch(packed, t(g["packed_f32_128_b3"])) <= MAX_INDEX_MISMATCH
+    assert ulp_diff(norms, t(g["norms_f32_128_b3"])).max() <= MAX_NORM_ULP
+    assert O.nibble_unpack(packed.cpu()).max() <= 7
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("d", [64, 128])
+def test_compress_large_vs_oracle(ops, d, dtype):
+    pr = Prims(d)
+    p = pr.cuda()
+    k, _ = O.synthetic_kv(2048, 8, d, seed=3, dtype=dtype)
+    ref_p, ref_n = O.compress_rows(k, pr.rot, pr.kb)
+    packed, norms = ops.tq4_compress(k.cuda(), p["even"], p["odd"], p["kb"])
+    mm = index_mismatch(packed, ref_p)
+    assert mm <= MAX_INDEX_MISMATCH, mm
+    u = ulp_diff(norms, ref_n)
+    assert u.max() <= MAX_NORM_ULP
+    # a one-ulp norm difference never moves an index by more than one bucket
+    a, b = O.nibble_unpack(packed.cpu()), O.nibble_unpack(ref_p)
+    assert (a - b).abs().max() <= 1
+
+
+def test_compress_out_contract(ops):
+    """out= returns the very same objects, holds identical values, and can be reused."""
+    pr = Prims(128)
+    p = pr.cuda()
+    x, _ = O.synthetic_kv(7, 8, 128, seed=5, dtype=torch.bfloat16)
+    x = x.cuda()
+    a_p, a_n = ops.tq4_compress(x, p["even"], p["odd"], p["kb"])
+    buf_p = torch.full((7, 8, 64), 0xAB, dtype=torch.uint8, device="cuda")
+    buf_n = torch.full((7, 8, 1), -1.0, dtype=torch.float32, device="cuda")
+    r_p, r_n = ops.tq4_compress(x, p["even"], p["odd"], p["kb"], out=(buf_p, buf_n))
+    assert r_p is buf_p and r_n is buf_n
+    assert torch.equal(buf_p, a_p) and torch.equal(buf_n, a_n)
+    ops.tq4_compress(x.flip(0).contiguous(), p["even"], p["odd"], p["kb"], out=(buf_p, buf_n))
+    assert torch.equal(buf_p, a_p.flip(0)) and torch.equal(buf_n, a_n.flip(0))
+
+
+def test_compress_empty_and_strided(ops):
+    pr = Prims(128)
+    p = pr.cuda()
+    packed, norms = ops.tq4_compress(torch.empty(0, 8, 128, dtype=torch.bfloat16, device="cuda"),
+                                     p["even"], p["odd"], p["kb"])
+    assert packed.shape == (0, 8, 64) and norms.shape == (0, 8, 1)
+    # key as a strided view of a fused qkv tensor (token stride != H*D)
+    qkv = torch.randn(33, 6144, device="cuda").bfloat16()
+    key = qkv[:, 4096:5120].view(33, 8, 128)
+    a = ops.tq4_compress(key, p["even"], p["odd"], p["kb"])
+    b = ops.tq4_compress(key.contiguous(), p["even"], p["odd"], p["kb"])
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_cpu_tensor_rejected(ops):
+    pr = Prims(128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.tq4_compress(torch.zeros(1, 1, 128), pr.even, pr.odd, pr.kb)
+
+
+def _regions(cache: torch.Tensor, h: int, d: int):
+    a, b, c, tot = O.row_layout(h, d)
+    flat = cache.reshape(-1, cache.shape[-1]).cpu()
+    kp = flat[:, :a].reshape(-1, h, d // 2)
+    kn = flat[:, a:b].contiguous().view(torch.float32)
+    vp = flat[:, b:c].reshape(-1, h, d // 2)
+    vn = flat[:, c:tot].contiguous().view(torch.float32)
+    return kp, kn, vp, vn, flat[:, tot:]
+
+
+@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7"])
+def test_write_paged_golden(ops, golden, tag):
+    """Fused K+V cache write against the cache the reference's _compress_and_store produced."""
+    g = golden("paged.npz")
+    d, h_kv, h_q, kb, vb, bs = [int(x) for x in g[f"{tag}_meta"]]
+    p = Prims(d, kb, vb).cuda()
+    ref = t(g[f"{tag}_cache"])
+    cache = torch.zeros_like(ref).cuda()
+    key, value = t(g[f"{tag}_key"]).bfloat16().cuda(), t(g[f"{tag}_value"]).bfloat16().cuda()
+    ops.tq4_write_paged(key, value, cache, t(g[f"{tag}_slot_mapping"]).cuda(),
+                        p["even"], p["odd"], p["kb"], p["vb"])
+    assert ops.read_and_clear_errors(cache.device) == 0
+    kp, kn, vp, vn, pad = _regions(cache, h_kv, d)
+    rkp, rkn, rvp, rvn, rpad = _regions(ref, h_kv, d)
+    assert index_mismatch(kp, rkp) <= MAX_INDEX_MISMATCH
+    assert index_mismatch(vp, rvp) <= MAX_INDEX_MISMATCH
+    assert ulp_diff(kn, rkn).max() <= MAX_NORM_ULP and ulp_diff(vn, rvn).max() <= MAX_NORM_ULP
+    assert torch.equal(pad, rpad)  # padding bytes (if any) untouched
+
+
+def test_write_paged_slot_semantics(ops):
+    """Negative slots are skipped, tokens beyond len(slot_mapping) are not written, a later
+    call overwrites a slot, untouched slots stay empty."""
+    pr = Prims(128)
+    p = pr.cuda()
+    h, d, bs = 8, 128, 16
+    width = O.row_layout(h, d)[3]
+    k, v = O.synthetic_kv(6, h, d, seed=9, dtype=torch.bfloat16)
+    cache = torch.zeros(4, bs, width, dtype=torch.uint8, device="cuda")
+    slots = torch.tensor([5, -1, 40, 7], dtype=torch.int64)  # 4 slots for 6 tokens
+    ops.tq4_write_paged(k.cuda(), v.cuda(), cache, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"])
+    ref = torch.zeros(4, bs, width, dtype=torch.uint8)
+    O.write_paged(k, v, ref, slots, pr.rot, pr.kb, pr.vb)
+    flat, rflat = cache.cpu().reshape(-1, width), ref.reshape(-1, width)
+    for s_ in range(flat.shape[0]):
+        if s_ in (5, 40, 7):
+            assert index_mismatch(flat[s_:s_ + 1, :512].reshape(1, 8, 64),
+                                  rflat[s_:s_ + 1, :512].reshape(1, 8, 64)) <= 1e-2
+            assert flat[s_].any()
+        else:
+            assert not flat[s_].any(), f"slot {s_} should be empty"
+    # overwrite slot 5 with token 4
+    ops.tq4_write_paged(k[4:5].cuda(), v[4:5].cuda(), cache, torch.tensor([5]).cuda(),
+                        p["even"], p["odd"], p["kb"], p["vb"])
+    O.write_paged(k[4:5], v[4:5], ref, torch.tensor([5]), pr.rot, pr.kb, pr.vb)
+    assert index_mismatch(cache.cpu().reshape(-1, width)[5:6, :512].reshape(1, 8, 64),
+                          ref.reshape(-1, width)[5:6, :512].reshape(1, 8, 64)) <= 1e-2
+
+
+def test_write_paged_bad_slot_sets_flag(ops):
+    pr = Prims(128)
+    p = pr.cuda()
+    k, v = O.synthetic_kv(2, 8, 128, seed=1, dtype=torch.bfloat16)
+    cache = torch.zeros(2, 16, 1088, dtype=torch.uint8, device="cuda")
+    ops.read_and_clear_errors(cache.device)
+    slots = torch.tensor([3, 32], dtype=torch.int64, device="cuda")  # 32 == num slots: out of range
+    ops.tq4_write_paged(k.cuda(), v.cuda(), cache, slots, p["even"], p["odd"], p["kb"], p["vb"])
+    assert ops.read_and_clear_errors(cache.device) & 1
+    assert cache[0, 3].any() and not cache[1].any()
+
+
+def test_write_then_read_roundtrip_full_size(ops):
+    """Size-independent property at the serving-mix write size (256 tokens x 8 heads):
+    decompress(write(x)) reconstructs x with the cosine the format is known for, and writing
+    the same tokens twice is idempotent."""
+    pr = Prims(128)
+    p = pr.cuda()
+    h, d, bs, n = 8, 128, 16, 256
+    k, v = O.synthetic_kv(n, h, d, seed=21, dtype=torch.bfloat16)
+    cache = torch.zeros(n // bs, bs, h * O.padded_slot_bytes(d), dtype=torch.uint8, device="cuda")
+    slots = torch.randperm(n, generator=torch.Generator().manual_seed(0)).cuda()
+    ops.tq4_write_paged(k.cuda(), v.cuda(), cache, slots, p["even"], p["odd"], p["kb"], p["vb"])
+    first = cache.clone()
+    ops.tq4_write_paged(k.cuda(), v.cuda(), cache, slots, p["even"], p["odd"], p["kb"], p["vb"])
+    assert torch.equal(first, cache)
+    kd, vd = ops.tq4_decompress_cache(cache, h, d, p["kc"], p["vc"], torch.float32)
+    k_rec = (kd @ p["rot"])[slots]  # row i of the input went to slot slots[i]
+    cos = torch.nn.functional.cosine_similarity(k_rec.flatten(1), k.cuda().float().flatten(1), dim=1)
+    assert cos.min() > 0.98

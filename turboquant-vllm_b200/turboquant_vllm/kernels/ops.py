@@ -253,7 +253,9 @@ def paged_tq4_attention(
     assert kv_cache.dtype == torch.uint8 and kv_cache.stride(2) == 1
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     assert seq_lens.dtype == torch.int32 and seq_lens.is_contiguous()
-    assert rotation.dtype == torch.float32 and rotation.is_contiguous()
+    assert rotation.dtype == torch.float32
+    if not rotation.is_contiguous():  # e.g. the column-major Q factor of torch.linalg.qr
+        rotation = rotation.contiguous()
     if query_start_loc is not None:
         assert query_start_loc.dtype == torch.int32 and query_start_loc.is_contiguous()
         nv.require_cuda(query_start_loc)
@@ -408,6 +410,7 @@ def combine_partials(
     assert parts_o.dtype == torch.float32 and parts_lse.dtype == torch.float32
     parts_o = parts_o.contiguous()
     parts_lse = parts_lse.contiguous()
+    rotation = rotation.contiguous()
     w, t, hq, d = parts_o.shape
     if out is None:
         out = torch.empty(t, hq, d, dtype=out_dtype, device=parts_o.device)
