@@ -1,0 +1,414 @@
+"""Benchmark of the TQ4 hot path: cache write of one new token per sequence + fused paged
+TQ4 decode over the packed cache, one transformer layer per step.
+
+Workload (N = 1): Llama-3.1-8B-shaped single-layer paged decode — batch 64, context 4096
+each, 32 query / 8 KV heads, head_dim 128, block_size 16 with a seeded shuffled block table,
+K4/V4 packed cache (vLLM padded rows) filled by the fused write kernel from N(0,1) K/V with
+four outlier channels scaled x8, bf16 queries.  Several layer caches are rotated so the
+working set is far larger than L2.
+N > 1: KV heads are sharded across ranks (tensor parallel, no collective inside attention);
+the global batch grows with N so per-GPU work is fixed (weak scaling).
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
+reference's PyTorch path (oracle/) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "turboquant-vllm_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+BATCH_PER_GPU_UNIT, CTX, HQ, HKV, D, BS = 64, 4096, 32, 8, 128, 16
+K_BITS = V_BITS = 4
+SEED = 0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant (attention) kernel
+# on this workload, from the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------------------
+# clocks sampling (read-only NVML)
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+            0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self._nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=1.0)
+        med = int(statistics.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------
+# workload
+# ----------------------------------------------------------------------------------------
+def primitives():
+    from turboquant_vllm.quantizer import TurboQuantMSE
+
+    kq = TurboQuantMSE(D, K_BITS, seed=42)
+    vq = kq if V_BITS == K_BITS else TurboQuantMSE(D, V_BITS, seed=42)
+    return kq, vq
+
+
+def synth_kv_gpu(n, h, gen, device):
+    k = torch.randn(n, h, D, device=device, generator=gen)
+    v = torch.randn(n, h, D, device=device, generator=gen)
+    for ch in (3, 17, 64, 101):
+        k[..., ch] *= 8.0
+        v[..., ch] *= 8.0
+    return k.bfloat16(), v.bfloat16()
+
+
+def build_workload(device, world, layers):
+    """Per-rank state: `layers` packed caches filled through the fused write kernel."""
+    from turboquant_vllm.kernels import ops
+
+    batch = BATCH_PER_GPU_UNIT * world
+    hkv, hq = HKV // world, HQ // world
+    kq, vq = primitives()
+    rot, even, odd, kc, kb = kq.device_primitives(device)
+    _, _, _, vc, vb = vq.device_primitives(device)
+    nblk = batch * CTX // BS
+    slot = 1 << ((D + 8) - 1).bit_length()  # vLLM padded per-head slot (256 B at D=128)
+    width = hkv * slot
+    gen = torch.Generator(device=device).manual_seed(SEED)
+    perm = torch.randperm(nblk, device=device, generator=gen)
+    block_table = perm.view(batch, CTX // BS).to(torch.int32).contiguous()
+    seq_lens = torch.full((batch,), CTX, dtype=torch.int32, device=device)
+    pos = torch.arange(CTX, device=device)
+    caches = []
+    chunk_seqs = max(1, 16384 // CTX)
+    for _ in range(layers):
+        cache = torch.zeros(nblk, BS, width, dtype=torch.uint8, device=device)
+        for s0 in range(0, batch, chunk_seqs):
+            s1 = min(batch, s0 + chunk_seqs)
+            slots = (block_table[s0:s1].long()[:, pos // BS] * BS + (pos % BS)).reshape(-1)
+            k, v = synth_kv_gpu(slots.numel(), hkv, gen, device)
+            ops.tq4_write_paged(k, v, cache, slots, even, odd, kb, vb)
+        caches.append(cache)
+    # the token appended each step lives at position CTX-1 of every sequence
+    new_slots = (block_table[:, (CTX - 1) // BS].long() * BS + (CTX - 1) % BS).contiguous()
+    cpu_gen = torch.Generator().manual_seed(SEED + 1)
+    q_host = torch.randn(batch, hq, D, generator=cpu_gen).bfloat16().pin_memory()
+    k_host = torch.randn(batch, hkv, D, generator=cpu_gen).bfloat16().pin_memory()
+    v_host = torch.randn(batch, hkv, D, generator=cpu_gen).bfloat16().pin_memory()
+    return dict(batch=batch, hkv=hkv, hq=hq, rot=rot, even=even, odd=odd, kc=kc, kb=kb, vc=vc, vb=vb,
+                caches=caches, block_table=block_table, seq_lens=seq_lens, new_slots=new_slots,
+                q_host=q_host, k_host=k_host, v_host=v_host, width=width, nblk=nblk)
+
+
+def run_ours(args, rank, world, device):
+    from turboquant_vllm import _native as nv
+    from turboquant_vllm.kernels import ops
+
+    wl = build_workload(device, world, args.layers)
+    batch, hkv, hq = wl["batch"], wl["hkv"], wl["hq"]
+    q = wl["q_host"].to(device)
+    k_new, v_new = wl["k_host"].to(device), wl["v_host"].to(device)
+    out = torch.empty(batch, hq, D, dtype=torch.bfloat16, device=device)
+    ws = torch.empty(ops.attention_workspace_bytes(batch, hq, hkv, D), dtype=torch.uint8, device=device)
+
+    def step(i, q_=q, k_=k_new, v_=v_new, slots_=wl["new_slots"], bt_=wl["block_table"], sl_=wl["seq_lens"]):
+        cache = wl["caches"][i % args.layers]
+        ops.tq4_write_paged(k_, v_, cache, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"])
+        ops.fused_paged_tq4_decode(q_, cache, bt_, sl_, wl["kc"], wl["rot"], hkv, D, BS, None, out,
+                                   v_centroids=wl["vc"], workspace=ws, mode=args.mode)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    ms_total = timed(step, args.steps)
+    clocks = sampler.stop()
+    ms_step = ms_total / args.steps
+    value = batch * args.steps / (ms_total * 1e-3)
+
+    # ---- per-kernel durations: an identical second pass with event brackets per kernel ------
+    nsamp = min(args.steps, 2000)
+    nv.profile_start(nsamp)
+    timed(step, nsamp)
+    nv.profile_stop()
+    prof = {name: nv.profile_read(kind, nsamp) for name, kind in
+            (("write", nv.PROF_WRITE), ("prologue", nv.PROF_PROLOGUE), ("attention", nv.PROF_ATTENTION),
+             ("combine", nv.PROF_COMBINE))}
+    avg = {k: (sum(v) / len(v) if v else None) for k, v in prof.items()}
+    alg_bytes = batch * CTX * hkv * (D + 8)  # 136 B per token per KV head at D=128
+    peak, peak_kind = measured_peak_gbs()
+    achieved = alg_bytes / (avg["attention"] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "kernel": "paged TQ4 attention (streaming) kernel", "peak_kind": f"of {peak_kind}",
+                "algorithmic_bytes_per_launch": alg_bytes,
+                "kernel_ms": {k: (round(v, 5) if v is not None else None) for k, v in avg.items()},
+                "frac_of_nominal_8TBs": round(achieved / 8000.0, 4)}
+
+    # ---- compress throughput (prefill-sized write: 16384 tokens, K and V) -----------------------
+    gen = torch.Generator(device=device).manual_seed(7)
+    nt = 16384
+    kc_, vc_ = synth_kv_gpu(nt, hkv, gen, device)
+    cslots = torch.arange(nt, device=device)
+
+    def wstep(i):
+        ops.tq4_write_paged(kc_, vc_, wl["caches"][i % args.layers], cslots, wl["even"], wl["odd"],
+                            wl["kb"], wl["vb"])
+
+    for i in range(3):
+        wstep(i)
+    wms = timed(wstep, 20) / 20
+    compress_mtok_s = nt / (wms * 1e-3) / 1e6
+    # restore the rows the compress timing overwrote is unnecessary: bytes stay valid TQ4 rows
+
+    # ---- end to end through the public API with host buffers ------------------------------------
+    q_d, k_d, v_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
+    slots_h = wl["new_slots"].cpu().pin_memory()
+    bt_h = wl["block_table"].cpu().pin_memory()
+    sl_h = wl["seq_lens"].cpu().pin_memory()
+    slots_d, bt_d, sl_d = torch.empty_like(wl["new_slots"]), torch.empty_like(wl["block_table"]), torch.empty_like(wl["seq_lens"])
+    out_h = torch.empty(batch, hq, D, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        q_d.copy_(wl["q_host"], non_blocking=True)
+        k_d.copy_(wl["k_host"], non_blocking=True)
+        v_d.copy_(wl["v_host"], non_blocking=True)
+        slots_d.copy_(slots_h, non_blocking=True)
+        bt_d.copy_(bt_h, non_blocking=True)
+        sl_d.copy_(sl_h, non_blocking=True)
+        step(i, q_d, k_d, v_d, slots_d, bt_d, sl_d)
+        out_h.copy_(out, non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, args.steps)
+    h2d = sum(x.numel() * x.element_size() for x in (wl["q_host"], wl["k_host"], wl["v_host"], slots_h, bt_h, sl_h))
+    d2h = out_h.numel() * out_h.element_size()
+    e2e = {"value": round(batch * args.steps / (e2e_ms * 1e-3), 1), "unit": "tok/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": round(e2e_ms / args.steps, 5)}
+
+    line = {
+        "metric": "paged_tq4_decode_tok_per_s", "value": round(value, 1), "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {
+            "workload": "Llama-3.1-8B-shaped single-layer paged TQ4 decode: cache write of 1 token/seq + "
+                        "fused paged decode; batch 64/GPU x ctx 4096, 32q/8kv heads (sharded over GPUs), "
+                        "head_dim 128, block 16 shuffled, K4/V4, bf16 q",
+            "global_batch": batch, "seq_len": CTX, "kv_heads_per_gpu": hkv, "q_heads_per_gpu": hq,
+            "parallelism": f"tp{world} head-sharded, no collective",
+            "l2": f"inputs>L2: {args.layers} rotating layer caches of {wl['nblk'] * BS * wl['width'] / 1e6:.0f} MB",
+            "kernel_mode": args.mode,
+        },
+        "hbm_gbs": round(alg_bytes / (ms_step * 1e-3) / 1e9, 1),
+        "compress_mtok_s": round(compress_mtok_s, 3),
+        "compress_config": f"{nt} tokens x {hkv} KV heads, K and V, bf16 -> paged cache, one launch",
+        "roofline": roofline, "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_budget)
+    return line
+
+
+# ----------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's PyTorch path
+# ----------------------------------------------------------------------------------------
+def cpu_workload(n_seqs, hkv=HKV, hq=HQ):
+    from oracle import tq4_oracle as O
+
+    cents, bounds = O.solve_lloyd_max(D, K_BITS)
+    rot = O.rotation_matrix(D, 42)
+    nblk = n_seqs * CTX // BS
+    cache = torch.zeros(nblk, BS, O.row_layout(hkv, D)[3], dtype=torch.uint8)
+    g = torch.Generator().manual_seed(SEED)
+    perm = torch.randperm(nblk, generator=g)
+    bt = perm.view(n_seqs, CTX // BS).to(torch.int32)
+    pos = torch.arange(CTX)
+    for s in range(n_seqs):
+        k, v = O.synthetic_kv(CTX, hkv, D, seed=SEED + s, dtype=torch.bfloat16)
+        slots = bt[s].long()[pos // BS] * BS + pos % BS
+        kp, kn = O.compress_rows(k, rot, bounds)
+        vp, vn = O.compress_rows(v, rot, bounds)
+        cache.view(-1, cache.shape[-1])[slots] = O.assemble_rows(kp, kn, vp, vn)
+    q = torch.randn(n_seqs, hq, D, generator=g).bfloat16()
+    k_new, v_new = O.synthetic_kv(n_seqs, hkv, D, seed=99, dtype=torch.bfloat16)
+    new_slots = bt[:, (CTX - 1) // BS].long() * BS + (CTX - 1) % BS
+    return dict(O=O, cents=cents, bounds=bounds, rot=rot, cache=cache, bt=bt, q=q, k_new=k_new,
+                v_new=v_new, new_slots=new_slots, n_seqs=n_seqs, hkv=hkv)
+
+
+def cpu_step(w):
+    O = w["O"]
+    O.write_paged(w["k_new"], w["v_new"], w["cache"], w["new_slots"], w["rot"], w["bounds"], w["bounds"])
+    return O.paged_decode_fp32(w["q"], w["cache"], w["bt"], [CTX] * w["n_seqs"], w["cents"], w["cents"],
+                               w["rot"], w["hkv"])
+
+
+def cpu_baseline(budget_s=15.0):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = cpu_workload(2)
+    cpu_step(w)
+    t0 = time.perf_counter()
+    cpu_step(w)
+    per = (time.perf_counter() - t0) / 2
+    reps = max(1, min(50, int(budget_s / max(per * 2, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu_step(w)
+    dt = time.perf_counter() - t0
+    return {"value": round(2 * reps / dt, 2), "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{reps} steps of 2 of the 64 sequences (ctx 4096, 8 KV heads): write 1 token/seq + fp32 "
+                      "decode with the CPU restatement of the reference's PyTorch path"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n_seqs = 2
+    w = cpu_workload(n_seqs)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_step(w)
+    steps = max(1, min(args.steps, 40))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(w)
+    dt = time.perf_counter() - t0
+    val = round(n_seqs * steps / dt, 2)
+    sample = (f"each step = 2 of the {BATCH_PER_GPU_UNIT * world} sequences (ctx 4096, 8 KV heads): cache write of "
+              "1 token/seq + fp32 paged decode, CPU restatement of the reference's PyTorch path (oracle/), "
+              f"{steps} timed steps")
+    return {
+        "impl": "reference", "metric": "paged_tq4_decode_tok_per_s", "value": val, "unit": "tok/s",
+        "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 3)),
+        "ms_per_step": round(dt / steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "Llama-3.1-8B-shaped single-layer paged TQ4 decode (CPU sample)",
+                   "global_batch": BATCH_PER_GPU_UNIT * world, "seq_len": CTX},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", type=int, default=0, help="0 auto, 1 fp32 CUDA-core kernel, 2 tensor-core LUT kernel")
+    ap.add_argument("--layers", type=int, default=4, help="distinct layer caches rotated per step")
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    if HKV % world:
+        raise SystemExit(f"{HKV} KV heads cannot be sharded over {world} GPUs")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    line = run_ours(args, rank, world, device)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -181,6 +181,24 @@ int tq4_combine_partials(const float* parts_o, const float* parts_lse, int world
                          void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
                          void* stream);
 
+/*
+ * Per-kernel timing aid (no counterpart in the reference, which times with torch.cuda.Event
+ * around whole Python calls, experiments/experiment_020_fused_paged_decode_benchmark.py:232-256).
+ * After tq4_profile_start(n) every entry point brackets its kernels with CUDA events recorded
+ * on the caller's stream (up to n samples per kind); tq4_profile_read(kind, ms, max) waits for
+ * the recorded events and returns the elapsed milliseconds of each sample.  Host calls; not
+ * for use during stream capture.
+ */
+#define TQ4_PROF_WRITE 0     /* fused paged cache write kernel            */
+#define TQ4_PROF_PROLOGUE 1  /* query rotation + tile plan kernel         */
+#define TQ4_PROF_ATTENTION 2 /* streaming attention kernel (dominant)     */
+#define TQ4_PROF_COMBINE 3   /* split merge + un-rotation kernel          */
+#define TQ4_PROF_COMPRESS 4  /* contiguous compress-rows kernel           */
+#define TQ4_PROF_KINDS 5
+int tq4_profile_start(int max_samples);
+int tq4_profile_stop(void);
+int tq4_profile_read(int kind, float* ms_out, int max_out); /* returns #samples, -1 on error */
+
 #ifdef __cplusplus
 }
 #endif

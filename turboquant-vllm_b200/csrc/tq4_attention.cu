@@ -616,9 +616,13 @@ extern "C" int tq4_paged_attention(
   for (int64_t r0 = 0; r0 < num_rows; r0 += kMaxRowsPerLaunch) {
     a.sh.rows = (int)((num_rows - r0) < kMaxRowsPerLaunch ? (num_rows - r0) : kMaxRowsPerLaunch);
     a.sh.row_offset = (int)r0;
+    prof_begin(TQ4_PROF_PROLOGUE, st);
     int rc = launch_qrot_plan(a, st);
+    prof_end(TQ4_PROF_PROLOGUE, st);
     if (rc != TQ4_OK) return rc;
+    prof_begin(TQ4_PROF_ATTENTION, st);
     rc = use_mma ? launch_attention_mma(a, st) : launch_attention_fp32(a, st);
+    prof_end(TQ4_PROF_ATTENTION, st);
     if (rc != TQ4_OK) return rc;
     CombineArgs c{};
     c.slot_base = a.plan.slot_base;
@@ -636,7 +640,9 @@ extern "C" int tq4_paged_attention(
     c.out_head_stride = out_head_stride;
     c.lse_out = lse_out;
     c.out_rotated = out_rotated;
+    prof_begin(TQ4_PROF_COMBINE, st);
     rc = launch_combine(c, head_dim, st);
+    prof_end(TQ4_PROF_COMBINE, st);
     if (rc != TQ4_OK) return rc;
   }
   return TQ4_OK;

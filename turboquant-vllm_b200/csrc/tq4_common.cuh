@@ -19,6 +19,10 @@
 
 namespace tq4 {
 
+// per-kernel event timing (tq4_profile.cu); no-ops unless tq4_profile_start() was called
+void prof_begin(int kind, cudaStream_t st);
+void prof_end(int kind, cudaStream_t st);
+
 __host__ __device__ inline bool supported_head_dim(int d) {
   return d == 64 || d == 96 || d == 128 || d == 256;
 }

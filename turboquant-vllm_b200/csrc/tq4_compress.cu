@@ -272,7 +272,10 @@ extern "C" int tq4_compress_rows(const void* x, int x_dtype, int64_t n_tokens, i
   a.rot_odd = rot_t_odd;
   a.packed_out = packed_out;
   a.norms_out = norms_out;
-  return tq4::dispatch_compress(a, head_dim, x_dtype, (cudaStream_t)stream);
+  tq4::prof_begin(TQ4_PROF_COMPRESS, (cudaStream_t)stream);
+  const int rc = tq4::dispatch_compress(a, head_dim, x_dtype, (cudaStream_t)stream);
+  tq4::prof_end(TQ4_PROF_COMPRESS, (cudaStream_t)stream);
+  return rc;
 }
 
 extern "C" int tq4_pack_rotated_rows(const float* rotated, int64_t n_rows, int head_dim,
@@ -334,5 +337,8 @@ extern "C" int tq4_write_paged(const void* key, const void* value, int kv_dtype,
   a.cache_token_stride = cache_token_stride;
   a.num_cache_slots = num_cache_slots;
   a.err_flag = err_flag;
-  return tq4::dispatch_compress(a, head_dim, kv_dtype, (cudaStream_t)stream);
+  tq4::prof_begin(TQ4_PROF_WRITE, (cudaStream_t)stream);
+  const int rc = tq4::dispatch_compress(a, head_dim, kv_dtype, (cudaStream_t)stream);
+  tq4::prof_end(TQ4_PROF_WRITE, (cudaStream_t)stream);
+  return rc;
 }

@@ -44,7 +44,28 @@ _SIGNATURES = {
                                     c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
     "tq4_combine_partials": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                      c_void_p, c_int, c_int64, c_int64, c_void_p]),
+    "tq4_profile_start": (c_int, [c_int]),
+    "tq4_profile_stop": (c_int, []),
+    "tq4_profile_read": (c_int, [c_int, c_void_p, c_int]),
 }
+
+PROF_WRITE, PROF_PROLOGUE, PROF_ATTENTION, PROF_COMBINE, PROF_COMPRESS = range(5)
+
+
+def profile_start(max_samples: int) -> None:
+    check(lib().tq4_profile_start(max_samples), "tq4_profile_start")
+
+
+def profile_stop() -> None:
+    lib().tq4_profile_stop()
+
+
+def profile_read(kind: int, max_samples: int) -> list[float]:
+    buf = (c_float * max_samples)()
+    n = lib().tq4_profile_read(kind, ctypes.cast(buf, c_void_p), max_samples)
+    if n < 0:
+        raise RuntimeError("tq4_profile_read failed")
+    return [float(buf[i]) for i in range(n)]
 
 
 def library_path() -> str:
