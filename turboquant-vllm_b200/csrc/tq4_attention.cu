@@ -538,7 +538,10 @@ extern "C" size_t tq4_attention_workspace_bytes(int64_t max_query_rows, int num_
   if (max_query_rows <= 0 || !tq4::make_shape(sh, num_q_heads, num_kv_heads, head_dim)) return 0;
   const int64_t rows = max_query_rows < tq4::kMaxRowsPerLaunch ? max_query_rows : tq4::kMaxRowsPerLaunch;
   tq4::AttnPlan p;
-  return tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, sh.TPC);
+  const size_t a = tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, sh.TPC);
+  tq4::make_shape(sh, num_q_heads, num_kv_heads, head_dim, tq4::kMmaWarpsPerCta);
+  const size_t b = tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, sh.TPC);
+  return a > b ? a : b;
 }
 
 extern "C" int tq4_paged_attention(
@@ -569,6 +572,12 @@ extern "C" int tq4_paged_attention(
       cache_token_stride < row_data_bytes(num_kv_heads, head_dim))
     return TQ4_ERR_INVALID_ARG;
   if (query_start_loc == nullptr && num_rows > num_seqs) return TQ4_ERR_INVALID_ARG;
+  const bool mma_ok = attention_mma_supported(a.sh, block_size, cache, cache_block_stride,
+                                              cache_token_stride);
+  if (mode == 2 && !mma_ok) return TQ4_ERR_UNSUPPORTED;
+  const bool use_mma = mode == 2 || (mode == 0 && mma_ok);
+  if (use_mma)
+    make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC));
   const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
   if (workspace_bytes < carve_plan(a.plan, nullptr, rows_cap, num_q_heads, head_dim, a.sh.TPC))
     return TQ4_ERR_WORKSPACE;
@@ -594,6 +603,8 @@ extern "C" int tq4_paged_attention(
   a.n_v_centroids = n_v_centroids;
   a.rotation = rotation;
   a.scale_log2e = sm_scale * 1.4426950408889634f;
+  a.lut_scale_k = lut_scale(head_dim, n_k_centroids);
+  a.lut_scale_v = lut_scale(head_dim, n_v_centroids);
   a.causal = causal;
   a.sliding_window = sliding_window > 0 ? sliding_window : 0;
   a.out = out;
@@ -604,10 +615,8 @@ extern "C" int tq4_paged_attention(
   a.out_rotated = out_rotated;
   a.err_flag = err_flag;
 
-  const bool use_mma = mode == 2 || (mode == 0 && attention_mma_supported(a.sh, block_size));
-  if (mode == 2 && !attention_mma_supported(a.sh, block_size)) return TQ4_ERR_UNSUPPORTED;
   const int sms = sm_count();
-  int ctas = (use_mma ? 2 : 4) * sms / a.sh.n_slices;
+  int ctas = (use_mma ? 1 : 4) * sms / a.sh.n_slices;
   if (ctas < 1) ctas = 1;
   if (ctas > kMaxCtasPerSlice) ctas = kMaxCtasPerSlice;
   a.sh.ctas = ctas;

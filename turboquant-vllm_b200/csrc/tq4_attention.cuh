@@ -12,11 +12,13 @@
 //   * the combine kernel merges the slots of a row, normalises and un-rotates.
 #pragma once
 #include "tq4_common.cuh"
+#include "tq4_lut_scale.h"
 
 namespace tq4 {
 
 constexpr int kTileTokens = 16;
-constexpr int kMaxWarpsPerCta = 8;
+constexpr int kMaxWarpsPerCta = 8;     // fp32 kernel
+constexpr int kMmaWarpsPerCta = 16;    // tensor-core LUT kernel (one CTA per SM)
 constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace sizing
 constexpr int kMaxRowsPerLaunch = 4096;    // larger query batches are processed in pieces
 
@@ -63,6 +65,7 @@ struct AttnArgs {
   int n_k_centroids, n_v_centroids;
   const float* rotation;
   float scale_log2e;  // sm_scale * log2(e)
+  float lut_scale_k, lut_scale_v;  // fp16 LUT scale factors (tensor-core kernel)
   int causal, sliding_window;
   void* out;
   int out_dtype;
@@ -76,16 +79,16 @@ inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
 
 // Split Hq query heads over warps: a VIRTUAL head is one KV head plus up to 8 of its query
 // heads; a CTA holds HPC virtual heads x TPC tile phases = at most 8 warps.
-inline bool make_shape(AttnShape& s, int Hq, int Hkv, int D) {
+inline bool make_shape(AttnShape& s, int Hq, int Hkv, int D, int max_warps = kMaxWarpsPerCta) {
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return false;
   s.Hq = Hq; s.Hkv = Hkv; s.D = D; s.G = Hq / Hkv;
   s.NCH = (s.G + 7) / 8;
   s.GC = (s.G + s.NCH - 1) / s.NCH;
   const int vh = Hkv * s.NCH;
   s.HPC = 1;
-  for (int c = kMaxWarpsPerCta; c >= 1; --c)
+  for (int c = max_warps; c >= 1; --c)
     if (vh % c == 0) { s.HPC = c; break; }
-  s.TPC = kMaxWarpsPerCta / s.HPC;
+  s.TPC = max_warps / s.HPC;
   s.n_slices = vh / s.HPC;
   return true;
 }
@@ -116,6 +119,8 @@ inline size_t carve_plan(AttnPlan& p, void* ws, int64_t rows, int Hq, int D, int
 // Launchers implemented in tq4_attention.cu / tq4_decode_mma.cu.
 int launch_attention_fp32(const AttnArgs& a, cudaStream_t st);
 int launch_attention_mma(const AttnArgs& a, cudaStream_t st);  // returns TQ4_ERR_UNSUPPORTED if shape not covered
-bool attention_mma_supported(const AttnShape& sh, int block_size);
+int mma_warps_per_cta(int D, int GC);
+bool attention_mma_supported(const AttnShape& sh, int block_size, const uint8_t* cache,
+                             int64_t block_stride, int64_t token_stride);
 
 }  // namespace tq4
