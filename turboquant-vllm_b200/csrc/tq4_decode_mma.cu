@@ -16,9 +16,12 @@
 // two LOP3s per 8 nibbles before the lookup.  Table entries are fp16(alpha * centroid) with a
 // per-codebook alpha (tq4_lut_scale.h) that puts all centroid magnitudes near fp16 grid points;
 // 1/alpha is folded into the fp32 score scale and the output.  Norms are factored out: scores are scaled by
-// knorm in fp32, probabilities by vnorm before the split.  Packed bytes go global -> registers
-// directly (each byte is used once); the next tile is prefetched while the current one is
-// consumed.
+// knorm in fp32, probabilities by vnorm before the split.
+//
+// Data movement: every thread cp.async-copies exactly the cache bytes it will consume itself
+// into a private slot of a per-warp shared-memory ring, kStages tiles ahead (no registers are
+// held by loads in flight, no cross-thread synchronisation is needed), and reads them back
+// with conflict-free 16/8-byte shared loads right before use.
 #include <math_constants.h>
 
 #include "tq4_attention.cuh"
@@ -28,7 +31,7 @@ namespace tq4 {
 namespace {
 
 constexpr uint32_t kTableBytes = 65536;
-constexpr uint32_t kMmaSmemBytes = 2 * kTableBytes;  // slack to reach a 64 KB boundary
+constexpr int kStages = 4;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -69,87 +72,113 @@ __device__ __forceinline__ uint32_t split_h2(float x) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-__device__ __forceinline__ uint32_t ldg_stream_b32(const uint8_t* p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
-__device__ __forceinline__ uint32_t ldg_stream_b16(const uint8_t* p) {
-  uint16_t v;
-  asm volatile("ld.global.nc.L1::no_allocate.b16 %0, [%1];" : "=h"(v) : "l"(p));
-  return (uint32_t)v;
-}
-__device__ __forceinline__ void ldg_stream_v2(const uint8_t* p, uint32_t& a, uint32_t& b) {
-  asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];" : "=r"(a), "=r"(b) : "l"(p));
-}
-__device__ __forceinline__ void ldg_stream_v4(const uint8_t* p, uint32_t& a, uint32_t& b,
-                                              uint32_t& c, uint32_t& d) {
-  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
-               : "l"(p));
-}
-__device__ __forceinline__ float ldg_f32(const uint8_t* p) {
-  float v;
-  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
-  return v;
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
-template <int D>
+template <int BYTES>
+__device__ __forceinline__ void cp_async(uint32_t dst, const uint8_t* src) {
+  if (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+  else if (BYTES == 8)
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int BYTES>
+__device__ __forceinline__ void lds_words(uint32_t addr, uint32_t* out) {
+  if (BYTES == 16)
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3]) : "r"(addr));
+  else if (BYTES == 8)
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(out[0]), "=r"(out[1]) : "r"(addr));
+  else
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(out[0]) : "r"(addr));
+}
+
+template <int D, bool ALIGNED>
 struct MmaCfg {
   static constexpr int HALF = D / 2;
-  static constexpr int KS = D / 16;      // k-steps of the K-side product
-  static constexpr int KW = D / 32;      // 32-bit words of K per thread per token (D/8 bytes)
-  static constexpr int VB = D / 16;      // V bytes per thread per token
-  static constexpr int VW = VB / 4;      // ... as full words
-  static constexpr int VH = (VB % 4) / 2;  // ... plus half-words (D = 96)
-  static constexpr int MB = VB;          // m-blocks of the V-side product
-  static constexpr int DPT = D / 4;      // query dims held per thread
-};
-
-template <int D>
-struct TileRegs {
-  uint32_t k[2][MmaCfg<D>::KW];                       // tokens g, g+8
-  uint32_t v[4][MmaCfg<D>::VW + MmaCfg<D>::VH];       // tokens 2c, 2c+1, 2c+8, 2c+9
-  float kn[2], vn[2];                                 // norms of tokens g, g+8
-  int pos0;                                           // absolute position of the tile's token 0
-  uint32_t okmask;                                    // bit j: token j's page is valid
+  static constexpr int KS = D / 16;         // k-steps of the K-side product
+  static constexpr int KBY = D / 8;         // K bytes per thread per token
+  static constexpr int KW = KBY / 4;        // ... as 32-bit words
+  static constexpr int VBY = D / 16;        // V bytes per thread per token
+  static constexpr int VW = VBY / 4;        // ... full words
+  static constexpr int VH = (VBY % 4) / 2;  // ... plus one half-word (D = 96)
+  static constexpr int MB = VBY;            // m-blocks of the V-side product
+  static constexpr int DPT = D / 4;         // query dims held per thread
+  // cp.async unit sizes (bytes) and counts
+  static constexpr int UK = ALIGNED ? (KBY >= 16 ? 16 : KBY) : 4;
+  static constexpr int NK = KBY / UK;
+  static constexpr int UV = ALIGNED ? (4 * VW >= 16 ? 16 : 4 * VW) : 4;
+  static constexpr int NV = (4 * VW) / UV;
+  // per-warp bytes of one ring stage: K (2 tokens) + V (4 tokens: words + half-word unit) + norms
+  static constexpr int kVTok = 32 * (4 * VW + 4 * VH);
+  static constexpr int kOffK1 = 32 * KBY;
+  static constexpr int kOffV = 64 * KBY;
+  static constexpr int kOffN = kOffV + 4 * kVTok;
+  static constexpr int kStageBytes = kOffN + 32 * 16;
 };
 
 // byte offset (within a head's D/2 V bytes) of this thread's m-block i
 template <int D>
 __device__ __forceinline__ int v_byte_of_mblock(int g, int i) {
-  using C = MmaCfg<D>;
-  return i < 4 * C::VW ? g * 4 * C::VW + i : 32 * C::VW + 2 * g + (i - 4 * C::VW);
+  constexpr int VW = (D / 16) / 4;
+  return i < 4 * VW ? g * 4 * VW + i : 32 * VW + 2 * g + (i - 4 * VW);
 }
 
 template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const AttnArgs a) {
-  using C = MmaCfg<D>;
+__global__ void __launch_bounds__(WARPS * 32, 1)
+attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
+  using C = MmaCfg<D, ALIGNED>;
   const AttnShape& sh = a.sh;
   const AttnPlan& p = a.plan;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ float s_cent[2][TQ4_MAX_CENTROIDS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+
+  // ---- shared memory map: [rings A][64 KB table on a 64 KB boundary][rings B] ------------------
   const uint32_t base = smem_u32(smem_raw);
   const uint32_t tab = (base + (kTableBytes - 1)) & ~(kTableBytes - 1);
-  if (tab + kTableBytes > base + kMmaSmemBytes) {  // cannot happen for a window base < 64 KB
+  constexpr uint32_t kRing = kStages * C::kStageBytes;
+  const uint32_t n_a = (tab - base) / kRing;
+  const uint32_t end = base + smem_total;
+  const uint32_t ring =
+      warp < (int)n_a ? base + warp * kRing : tab + kTableBytes + (warp - n_a) * kRing;
+  if (tab + kTableBytes > end || ring + kRing > end) {  // the host sized smem_total to fit
     if (threadIdx.x == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
     return;
   }
-  // ---- build the replicated byte -> half2 tables: slot l < 32 = K table of lane l, 32+l = V ----
+  // ---- replicated byte -> half2 tables: slot l < 32 = K table of lane l, slot 32 + l = V -------
+  if (threadIdx.x < 2 * TQ4_MAX_CENTROIDS) {
+    const int w = threadIdx.x >> 4, i = threadIdx.x & 15;
+    const float* cent = w ? a.v_centroids : a.k_centroids;
+    const int nc = w ? a.n_v_centroids : a.n_k_centroids;
+    s_cent[w][i] = i < nc ? __fmul_rn(w ? a.lut_scale_v : a.lut_scale_k, cent[i]) : 0.f;
+  }
+  __syncthreads();
   {
     uint32_t* t = reinterpret_cast<uint32_t*>(smem_raw + (tab - base));
     for (int i = threadIdx.x; i < 256 * 64; i += blockDim.x) {
-      const int byte = i >> 6, slot = i & 63;
-      const float* cent = slot < 32 ? a.k_centroids : a.v_centroids;
-      const int nc = slot < 32 ? a.n_k_centroids : a.n_v_centroids;
-      const float al = slot < 32 ? a.lut_scale_k : a.lut_scale_v;
-      const int hi = byte >> 4, lo = byte & 15;
-      t[i] = pack_h2(hi < nc ? __fmul_rn(al, cent[hi]) : 0.f, lo < nc ? __fmul_rn(al, cent[lo]) : 0.f);
+      const int byte = i >> 6, w = (i >> 5) & 1;
+      t[i] = pack_h2(s_cent[w][byte >> 4], s_cent[w][byte & 15]);
     }
   }
   __syncthreads();
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, c = lane & 3;
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
 
   const int cta = blockIdx.x % sh.ctas, slice = blockIdx.x / sh.ctas;
@@ -161,9 +190,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
   const int t_begin = cta * tps, t_end = min(total, t_begin + tps);
   if (t_begin >= t_end) return;
   const RowLayout lay = row_layout(sh.Hkv, D);
-  const int k_off = lay.k_idx + kvh * C::HALF + c * (D / 8);
-  const int kn_off = lay.k_norm + kvh * 4, vn_off = lay.v_norm + kvh * 4;
-  const int v_off = lay.v_idx + kvh * C::HALF;
+  const int k_off = lay.k_idx + kvh * C::HALF + c * C::KBY;  // this thread's K chunk
+  const int kn_off = lay.k_norm + kvh * 4;
+  const int vn_delta = lay.v_norm - lay.k_norm;              // V norm sits this far after the K norm
+  const int v_off = lay.v_idx + kvh * C::HALF + g * 4 * C::VW;  // this thread's V word chunk
+  const int vh_off = lay.v_idx + kvh * C::HALF + 32 * C::VW + 4 * (g >> 1);  // word with its half-word
+  const uint32_t ts32 = (uint32_t)a.cache_token_stride;
+  const int bs_shift = (a.block_size & (a.block_size - 1)) == 0 ? __ffs(a.block_size) - 1 : -1;
 
   int r;
   {
@@ -186,7 +219,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
 
     // ---- query fragments: column g of n-block nb = head nb*4 + g/2, term g%2 (hi / lo) ------
     uint32_t qf[NB][C::KS][2];
-    float fscale[NB];  // qmax * sm_scale * log2(e) of head nb*4 + c
+    float fscale[NB];  // qmax * sm_scale * log2(e) / alpha_k of head nb*4 + c
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       const int hh = nb * 4 + (g >> 1);
@@ -221,7 +254,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
         qf[nb][s][0] = pack_h2(v[4 * s], v[4 * s + 1]);
         qf[nb][s][1] = pack_h2(v[4 * s + 2], v[4 * s + 3]);
       }
-      // head nb*4 + c lives in column 2c: take its qmax from lane g' = 2c
+      // head nb*4 + c lives in columns 2c, 2c+1: take its qmax from lane g' = 2c
       fscale[nb] = __shfl_sync(0xffffffffu, qmax, 8 * c) * (a.scale_log2e / a.lut_scale_k);
     }
 
@@ -236,144 +269,157 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
         for (int e = 0; e < 4; ++e) acc[i][nb][e] = 0.f;
     }
 
-    // ---- tile loader ---------------------------------------------------------------------
-    auto row_offset = [&](int pos, bool& ok) -> int64_t {
-      // byte offset of the token row at absolute position pos (clamped into the row's range)
+    auto pos0_of = [&](int tt) { return (tile0 + (tt - row_t0)) * kTileTokens; };
+    auto page_of = [&](int pos0) { return bs_shift >= 0 ? (pos0 >> bs_shift) : (pos0 / a.block_size); };
+    auto token_row = [&](int pos) -> const uint8_t* {  // generic addressing: one lookup per token
       const int pc = min(max(pos, kv_start), kv_end - 1);
-      const int blk = bt[pc / a.block_size];
-      ok = blk >= 0 && blk < a.num_blocks;
-      if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
-      return (int64_t)(ok ? blk : 0) * a.cache_block_stride +
+      const int blk = __ldg(bt + pc / a.block_size);
+      const bool ok = blk >= 0 && blk < a.num_blocks;
+      return a.cache + (int64_t)(ok ? blk : 0) * a.cache_block_stride +
              (int64_t)(pc % a.block_size) * a.cache_token_stride;
     };
-    auto load_tile = [&](int tt, TileRegs<D>& R) {
-      const int pos0 = (tile0 + (tt - row_t0)) * kTileTokens;
-      R.pos0 = pos0;
-      int64_t off_k0, off_k1, off_v[4];
+    // ---- issue the cp.async copies of one tile into ring stage st; returns 1 if its page is valid
+    auto issue_tile = [&](int tt, int blk, int st) -> uint32_t {
+      const int pos0 = pos0_of(tt);
+      const uint32_t sb = ring + st * C::kStageBytes;
+      const uint8_t *rk0, *rk1, *rv[4];
+      uint32_t ok = 1;
       if (PAGE16) {
-        bool ok;
-        const int64_t b0 = row_offset(max(pos0, kv_start), ok) -
-                           (int64_t)(max(pos0, kv_start) - pos0) * a.cache_token_stride;
-        R.okmask = ok ? 0xFFFFu : 0u;
-        off_k0 = b0 + (int64_t)g * a.cache_token_stride;
-        off_k1 = off_k0 + 8 * a.cache_token_stride;
-        off_v[0] = b0 + (int64_t)(2 * c) * a.cache_token_stride;
-        off_v[1] = off_v[0] + a.cache_token_stride;
-        off_v[2] = off_v[0] + 8 * a.cache_token_stride;
-        off_v[3] = off_v[2] + a.cache_token_stride;
+        ok = blk >= 0 && blk < a.num_blocks;
+        if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+        const int inpage = bs_shift >= 0 ? (pos0 & (a.block_size - 1)) : (pos0 % a.block_size);
+        const uint8_t* pb = a.cache + (int64_t)(ok ? blk : 0) * a.cache_block_stride +
+                            (int64_t)inpage * a.cache_token_stride;
+        rk0 = pb + g * ts32;
+        rk1 = rk0 + 8 * ts32;
+        rv[0] = pb + 2 * c * ts32;
+        rv[1] = rv[0] + ts32;
+        rv[2] = rv[0] + 8 * ts32;
+        rv[3] = rv[2] + ts32;
       } else {
-        bool ok0, ok1, okv;
-        off_k0 = row_offset(pos0 + g, ok0);
-        off_k1 = row_offset(pos0 + g + 8, ok1);
-        // every lane publishes the validity of tokens g and g+8; gather the 16-bit mask
-        const uint32_t b0 = __ballot_sync(0xffffffffu, ok0), b1 = __ballot_sync(0xffffffffu, ok1);
-        uint32_t mask = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mask |= (((b0 >> (4 * j)) & 1u) << j) | (((b1 >> (4 * j)) & 1u) << (j + 8));
-        R.okmask = mask;
-        off_v[0] = row_offset(pos0 + 2 * c, okv);
-        off_v[1] = row_offset(pos0 + 2 * c + 1, okv);
-        off_v[2] = row_offset(pos0 + 2 * c + 8, okv);
-        off_v[3] = row_offset(pos0 + 2 * c + 9, okv);
+        rk0 = token_row(pos0 + g);
+        rk1 = token_row(pos0 + g + 8);
+        rv[0] = token_row(pos0 + 2 * c);
+        rv[1] = token_row(pos0 + 2 * c + 1);
+        rv[2] = token_row(pos0 + 2 * c + 8);
+        rv[3] = token_row(pos0 + 2 * c + 9);
       }
-      const uint8_t* k0 = a.cache + off_k0;
-      const uint8_t* k1 = a.cache + off_k1;
-      if (ALIGNED && C::KW % 4 == 0) {
 #pragma unroll
-        for (int w = 0; w < C::KW; w += 4) {
-          ldg_stream_v4(k0 + k_off + 4 * w, R.k[0][w], R.k[0][w + 1], R.k[0][w + 2], R.k[0][w + 3]);
-          ldg_stream_v4(k1 + k_off + 4 * w, R.k[1][w], R.k[1][w + 1], R.k[1][w + 2], R.k[1][w + 3]);
-        }
-      } else if (ALIGNED && C::KW % 2 == 0) {
-#pragma unroll
-        for (int w = 0; w < C::KW; w += 2) {
-          ldg_stream_v2(k0 + k_off + 4 * w, R.k[0][w], R.k[0][w + 1]);
-          ldg_stream_v2(k1 + k_off + 4 * w, R.k[1][w], R.k[1][w + 1]);
-        }
-      } else {
-#pragma unroll
-        for (int w = 0; w < C::KW; ++w) {
-          R.k[0][w] = ldg_stream_b32(k0 + k_off + 4 * w);
-          R.k[1][w] = ldg_stream_b32(k1 + k_off + 4 * w);
-        }
+      for (int u = 0; u < C::NK; ++u) {
+        cp_async<C::UK>(sb + u * 32 * C::UK + lane * C::UK, rk0 + k_off + u * C::UK);
+        cp_async<C::UK>(sb + C::kOffK1 + u * 32 * C::UK + lane * C::UK, rk1 + k_off + u * C::UK);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint8_t* vp = a.cache + off_v[j] + v_off;
-        if (ALIGNED && C::VW == 4) {
-          ldg_stream_v4(vp + g * 16, R.v[j][0], R.v[j][1], R.v[j][2], R.v[j][3]);
-        } else if (ALIGNED && C::VW == 2) {
-          ldg_stream_v2(vp + g * 8, R.v[j][0], R.v[j][1]);
-        } else {
+        const uint32_t vb = sb + C::kOffV + j * C::kVTok;
 #pragma unroll
-          for (int w = 0; w < C::VW; ++w) R.v[j][w] = ldg_stream_b32(vp + g * 4 * C::VW + 4 * w);
-        }
-        if (C::VH) R.v[j][C::VW] = ldg_stream_b16(vp + 32 * C::VW + 2 * g);
+        for (int u = 0; u < C::NV; ++u)
+          cp_async<C::UV>(vb + u * 32 * C::UV + lane * C::UV, rv[j] + v_off + u * C::UV);
+        if (C::VH) cp_async<4>(vb + 32 * 4 * C::VW + lane * 4, rv[j] + vh_off);
       }
-      R.kn[0] = ldg_f32(k0 + kn_off);
-      R.kn[1] = ldg_f32(k1 + kn_off);
-      R.vn[0] = ldg_f32(k0 + vn_off);
-      R.vn[1] = ldg_f32(k1 + vn_off);
+      const uint32_t nbase = sb + C::kOffN + lane * 16;
+      cp_async<4>(nbase, rk0 + kn_off);
+      cp_async<4>(nbase + 4, rk1 + kn_off);
+      cp_async<4>(nbase + 8, rk0 + kn_off + vn_delta);
+      cp_async<4>(nbase + 12, rk1 + kn_off + vn_delta);
+      return ok;
+    };
+    // generic addressing only: validity of each of the tile's 16 tokens
+    auto token_okmask = [&](int pos0) -> uint32_t {
+      const int pos = min(max(pos0 + (lane & 15), kv_start), kv_end - 1);
+      const int b = __ldg(bt + pos / a.block_size);
+      const bool ok = b >= 0 && b < a.num_blocks;
+      if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+      return __ballot_sync(0xffffffffu, ok) & 0xFFFFu;
     };
 
-    // ---- stream the segment's tiles ------------------------------------------------------------
-    TileRegs<D> cur, nxt;
-    int tt = t + ts;
-    if (tt < seg_end) load_tile(tt, cur);
-    for (; tt < seg_end; tt += sh.TPC) {
-      const bool has_next = tt + sh.TPC < seg_end;
-      if (has_next) load_tile(tt + sh.TPC, nxt);
-
-      // K side: S^T = K * Qsplit^T
-      float sacc[NB][4];
+    // ---- one 16-token tile from ring stage st: scores, online softmax, PV ------------------------
+    auto compute_tile = [&](int st, int pos0, uint32_t okmask) {
+      const uint32_t sb = ring + st * C::kStageBytes;
+      uint32_t kw0[C::KW], kw1[C::KW];
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb) sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+      for (int u = 0; u < C::NK; ++u) {
+        lds_words<C::UK>(sb + u * 32 * C::UK + lane * C::UK, kw0 + u * (C::UK / 4));
+        lds_words<C::UK>(sb + C::kOffK1 + u * 32 * C::UK + lane * C::UK, kw1 + u * (C::UK / 4));
+      }
+      float nrm[4];  // kn(g), kn(g+8), vn(g), vn(g+8)
+      lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
+
+      float sacc[NB][2][4];  // two independent accumulation chains per n-block
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[nb][0][e] = sacc[nb][1][e] = 0.f;
 #pragma unroll
       for (int w = 0; w < C::KW; ++w) {
-        const uint32_t w0 = cur.k[0][w], w1 = cur.k[1][w];
+        const uint32_t w0 = kw0[w], w1 = kw1[w];
         {
           const uint32_t a0 = lut<0>(w0, lb_k), a2 = lut<1>(w0, lb_k);
           const uint32_t a1 = lut<0>(w1, lb_k), a3 = lut<1>(w1, lb_k);
 #pragma unroll
-          for (int nb = 0; nb < NB; ++nb) mma16816(sacc[nb], a0, a1, a2, a3, qf[nb][2 * w][0], qf[nb][2 * w][1]);
+          for (int nb = 0; nb < NB; ++nb)
+            mma16816(sacc[nb][0], a0, a1, a2, a3, qf[nb][2 * w][0], qf[nb][2 * w][1]);
         }
         {
           const uint32_t a0 = lut<2>(w0, lb_k), a2 = lut<3>(w0, lb_k);
           const uint32_t a1 = lut<2>(w1, lb_k), a3 = lut<3>(w1, lb_k);
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb)
-            mma16816(sacc[nb], a0, a1, a2, a3, qf[nb][2 * w + 1][0], qf[nb][2 * w + 1][1]);
+            mma16816(sacc[nb][1], a0, a1, a2, a3, qf[nb][2 * w + 1][0], qf[nb][2 * w + 1][1]);
         }
       }
 
-      // softmax on (token g, head c) and (token g+8, head c)
-      const int p0 = cur.pos0 + g, p1 = p0 + 8;
-      const bool ok0 = p0 >= kv_start && p0 < kv_end && ((cur.okmask >> g) & 1u);
-      const bool ok1 = p1 >= kv_start && p1 < kv_end && ((cur.okmask >> (g + 8)) & 1u);
-      const float lg0 = ok0 ? fmaxf(log2f(cur.vn[0]), -30.f) : -CUDART_INF_F;
-      const float lg1 = ok1 ? fmaxf(log2f(cur.vn[1]), -30.f) : -CUDART_INF_F;
+      // V words of tokens 2c, 2c+1, 2c+8, 2c+9 (loaded now, consumed after the softmax)
+      uint32_t vw[4][C::VW + C::VH];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t vb = sb + C::kOffV + j * C::kVTok;
+#pragma unroll
+        for (int u = 0; u < C::NV; ++u)
+          lds_words<C::UV>(vb + u * 32 * C::UV + lane * C::UV, vw[j] + u * (C::UV / 4));
+        if (C::VH) {
+          uint32_t x;
+          lds_words<4>(vb + 32 * 4 * C::VW + lane * 4, &x);
+          vw[j][C::VW] = (g & 1) ? (x >> 16) : (x & 0xFFFFu);
+        }
+      }
+
+      // (token g, head c) and (token g+8, head c); a tile strictly inside the row needs no masks
+      float kn0 = nrm[0], kn1 = nrm[1], vn0 = nrm[2], vn1 = nrm[3];
+      float lg0 = fmaxf(lg2_approx(vn0), -30.f), lg1 = fmaxf(lg2_approx(vn1), -30.f);
+      const bool full = pos0 >= kv_start && pos0 + kTileTokens <= kv_end && okmask == 0xFFFFu;
+      bool ok0 = true, ok1 = true;
+      if (!full) {
+        const int p0 = pos0 + g, p1 = p0 + 8;
+        ok0 = p0 >= kv_start && p0 < kv_end && ((okmask >> g) & 1u);
+        ok1 = p1 >= kv_start && p1 < kv_end && ((okmask >> (g + 8)) & 1u);
+        if (!ok0) { vn0 = 0.f; lg0 = -CUDART_INF_F; }
+        if (!ok1) { vn1 = 0.f; lg1 = -CUDART_INF_F; }
+      }
       uint32_t pf[NB][2];
       float alpha[NB];
       bool rescale = false;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
-        const float s0 = ok0 ? (sacc[nb][0] + sacc[nb][1]) * (fscale[nb] * cur.kn[0]) : -CUDART_INF_F;
-        const float s1 = ok1 ? (sacc[nb][2] + sacc[nb][3]) * (fscale[nb] * cur.kn[1]) : -CUDART_INF_F;
+        float s0 = ((sacc[nb][0][0] + sacc[nb][1][0]) + (sacc[nb][0][1] + sacc[nb][1][1])) * (fscale[nb] * kn0);
+        float s1 = ((sacc[nb][0][2] + sacc[nb][1][2]) + (sacc[nb][0][3] + sacc[nb][1][3])) * (fscale[nb] * kn1);
+        if (!full) {
+          s0 = ok0 ? s0 : -CUDART_INF_F;
+          s1 = ok1 ? s1 : -CUDART_INF_F;
+        }
         float mt = fmaxf(s0 + lg0, s1 + lg1);
         mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
         mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
         mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
         const float m_new = fmaxf(m[nb], mt);
         const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
-        alpha[nb] = exp2f(m[nb] - m_use);
+        alpha[nb] = ex2_approx(m[nb] - m_use);
         rescale |= (m_new != m[nb]);
-        const float e0 = exp2f(s0 - m_use), e1 = exp2f(s1 - m_use);
+        const float e0 = ex2_approx(s0 - m_use), e1 = ex2_approx(s1 - m_use);
         l[nb] = l[nb] * alpha[nb] + e0 + e1;
         m[nb] = m_new;
-        const float w0 = ok0 ? e0 * cur.vn[0] : 0.f;
-        const float w1 = ok1 ? e1 * cur.vn[1] : 0.f;
-        pf[nb][0] = movmatrix_trans(split_h2(w0));
-        pf[nb][1] = movmatrix_trans(split_h2(w1));
+        pf[nb][0] = movmatrix_trans(split_h2(e0 * vn0));
+        pf[nb][1] = movmatrix_trans(split_h2(e1 * vn1));
       }
       if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
@@ -387,7 +433,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
       // V side: O^T += V^T * Psplit^T
 #pragma unroll
       for (int w = 0; w < C::VW + C::VH; ++w) {
-        const uint32_t x0 = cur.v[0][w], y0 = cur.v[1][w], x1 = cur.v[2][w], y1 = cur.v[3][w];
+        const uint32_t x0 = vw[0][w], y0 = vw[1][w], x1 = vw[2][w], y1 = vw[3][w];
         const uint32_t ee0 = (x0 & 0xF0F0F0F0u) | ((y0 >> 4) & 0x0F0F0F0Fu);
         const uint32_t oo0 = ((x0 << 4) & 0xF0F0F0F0u) | (y0 & 0x0F0F0F0Fu);
         const uint32_t ee1 = (x1 & 0xF0F0F0F0u) | ((y1 >> 4) & 0x0F0F0F0Fu);
@@ -406,7 +452,39 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
         TQ4_V_STEP(3)
 #undef TQ4_V_STEP
       }
-      if (has_next) cur = nxt;
+    };
+
+    // ---- stream the segment: kStages-deep cp.async ring; block ids are fetched one issue ahead ---
+    {
+      const int step = sh.TPC;
+      const int first = t + ts;
+      const int n_tiles = first < seg_end ? (seg_end - first + step - 1) / step : 0;
+      if (n_tiles > 0) {
+        int blkp[kStages];  // block ids of the first tiles, fetched together
+#pragma unroll
+        for (int s = 0; s < kStages; ++s)
+          blkp[s] = (PAGE16 && s < n_tiles) ? __ldg(bt + page_of(pos0_of(first + s * step))) : 0;
+        uint32_t okbits = 0;  // bit i: page of tile k + i is valid
+#pragma unroll
+        for (int s = 0; s < kStages - 1; ++s) {
+          if (s < n_tiles) okbits |= issue_tile(first + s * step, blkp[s], s) << s;
+          cp_async_commit();
+        }
+        int blk_next = blkp[kStages - 1];
+        for (int k = 0; k < n_tiles; ++k) {
+          const int kn = k + kStages - 1;
+          if (kn < n_tiles)
+            okbits |= issue_tile(first + kn * step, blk_next, kn % kStages) << (kStages - 1);
+          cp_async_commit();
+          if (PAGE16 && kn + 1 < n_tiles) blk_next = __ldg(bt + page_of(pos0_of(first + (kn + 1) * step)));
+          const int pos0 = pos0_of(first + k * step);
+          const uint32_t okmask = PAGE16 ? ((okbits & 1u) ? 0xFFFFu : 0u) : token_okmask(pos0);
+          okbits >>= 1;
+          cp_async_wait<kStages - 1>();
+          compute_tile(k % kStages, pos0, okmask);
+        }
+        cp_async_wait<0>();
+      }
     }
 
     // ---- write this warp's partial for the segment ---------------------------------------------
@@ -430,8 +508,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
 #pragma unroll
         for (int i = 0; i < C::MB; ++i) {
           const int vb = v_byte_of_mblock<D>(g, i);
-          *reinterpret_cast<float2*>(dst + 2 * vb) =
-              make_float2((acc[i][nb][0] + acc[i][nb][1]) * inv_av, (acc[i][nb][2] + acc[i][nb][3]) * inv_av);
+          *reinterpret_cast<float2*>(dst + 2 * vb) = make_float2(
+              (acc[i][nb][0] + acc[i][nb][1]) * inv_av, (acc[i][nb][2] + acc[i][nb][3]) * inv_av);
         }
       }
     }
@@ -446,16 +524,25 @@ __global__ void __launch_bounds__(WARPS * 32, 1) attention_mma_kernel(const Attn
 template <int D, int NB, bool ALIGNED, bool PAGE16>
 int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   constexpr int WARPS = (D * NB <= 128) ? 16 : 8;
+  using C = MmaCfg<D, ALIGNED>;
+  // All opt-in shared memory of the SM (one CTA per SM by design): the 64 KB table sits on a
+  // 64 KB boundary of the shared window and whole rings are packed on both sides of it.
+  static int smem_total = 0;
   auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmemBytes) !=
-        cudaSuccess)
+  if (smem_total == 0) {
+    int dev = 0, optin = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return TQ4_ERR_CUDA;
+    const int want = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
+    if (want < (int)kTableBytes + WARPS * kStages * C::kStageBytes) return TQ4_ERR_UNSUPPORTED;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
       return TQ4_ERR_CUDA;
-    attr_set = true;
+    smem_total = want;
   }
   const int warps = a.sh.HPC * a.sh.TPC;
-  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, kMmaSmemBytes, st>>>(a);
+  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
