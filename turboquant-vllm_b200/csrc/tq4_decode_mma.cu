@@ -22,7 +22,11 @@
 // into a private slot of a per-warp shared-memory ring, kStages tiles ahead (no registers are
 // held by loads in flight, no cross-thread synchronisation is needed), and reads them back
 // with conflict-free 16/8-byte shared loads right before use.
+#include <cuda.h>
 #include <math_constants.h>
+
+#include <cstdlib>
+#include <cstring>
 
 #include "tq4_attention.cuh"
 
@@ -109,6 +113,38 @@ __device__ __forceinline__ void lds_words(uint32_t addr, uint32_t* out) {
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(out[0]) : "r"(addr));
 }
 
+// ---- mbarrier / TMA (bulk tensor copy) primitives; every wait is bounded ---------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Returns false if the phase did not complete within the iteration limit.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < (1 << 18); ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+
 template <int D, bool ALIGNED>
 struct MmaCfg {
   static constexpr int HALF = D / 2;
@@ -131,6 +167,10 @@ struct MmaCfg {
   static constexpr int kOffV = 64 * KBY;
   static constexpr int kOffN = kOffV + 4 * kVTok;
   static constexpr int kStageBytes = kOffN + 32 * 16;
+  // TMA stage: K tile [16 tok][D/2] | V tile [16 tok][D/2] | K-norm tile [16][16 B] | V-norm tile
+  static constexpr int kTmaV = 16 * HALF, kTmaKN = 32 * HALF, kTmaVN = 32 * HALF + 256;
+  static constexpr int kTmaStageBytes = 32 * HALF + 512;
+  static constexpr int kTmaTxBytes = 32 * HALF + 512;
 };
 
 // byte offset (within a head's D/2 V bytes) of this thread's m-block i
@@ -140,21 +180,25 @@ __device__ __forceinline__ int v_byte_of_mblock(int g, int i) {
   return i < 4 * VW ? g * 4 * VW + i : 32 * VW + 2 * g + (i - 4 * VW);
 }
 
-template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS>
+template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS, bool TMA>
 __global__ void __launch_bounds__(WARPS * 32, 1)
-attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
+attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
+                     const __grid_constant__ CUtensorMap tm_data,
+                     const __grid_constant__ CUtensorMap tm_norm) {
   using C = MmaCfg<D, ALIGNED>;
+  constexpr int kStage = TMA ? C::kTmaStageBytes : C::kStageBytes;
   const AttnShape& sh = a.sh;
   const AttnPlan& p = a.plan;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ float s_cent[2][TQ4_MAX_CENTROIDS];
+  __shared__ __align__(8) uint64_t s_bar[WARPS][kStages];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
 
   // ---- shared memory map: [rings A][64 KB table on a 64 KB boundary][rings B] ------------------
   const uint32_t base = smem_u32(smem_raw);
   const uint32_t tab = (base + (kTableBytes - 1)) & ~(kTableBytes - 1);
-  constexpr uint32_t kRing = kStages * C::kStageBytes;
+  constexpr uint32_t kRing = kStages * kStage;
   const uint32_t n_a = (tab - base) / kRing;
   const uint32_t end = base + smem_total;
   const uint32_t ring =
@@ -178,8 +222,17 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
       t[i] = pack_h2(s_cent[w][byte >> 4], s_cent[w][byte & 15]);
     }
   }
+  if (TMA && lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&s_bar[warp][s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   __syncthreads();
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
+  const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
+  uint32_t gk = 0;      // tiles this warp has pushed through the ring (stage = gk % kStages)
+  bool dead = false;    // a bounded wait gave up: stop issuing work, fall through to the end
 
   const int cta = blockIdx.x % sh.ctas, slice = blockIdx.x / sh.ctas;
   const int vh = slice * sh.HPC + warp % sh.HPC, ts = warp / sh.HPC;
@@ -278,12 +331,27 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
       return a.cache + (int64_t)(ok ? blk : 0) * a.cache_block_stride +
              (int64_t)(pc % a.block_size) * a.cache_token_stride;
     };
-    // ---- issue the cp.async copies of one tile into ring stage st; returns 1 if its page is valid
+    // ---- issue the copies of one tile into ring stage st; returns 1 if its page is valid --------
     auto issue_tile = [&](int tt, int blk, int st) -> uint32_t {
       const int pos0 = pos0_of(tt);
-      const uint32_t sb = ring + st * C::kStageBytes;
-      const uint8_t *rk0, *rk1, *rv[4];
+      const uint32_t sb = ring + st * kStage;
       uint32_t ok = 1;
+      if (TMA) {
+        // four box copies by one lane: K rows, V rows, K-norm and V-norm columns of the 16 tokens
+        ok = blk >= 0 && blk < a.num_blocks;
+        if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+        if (lane == 0) {
+          const int inpage = bs_shift >= 0 ? (pos0 & (a.block_size - 1)) : (pos0 % a.block_size);
+          const uint32_t bar = bar0 + st * 8;
+          mbar_expect_tx(bar, C::kTmaTxBytes);
+          tma_load_3d(sb, &tm_data, lay.k_idx + kvh * C::HALF, inpage, blk, bar);
+          tma_load_3d(sb + C::kTmaV, &tm_data, lay.v_idx + kvh * C::HALF, inpage, blk, bar);
+          tma_load_3d(sb + C::kTmaKN, &tm_norm, lay.k_norm + (kvh >> 2) * 16, inpage, blk, bar);
+          tma_load_3d(sb + C::kTmaVN, &tm_norm, lay.v_norm + (kvh >> 2) * 16, inpage, blk, bar);
+        }
+        return ok;
+      }
+      const uint8_t *rk0, *rk1, *rv[4];
       if (PAGE16) {
         ok = blk >= 0 && blk < a.num_blocks;
         if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
@@ -335,15 +403,29 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
 
     // ---- one 16-token tile from ring stage st: scores, online softmax, PV ------------------------
     auto compute_tile = [&](int st, int pos0, uint32_t okmask) {
-      const uint32_t sb = ring + st * C::kStageBytes;
+      const uint32_t sb = ring + st * kStage;
       uint32_t kw0[C::KW], kw1[C::KW];
-#pragma unroll
-      for (int u = 0; u < C::NK; ++u) {
-        lds_words<C::UK>(sb + u * 32 * C::UK + lane * C::UK, kw0 + u * (C::UK / 4));
-        lds_words<C::UK>(sb + C::kOffK1 + u * 32 * C::UK + lane * C::UK, kw1 + u * (C::UK / 4));
-      }
       float nrm[4];  // kn(g), kn(g+8), vn(g), vn(g+8)
-      lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
+      if (TMA) {
+        const uint32_t ka = sb + g * C::HALF + c * C::KBY;
+#pragma unroll
+        for (int u = 0; u < C::NK; ++u) {
+          lds_words<C::UK>(ka + u * C::UK, kw0 + u * (C::UK / 4));
+          lds_words<C::UK>(ka + 8 * C::HALF + u * C::UK, kw1 + u * (C::UK / 4));
+        }
+        const uint32_t na = sb + C::kTmaKN + g * 16 + (kvh & 3) * 4;
+        lds_words<4>(na, reinterpret_cast<uint32_t*>(nrm));
+        lds_words<4>(na + 128, reinterpret_cast<uint32_t*>(nrm + 1));
+        lds_words<4>(na + 256, reinterpret_cast<uint32_t*>(nrm + 2));
+        lds_words<4>(na + 384, reinterpret_cast<uint32_t*>(nrm + 3));
+      } else {
+#pragma unroll
+        for (int u = 0; u < C::NK; ++u) {
+          lds_words<C::UK>(sb + u * 32 * C::UK + lane * C::UK, kw0 + u * (C::UK / 4));
+          lds_words<C::UK>(sb + C::kOffK1 + u * 32 * C::UK + lane * C::UK, kw1 + u * (C::UK / 4));
+        }
+        lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
+      }
 
       float sacc[NB][2][4];  // two independent accumulation chains per n-block
 #pragma unroll
@@ -373,14 +455,21 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
       uint32_t vw[4][C::VW + C::VH];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint32_t vb = sb + C::kOffV + j * C::kVTok;
+        if (TMA) {
+          const int tok = 2 * c + (j & 1) + 8 * (j >> 1);
+          const uint32_t va = sb + C::kTmaV + tok * C::HALF + g * C::VBY;
 #pragma unroll
-        for (int u = 0; u < C::NV; ++u)
-          lds_words<C::UV>(vb + u * 32 * C::UV + lane * C::UV, vw[j] + u * (C::UV / 4));
-        if (C::VH) {
-          uint32_t x;
-          lds_words<4>(vb + 32 * 4 * C::VW + lane * 4, &x);
-          vw[j][C::VW] = (g & 1) ? (x >> 16) : (x & 0xFFFFu);
+          for (int u = 0; u < C::NV; ++u) lds_words<C::UV>(va + u * C::UV, vw[j] + u * (C::UV / 4));
+        } else {
+          const uint32_t vb = sb + C::kOffV + j * C::kVTok;
+#pragma unroll
+          for (int u = 0; u < C::NV; ++u)
+            lds_words<C::UV>(vb + u * 32 * C::UV + lane * C::UV, vw[j] + u * (C::UV / 4));
+          if (C::VH) {
+            uint32_t x;
+            lds_words<4>(vb + 32 * 4 * C::VW + lane * 4, &x);
+            vw[j][C::VW] = (g & 1) ? (x >> 16) : (x & 0xFFFFu);
+          }
         }
       }
 
@@ -396,9 +485,12 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
         if (!ok0) { vn0 = 0.f; lg0 = -CUDART_INF_F; }
         if (!ok1) { vn1 = 0.f; lg1 = -CUDART_INF_F; }
       }
+      // Online softmax with a lazily updated reference: the running reference m only moves when
+      // the tile maximum exceeds it by more than 2^8, so accumulators are rescaled a handful of
+      // times per row; probabilities stay below 2^8 (exact in the fp16 hi/lo split).
       uint32_t pf[NB][2];
       float alpha[NB];
-      bool rescale = false;
+      bool bump = false;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         float s0 = ((sacc[nb][0][0] + sacc[nb][1][0]) + (sacc[nb][0][1] + sacc[nb][1][1])) * (fscale[nb] * kn0);
@@ -411,23 +503,27 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
         mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
         mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
         mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
-        const float m_new = fmaxf(m[nb], mt);
+        const bool up = mt > m[nb] + 8.f;  // also true for the first finite maximum (m = -inf)
+        const float m_new = up ? mt : m[nb];
         const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
-        alpha[nb] = ex2_approx(m[nb] - m_use);
-        rescale |= (m_new != m[nb]);
-        const float e0 = ex2_approx(s0 - m_use), e1 = ex2_approx(s1 - m_use);
-        l[nb] = l[nb] * alpha[nb] + e0 + e1;
+        alpha[nb] = up ? ex2_approx(m[nb] - m_use) : 1.f;
+        bump |= up;
         m[nb] = m_new;
+        const float e0 = ex2_approx(s0 - m_use), e1 = ex2_approx(s1 - m_use);
+        l[nb] = fmaf(l[nb], alpha[nb], e0 + e1);
         pf[nb][0] = movmatrix_trans(split_h2(e0 * vn0));
         pf[nb][1] = movmatrix_trans(split_h2(e1 * vn1));
       }
-      if (__any_sync(0xffffffffu, rescale)) {
+      if (__any_sync(0xffffffffu, bump)) {
+        asm volatile("" ::: "memory");  // keep this rare path a real branch
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
+        for (int nb = 0; nb < NB; ++nb) {
+          // alpha == 1 where the reference did not move
 #pragma unroll
           for (int i = 0; i < C::MB; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][nb][e] *= alpha[nb];
+        }
       }
 
       // V side: O^T += V^T * Psplit^T
@@ -454,11 +550,11 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
       }
     };
 
-    // ---- stream the segment: kStages-deep cp.async ring; block ids are fetched one issue ahead ---
+    // ---- stream the segment through the kStages-deep ring; block ids are fetched one issue ahead --
     {
       const int step = sh.TPC;
       const int first = t + ts;
-      const int n_tiles = first < seg_end ? (seg_end - first + step - 1) / step : 0;
+      const int n_tiles = (first < seg_end && !dead) ? (seg_end - first + step - 1) / step : 0;
       if (n_tiles > 0) {
         int blkp[kStages];  // block ids of the first tiles, fetched together
 #pragma unroll
@@ -467,23 +563,34 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
         uint32_t okbits = 0;  // bit i: page of tile k + i is valid
 #pragma unroll
         for (int s = 0; s < kStages - 1; ++s) {
-          if (s < n_tiles) okbits |= issue_tile(first + s * step, blkp[s], s) << s;
-          cp_async_commit();
+          if (s < n_tiles) okbits |= issue_tile(first + s * step, blkp[s], (gk + s) % kStages) << s;
+          if (!TMA) cp_async_commit();
         }
         int blk_next = blkp[kStages - 1];
         for (int k = 0; k < n_tiles; ++k) {
           const int kn = k + kStages - 1;
+          if (TMA) __syncwarp();  // every lane has finished reading the stage about to be refilled
           if (kn < n_tiles)
-            okbits |= issue_tile(first + kn * step, blk_next, kn % kStages) << (kStages - 1);
-          cp_async_commit();
+            okbits |= issue_tile(first + kn * step, blk_next, (gk + kn) % kStages) << (kStages - 1);
+          if (!TMA) cp_async_commit();
           if (PAGE16 && kn + 1 < n_tiles) blk_next = __ldg(bt + page_of(pos0_of(first + (kn + 1) * step)));
           const int pos0 = pos0_of(first + k * step);
           const uint32_t okmask = PAGE16 ? ((okbits & 1u) ? 0xFFFFu : 0u) : token_okmask(pos0);
           okbits >>= 1;
-          cp_async_wait<kStages - 1>();
-          compute_tile(k % kStages, pos0, okmask);
+          const uint32_t use = gk + k;
+          if (TMA) {
+            if (!mbar_wait_bounded(bar0 + (use % kStages) * 8, (use / kStages) & 1u)) {
+              if (lane == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
+              dead = true;
+              break;
+            }
+          } else {
+            cp_async_wait<kStages - 1>();
+          }
+          compute_tile(use % kStages, pos0, okmask);
         }
-        cp_async_wait<0>();
+        if (!TMA) cp_async_wait<0>();
+        gk += n_tiles;
       }
     }
 
@@ -501,8 +608,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
       if (hh < gcount) {
         const int64_t hidx = pidx * sh.Hq + qh0 + hh;
         if (g == 0) {
-          p.part_m[hidx] = m[nb];
-          p.part_l[hidx] = ls;
+          p.part_m[hidx] = dead ? -CUDART_INF_F : m[nb];
+          p.part_l[hidx] = dead ? 0.f : ls;
         }
         float* dst = p.part_o + hidx * D;
 #pragma unroll
@@ -521,14 +628,46 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total) {
   }
 }
 
-template <int D, int NB, bool ALIGNED, bool PAGE16>
+// ---- TMA tensor maps over the paged cache: dims (row bytes, tokens in a block, blocks) -----------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+bool make_cache_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)a.cache_token_stride, (cuuint64_t)a.block_size,
+                              (cuuint64_t)a.num_blocks};
+  const cuuint64_t strides[2] = {(cuuint64_t)a.cache_token_stride, (cuuint64_t)a.cache_block_stride};
+  const cuuint32_t box[3] = {box_bytes, (cuuint32_t)kTileTokens, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(a.cache), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D, int NB, bool ALIGNED, bool PAGE16, bool TMA>
 int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   constexpr int WARPS = (D * NB <= 128) ? 16 : 8;
   using C = MmaCfg<D, ALIGNED>;
   // All opt-in shared memory of the SM (one CTA per SM by design): the 64 KB table sits on a
   // 64 KB boundary of the shared window and whole rings are packed on both sides of it.
   static int smem_total = 0;
-  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS>;
+  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA>;
   if (smem_total == 0) {
     int dev = 0, optin = 0;
     cudaGetDevice(&dev);
@@ -536,13 +675,18 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return TQ4_ERR_CUDA;
     const int want = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
-    if (want < (int)kTableBytes + WARPS * kStages * C::kStageBytes) return TQ4_ERR_UNSUPPORTED;
+    const int stage = TMA ? C::kTmaStageBytes : C::kStageBytes;
+    if (want < (int)kTableBytes + WARPS * kStages * stage) return TQ4_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
       return TQ4_ERR_CUDA;
     smem_total = want;
   }
+  CUtensorMap tm_data, tm_norm;
+  memset(&tm_data, 0, sizeof(tm_data));
+  memset(&tm_norm, 0, sizeof(tm_norm));
+  if (TMA && (!make_cache_map(&tm_data, a, D / 2) || !make_cache_map(&tm_norm, a, 16))) return TQ4_ERR_CUDA;
   const int warps = a.sh.HPC * a.sh.TPC;
-  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total);
+  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total, tm_data, tm_norm);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
@@ -555,14 +699,25 @@ bool cache_aligned(const AttnShape& sh, const uint8_t* cache, int64_t bs, int64_
          (sh.D / 2) % valign == 0 && sh.D != 96;
 }
 
+// TMA boxes start on 16-byte boundaries of the token row: every region offset of every head must
+// be a multiple of 16 (true whenever the number of KV heads is a multiple of 4).
+bool cache_tma_ok(const AttnArgs& a) {
+  const RowLayout lay = row_layout(a.sh.Hkv, a.sh.D);
+  return cache_aligned(a.sh, a.cache, a.cache_block_stride, a.cache_token_stride) &&
+         a.block_size % kTileTokens == 0 && a.block_size <= 256 && lay.k_norm % 16 == 0 &&
+         lay.v_idx % 16 == 0 && lay.v_norm % 16 == 0 && (a.sh.D / 2) % 16 == 0 && a.sh.Hkv % 4 == 0 &&
+         a.num_blocks < (1ll << 31) && getenv("TQ4_NO_TMA") == nullptr && encode_tiled_fn() != nullptr;
+}
+
 template <int D, int NB>
 int launch_mma_dn(const AttnArgs& a, cudaStream_t st) {
   const bool aligned = cache_aligned(a.sh, a.cache, a.cache_block_stride, a.cache_token_stride);
   const bool page16 = a.block_size % kTileTokens == 0;
-  if (aligned && page16) return launch_mma_t<D, NB, true, true>(a, st);
-  if (aligned) return launch_mma_t<D, NB, true, false>(a, st);
-  if (page16) return launch_mma_t<D, NB, false, true>(a, st);
-  return launch_mma_t<D, NB, false, false>(a, st);
+  if (D != 96 && cache_tma_ok(a)) return launch_mma_t<D, NB, true, true, (D != 96)>(a, st);
+  if (aligned && page16) return launch_mma_t<D, NB, true, true, false>(a, st);
+  if (aligned) return launch_mma_t<D, NB, true, false, false>(a, st);
+  if (page16) return launch_mma_t<D, NB, false, true, false>(a, st);
+  return launch_mma_t<D, NB, false, false, false>(a, st);
 }
 
 template <int D>
