@@ -9,9 +9,6 @@ namespace tq4 {
 // ======================================================================================
 // 1. Prologue: q_rot = q * Pi^T for every (row, head), and (last block) the tile plan.
 // ======================================================================================
-template <int D>
-__host__ __device__ constexpr int qrot_vecs() { return D <= 128 ? 16 : 8; }  // (row, head) vectors per block
-
 __device__ void build_plan(const AttnArgs& a) {
   // One block.  Per row: visible key range, tiles; then two exclusive scans.
   const AttnShape& sh = a.sh;
@@ -112,48 +109,104 @@ __device__ void build_plan(const AttnArgs& a) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(D) qrot_plan_kernel(const AttnArgs a) {
-  if (blockIdx.x == gridDim.x - 1) {  // the planning block (blockDim.x == D threads)
+struct QrotCfg {
+  static constexpr int DC = D < 128 ? D : 128;          // columns of Pi staged per pass
+  static constexpr int G = 256 / D >= 1 ? 256 / D : 1;  // thread groups (one output column each)
+  static constexpr int VPG = 16;                        // vectors per group
+  static constexpr int VB = G * VPG;                    // (row, head) vectors per block
+  static constexpr int THREADS = G * D;
+  static constexpr size_t smem_bytes = ((size_t)D * (DC + 1) + (size_t)D * VB) * sizeof(float);
+};
+
+// q_rot[v][j] = sum_d q[v][d] * Pi[j][d].  Pi is staged once per block, transposed into a padded
+// shared array so that thread j walks its own row without bank conflicts; the block's vectors sit
+// in shared memory as [d][v] (swizzled) so that one 16-byte broadcast load feeds four FMAs.
+template <int D>
+__global__ void __launch_bounds__(QrotCfg<D>::THREADS) qrot_plan_kernel(const AttnArgs a) {
+  using Q = QrotCfg<D>;
+  if (blockIdx.x == gridDim.x - 1) {  // the planning block
     build_plan(a);
     return;
   }
-  constexpr int kQrotVecs = qrot_vecs<D>();
-  __shared__ float s_pi[D][33];
-  __shared__ float s_q[kQrotVecs][D];
+  constexpr int DC = Q::DC, VB = Q::VB, VPG = Q::VPG, PITCH = DC + 1;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_pi = reinterpret_cast<float*>(smem_raw);  // [D][DC + 1]
+  float* s_q = s_pi + D * PITCH;                     // [D][VB], v swizzled by d
   const AttnShape& sh = a.sh;
   const int64_t n_vec = (int64_t)sh.rows * sh.Hq;
-  const int64_t v0 = (int64_t)blockIdx.x * kQrotVecs;
-  const int j = threadIdx.x;
-#pragma unroll 1
-  for (int v = 0; v < kQrotVecs; ++v) {
-    const int64_t vec = v0 + v;
-    float x = 0.f;
-    if (vec < n_vec) {
-      const int64_t row = vec / sh.Hq + sh.row_offset;
-      const int h = (int)(vec % sh.Hq);
-      x = load_as_float(a.q, a.q_dtype, row * a.q_token_stride + h * a.q_head_stride + j);
+  const int64_t v0 = (int64_t)blockIdx.x * VB;
+  const int tid = threadIdx.x, grp = tid / D, j = tid - grp * D;
+  auto swz = [](int d) { return ((d & 7) << 2) & (VB - 1); };
+
+  // the block's vectors (coalesced over d), converted to fp32
+  for (int i0 = 0; i0 < VB * D; i0 += Q::THREADS * 8) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * Q::THREADS + tid;
+      const int v = i / D, d = i - v * D;
+      const int64_t vec = v0 + v;
+      x[u] = 0.f;
+      if (i < VB * D && vec < n_vec) {
+        const int64_t row = vec / sh.Hq + sh.row_offset;
+        const int h = (int)(vec % sh.Hq);
+        x[u] = load_as_float(a.q, a.q_dtype, row * a.q_token_stride + h * a.q_head_stride + d);
+      }
     }
-    s_q[v][j] = x;
-  }
-  float acc[kQrotVecs];
 #pragma unroll
-  for (int v = 0; v < kQrotVecs; ++v) acc[v] = 0.f;
-  const int warp = j >> 5, lane = j & 31;
-  for (int d0 = 0; d0 < D; d0 += 32) {
-    __syncthreads();
-    // stage Pi[:, d0:d0+32] (row jj, 32 consecutive floats per warp-load)
-    for (int jj = warp; jj < D; jj += D / 32) s_pi[jj][lane] = a.rotation[(size_t)jj * D + d0 + lane];
-    __syncthreads();
-#pragma unroll 8
-    for (int dd = 0; dd < 32; ++dd) {
-      const float pv = s_pi[j][dd];
-#pragma unroll
-      for (int v = 0; v < kQrotVecs; ++v) acc[v] = fmaf(s_q[v][d0 + dd], pv, acc[v]);
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * Q::THREADS + tid;
+      const int v = i / D, d = i - v * D;
+      if (i < VB * D) s_q[d * VB + (v ^ swz(d))] = x[u];
     }
   }
+
+  float acc[VPG];
 #pragma unroll
-  for (int v = 0; v < kQrotVecs; ++v) {
-    const int64_t vec = v0 + v;
+  for (int v = 0; v < VPG; ++v) acc[v] = 0.f;
+  for (int d0 = 0; d0 < D; d0 += DC) {
+    __syncthreads();
+    // stage Pi[:, d0 : d0 + DC] with 16-byte loads, eight in flight per thread
+    constexpr int N4 = D * DC / 4;
+    for (int i0 = 0; i0 < N4; i0 += Q::THREADS * 8) {
+      float4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * Q::THREADS + tid;
+        if (i < N4) {
+          const int jj = i / (DC / 4), c4 = i - jj * (DC / 4);
+          x[u] = __ldg(reinterpret_cast<const float4*>(a.rotation + (size_t)jj * D + d0) + c4);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * Q::THREADS + tid;
+        if (i < N4) {
+          const int jj = i / (DC / 4), c4 = i - jj * (DC / 4);
+          float* dst = s_pi + jj * PITCH + 4 * c4;
+          dst[0] = x[u].x; dst[1] = x[u].y; dst[2] = x[u].z; dst[3] = x[u].w;
+        }
+      }
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int dd = 0; dd < DC; ++dd) {
+      const float pv = s_pi[j * PITCH + dd];
+      const int d = d0 + dd;
+      const float* qrow = s_q + d * VB;
+#pragma unroll
+      for (int v4 = 0; v4 < VPG / 4; ++v4) {
+        const float4 qv = *reinterpret_cast<const float4*>(qrow + ((grp * VPG + 4 * v4) ^ swz(d)));
+        acc[4 * v4] = fmaf(qv.x, pv, acc[4 * v4]);
+        acc[4 * v4 + 1] = fmaf(qv.y, pv, acc[4 * v4 + 1]);
+        acc[4 * v4 + 2] = fmaf(qv.z, pv, acc[4 * v4 + 2]);
+        acc[4 * v4 + 3] = fmaf(qv.w, pv, acc[4 * v4 + 3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VPG; ++v) {
+    const int64_t vec = v0 + grp * VPG + v;
     if (vec < n_vec) a.plan.q_rot[vec * D + j] = acc[v];
   }
 }
@@ -428,52 +481,71 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
   const int r = blockIdx.x, h0 = blockIdx.y * kCombHeads, d = threadIdx.x;
   const int nh = min(kCombHeads, a.Hq - h0);
   constexpr float kLn2 = 0.6931471805599453f, kLog2e = 1.4426950408889634f;
-  for (int hh = 0; hh < nh; ++hh) {
-    const int h = h0 + hh;
-    float M = -CUDART_INF_F, L = 0.f, o = 0.f;
-    if (a.slot_base != nullptr) {
-      const int64_t p0 = (int64_t)a.slot_base[r] * a.TPC, p1 = (int64_t)a.slot_base[r + 1] * a.TPC;
-      for (int64_t pi = p0; pi < p1; ++pi) M = fmaxf(M, a.part_m[pi * a.Hq + h]);
-      const float m_use = M == -CUDART_INF_F ? 0.f : M;
-      for (int64_t pi = p0; pi < p1; ++pi) {
-        const float w = exp2f(a.part_m[pi * a.Hq + h] - m_use);
-        if (w > 0.f) {
-          L = fmaf(a.part_l[pi * a.Hq + h], w, L);
-          o = fmaf(a.part_o[(pi * a.Hq + h) * D + d], w, o);
+  const bool sparse = a.slot_base != nullptr;
+  // partial p of this row: sparse = slot-major list, dense = one per shard
+  const int64_t p0 = sparse ? (int64_t)a.slot_base[r] * a.TPC : 0;
+  const int np = sparse ? (int)((int64_t)a.slot_base[r + 1] * a.TPC - p0) : a.world;
+  auto pidx = [&](int i) -> int64_t { return sparse ? p0 + i : (int64_t)i * a.rows + r; };
+  const float mscale = sparse ? 1.f : kLog2e;  // dense partials carry natural-log LSE
+
+  // all heads of the block advance together so their loads overlap
+  float M[kCombHeads], L[kCombHeads], o[kCombHeads];
+#pragma unroll
+  for (int hh = 0; hh < kCombHeads; ++hh) { M[hh] = -CUDART_INF_F; L[hh] = 0.f; o[hh] = 0.f; }
+#pragma unroll 2
+  for (int i = 0; i < np; ++i) {
+    const int64_t pi = pidx(i);
+#pragma unroll
+    for (int hh = 0; hh < kCombHeads; ++hh)
+      if (hh < nh) M[hh] = fmaxf(M[hh], __ldg(a.part_m + pi * a.Hq + h0 + hh) * mscale);
+  }
+#pragma unroll
+  for (int hh = 0; hh < kCombHeads; ++hh) M[hh] = M[hh] == -CUDART_INF_F ? 0.f : M[hh];
+#pragma unroll 2
+  for (int i = 0; i < np; ++i) {
+    const int64_t pi = pidx(i);
+#pragma unroll
+    for (int hh = 0; hh < kCombHeads; ++hh) {
+      if (hh < nh) {
+        const int64_t hi = pi * a.Hq + h0 + hh;
+        const float w = exp2f(__ldg(a.part_m + hi) * mscale - M[hh]);
+        const float lv = sparse ? __ldg(a.part_l + hi) : 1.f;
+        const float ov = __ldg(a.part_o + hi * D + d);
+        if (w > 0.f) {  // skips empty partials (m = -inf), whose o / l may be uninitialised
+          L[hh] = fmaf(lv, w, L[hh]);
+          o[hh] = fmaf(ov, w, o[hh]);
         }
       }
-      M = m_use;
-    } else {
-      for (int w = 0; w < a.world; ++w)
-        M = fmaxf(M, a.part_m[((int64_t)w * a.rows + r) * a.Hq + h] * kLog2e);
-      const float m_use = M == -CUDART_INF_F ? 0.f : M;
-      for (int w = 0; w < a.world; ++w) {
-        const int64_t pi = (int64_t)w * a.rows + r;
-        const float wt = exp2f(a.part_m[pi * a.Hq + h] * kLog2e - m_use);
-        if (wt > 0.f) {
-          L += wt;
-          o = fmaf(a.part_o[(pi * a.Hq + h) * D + d], wt, o);
-        }
-      }
-      M = m_use;
     }
-    s_o[hh][d] = L > 0.f ? o / L : 0.f;
-    if (d == 0 && a.lse_out)
-      a.lse_out[(int64_t)(r + a.row_offset) * a.Hq + h] = L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
+  }
+#pragma unroll
+  for (int hh = 0; hh < kCombHeads; ++hh) {
+    if (hh < nh) {
+      s_o[hh][d] = L[hh] > 0.f ? o[hh] / L[hh] : 0.f;
+      if (d == 0 && a.lse_out)
+        a.lse_out[(int64_t)(r + a.row_offset) * a.Hq + h0 + hh] =
+            L[hh] > 0.f ? (M[hh] + log2f(L[hh])) * kLn2 : -CUDART_INF_F;
+    } else {
+      s_o[hh][d] = 0.f;
+    }
   }
   __syncthreads();
   float acc[kCombHeads];
   if (a.out_rotated) {
 #pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = hh < nh ? s_o[hh][d] : 0.f;
+    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = s_o[hh][d];
   } else {
 #pragma unroll
     for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = 0.f;
-#pragma unroll 4
-    for (int j = 0; j < D; ++j) {
-      const float pv = __ldg(a.rotation + (size_t)j * D + d);
+    // column d of Pi: 16 independent loads in flight per batch
+    for (int j0 = 0; j0 < D; j0 += 16) {
+      float pv[16];
 #pragma unroll
-      for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh][j], pv, acc[hh]);
+      for (int u = 0; u < 16; ++u) pv[u] = __ldg(a.rotation + (size_t)(j0 + u) * D + d);
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+#pragma unroll
+        for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh][j0 + u], pv[u], acc[hh]);
     }
   }
 #pragma unroll
@@ -499,19 +571,31 @@ int launch_combine(const CombineArgs& c, int D, cudaStream_t st) {
   return TQ4_OK;
 }
 
-int launch_qrot_plan(const AttnArgs& a, cudaStream_t st) {
-  const int64_t n_vec = (int64_t)a.sh.rows * a.sh.Hq;
-  const int vecs = a.sh.D <= 128 ? 16 : 8;
-  const unsigned grid = (unsigned)((n_vec + vecs - 1) / vecs) + 1;
-  switch (a.sh.D) {
-    case 64: qrot_plan_kernel<64><<<grid, 64, 0, st>>>(a); break;
-    case 96: qrot_plan_kernel<96><<<grid, 96, 0, st>>>(a); break;
-    case 128: qrot_plan_kernel<128><<<grid, 128, 0, st>>>(a); break;
-    case 256: qrot_plan_kernel<256><<<grid, 256, 0, st>>>(a); break;
-    default: return TQ4_ERR_UNSUPPORTED;
+template <int D>
+int launch_qrot_plan_t(const AttnArgs& a, cudaStream_t st) {
+  using Q = QrotCfg<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(qrot_plan_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)Q::smem_bytes) != cudaSuccess)
+      return TQ4_ERR_CUDA;
+    attr_set = true;
   }
+  const int64_t n_vec = (int64_t)a.sh.rows * a.sh.Hq;
+  const unsigned grid = (unsigned)((n_vec + Q::VB - 1) / Q::VB) + 1;
+  qrot_plan_kernel<D><<<grid, Q::THREADS, Q::smem_bytes, st>>>(a);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
+}
+
+int launch_qrot_plan(const AttnArgs& a, cudaStream_t st) {
+  switch (a.sh.D) {
+    case 64: return launch_qrot_plan_t<64>(a, st);
+    case 96: return launch_qrot_plan_t<96>(a, st);
+    case 128: return launch_qrot_plan_t<128>(a, st);
+    case 256: return launch_qrot_plan_t<256>(a, st);
+  }
+  return TQ4_ERR_UNSUPPORTED;
 }
 
 }  // namespace tq4

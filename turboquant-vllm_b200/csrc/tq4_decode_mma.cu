@@ -522,7 +522,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
 #pragma unroll
           for (int i = 0; i < C::MB; ++i)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[i][nb][e] *= alpha[nb];
+            for (int e = 0; e < 4; ++e)  // volatile asm: must not be hoisted out of the branch
+              asm volatile("mul.f32 %0, %0, %1;" : "+f"(acc[i][nb][e]) : "f"(alpha[nb]));
         }
       }
 
