@@ -112,7 +112,7 @@ template <int D>
 struct QrotCfg {
   static constexpr int DC = D < 128 ? D : 128;          // columns of Pi staged per pass
   static constexpr int G = 256 / D >= 1 ? 256 / D : 1;  // thread groups (one output column each)
-  static constexpr int VPG = 16;                        // vectors per group
+  static constexpr int VPG = 4;                         // vectors per group (small: many blocks)
   static constexpr int VB = G * VPG;                    // (row, head) vectors per block
   static constexpr int THREADS = G * D;
   static constexpr size_t smem_bytes = ((size_t)D * (DC + 1) + (size_t)D * VB) * sizeof(float);
@@ -475,77 +475,125 @@ struct CombineArgs {
   int out_rotated;
 };
 
+constexpr int kCombMaxParts = 64;  // partials of one row merged per pass
+
+// One block per (row, 8 heads), D threads.  Pi is copied to shared memory asynchronously at
+// kernel entry and overlaps the merge of the row's partials; the merge weights of all
+// (partial, head) pairs are computed once into shared memory so that the accumulation loop
+// issues nothing but independent loads.
 template <int D>
 __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
-  __shared__ float s_o[kCombHeads][D];
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* s_pi = reinterpret_cast<float*>(smem_raw);            // [D][D] (D <= 128 only)
+  float* s_o = s_pi + (D <= 128 ? D * D : 0);                   // [kCombHeads][D]
+  float* s_w = s_o + kCombHeads * D;                            // [kCombMaxParts][kCombHeads]
+  float* s_m = s_w + kCombMaxParts * kCombHeads;                // [kCombHeads] running max
+  float* s_l = s_m + kCombHeads;                                // [kCombHeads] running sum
   const int r = blockIdx.x, h0 = blockIdx.y * kCombHeads, d = threadIdx.x;
   const int nh = min(kCombHeads, a.Hq - h0);
   constexpr float kLn2 = 0.6931471805599453f, kLog2e = 1.4426950408889634f;
+  constexpr bool kStagePi = D <= 128;  // a 256 x 256 fp32 Pi does not fit in shared memory
+  if (kStagePi && !a.out_rotated) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(s_pi);
+    for (int i = d; i < D * D / 4; i += D)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16),
+                   "l"(a.rotation + (size_t)i * 4) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   const bool sparse = a.slot_base != nullptr;
-  // partial p of this row: sparse = slot-major list, dense = one per shard
   const int64_t p0 = sparse ? (int64_t)a.slot_base[r] * a.TPC : 0;
   const int np = sparse ? (int)((int64_t)a.slot_base[r + 1] * a.TPC - p0) : a.world;
   auto pidx = [&](int i) -> int64_t { return sparse ? p0 + i : (int64_t)i * a.rows + r; };
-  const float mscale = sparse ? 1.f : kLog2e;  // dense partials carry natural-log LSE
+  const float mscale = sparse ? 1.f : kLog2e;  // dense partials carry a natural-log LSE
 
-  // all heads of the block advance together so their loads overlap
-  float M[kCombHeads], L[kCombHeads], o[kCombHeads];
+  if (d < kCombHeads) { s_m[d] = -CUDART_INF_F; s_l[d] = 0.f; }
+  float o[kCombHeads];
 #pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh) { M[hh] = -CUDART_INF_F; L[hh] = 0.f; o[hh] = 0.f; }
-#pragma unroll 2
-  for (int i = 0; i < np; ++i) {
-    const int64_t pi = pidx(i);
+  for (int hh = 0; hh < kCombHeads; ++hh) o[hh] = 0.f;
+  for (int c0 = 0; c0 < np; c0 += kCombMaxParts) {
+    const int nc = min(kCombMaxParts, np - c0);
+    __syncthreads();
+    // (partial, head) pairs -> log2-domain maxima
+    for (int t = d; t < nc * kCombHeads; t += D) {
+      const int i = t / kCombHeads, hh = t - i * kCombHeads;
+      s_w[t] = hh < nh ? __ldg(a.part_m + pidx(c0 + i) * a.Hq + h0 + hh) * mscale : -CUDART_INF_F;
+    }
+    __syncthreads();
+    if (d < kCombHeads) {  // new running max of head d; rescale what was accumulated so far
+      float M = s_m[d];
+      for (int i = 0; i < nc; ++i) M = fmaxf(M, s_w[i * kCombHeads + d]);
+      const float m_use = M == -CUDART_INF_F ? 0.f : M;
+      const float resc = s_m[d] == -CUDART_INF_F ? 0.f : exp2f(s_m[d] - m_use);
+      s_l[d] *= resc;
+      s_o[d] = resc;       // reuse s_o[0..7] to publish the rescale factor
+      s_m[d] = M;
+    }
+    __syncthreads();
 #pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh)
-      if (hh < nh) M[hh] = fmaxf(M[hh], __ldg(a.part_m + pi * a.Hq + h0 + hh) * mscale);
-  }
+    for (int hh = 0; hh < kCombHeads; ++hh) o[hh] *= s_o[hh];
+    __syncthreads();
+    for (int t = d; t < nc * kCombHeads; t += D) {
+      const int hh = t % kCombHeads;
+      const float M = s_m[hh];
+      s_w[t] = exp2f(s_w[t] - (M == -CUDART_INF_F ? 0.f : M));  // 0 for empty partials
+    }
+    __syncthreads();
+    if (d < nh) {  // running sum of head d
+      float L = s_l[d];
+      for (int i = 0; i < nc; ++i) {
+        const float w = s_w[i * kCombHeads + d];
+        if (w > 0.f) L = fmaf(sparse ? __ldg(a.part_l + pidx(c0 + i) * a.Hq + h0 + d) : 1.f, w, L);
+      }
+      s_l[d] = L;
+    }
+    // accumulate: independent loads, four partials in flight
+#pragma unroll 4
+    for (int i = 0; i < nc; ++i) {
+      const int64_t hi = pidx(c0 + i) * a.Hq + h0;
 #pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh) M[hh] = M[hh] == -CUDART_INF_F ? 0.f : M[hh];
-#pragma unroll 2
-  for (int i = 0; i < np; ++i) {
-    const int64_t pi = pidx(i);
-#pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh) {
-      if (hh < nh) {
-        const int64_t hi = pi * a.Hq + h0 + hh;
-        const float w = exp2f(__ldg(a.part_m + hi) * mscale - M[hh]);
-        const float lv = sparse ? __ldg(a.part_l + hi) : 1.f;
-        const float ov = __ldg(a.part_o + hi * D + d);
-        if (w > 0.f) {  // skips empty partials (m = -inf), whose o / l may be uninitialised
-          L[hh] = fmaf(lv, w, L[hh]);
-          o[hh] = fmaf(ov, w, o[hh]);
-        }
+      for (int hh = 0; hh < kCombHeads; ++hh) {
+        const float w = s_w[i * kCombHeads + hh];
+        if (hh < nh && w > 0.f) o[hh] = fmaf(__ldg(a.part_o + (hi + hh) * D + d), w, o[hh]);
       }
     }
   }
+  __syncthreads();
 #pragma unroll
   for (int hh = 0; hh < kCombHeads; ++hh) {
-    if (hh < nh) {
-      s_o[hh][d] = L[hh] > 0.f ? o[hh] / L[hh] : 0.f;
-      if (d == 0 && a.lse_out)
-        a.lse_out[(int64_t)(r + a.row_offset) * a.Hq + h0 + hh] =
-            L[hh] > 0.f ? (M[hh] + log2f(L[hh])) * kLn2 : -CUDART_INF_F;
-    } else {
-      s_o[hh][d] = 0.f;
-    }
+    const float L = s_l[hh];
+    s_o[hh * D + d] = (hh < nh && L > 0.f) ? o[hh] / L : 0.f;
   }
+  if (d < nh && a.lse_out) {
+    const float L = s_l[d], M = s_m[d];
+    a.lse_out[(int64_t)(r + a.row_offset) * a.Hq + h0 + d] =
+        L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
   float acc[kCombHeads];
   if (a.out_rotated) {
 #pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = s_o[hh][d];
+    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = s_o[hh * D + d];
   } else {
 #pragma unroll
     for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = 0.f;
-    // column d of Pi: 16 independent loads in flight per batch
-    for (int j0 = 0; j0 < D; j0 += 16) {
-      float pv[16];
+    if (kStagePi) {
+#pragma unroll 8
+      for (int j = 0; j < D; ++j) {
+        const float pv = s_pi[j * D + d];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) pv[u] = __ldg(a.rotation + (size_t)(j0 + u) * D + d);
+        for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh * D + j], pv, acc[hh]);
+      }
+    } else {
+      for (int j0 = 0; j0 < D; j0 += 16) {  // column d of Pi from L2, 16 loads in flight
+        float pv[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
+        for (int u = 0; u < 16; ++u) pv[u] = __ldg(a.rotation + (size_t)(j0 + u) * D + d);
 #pragma unroll
-        for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh][j0 + u], pv[u], acc[hh]);
+        for (int u = 0; u < 16; ++u)
+#pragma unroll
+          for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh * D + j0 + u], pv[u], acc[hh]);
+      }
     }
   }
 #pragma unroll
@@ -557,18 +605,32 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
                        acc[hh]);
 }
 
-int launch_combine(const CombineArgs& c, int D, cudaStream_t st) {
-  if (c.rows == 0) return TQ4_OK;
-  dim3 grid(c.rows, (c.Hq + kCombHeads - 1) / kCombHeads);
-  switch (D) {
-    case 64: combine_kernel<64><<<grid, 64, 0, st>>>(c); break;
-    case 96: combine_kernel<96><<<grid, 96, 0, st>>>(c); break;
-    case 128: combine_kernel<128><<<grid, 128, 0, st>>>(c); break;
-    case 256: combine_kernel<256><<<grid, 256, 0, st>>>(c); break;
-    default: return TQ4_ERR_UNSUPPORTED;
+template <int D>
+int launch_combine_t(const CombineArgs& c, cudaStream_t st) {
+  constexpr size_t smem = ((size_t)(D <= 128 ? D * D : 0) + kCombHeads * D +
+                           kCombMaxParts * kCombHeads + 2 * kCombHeads) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(combine_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return TQ4_ERR_CUDA;
+    attr_set = true;
   }
+  dim3 grid(c.rows, (c.Hq + kCombHeads - 1) / kCombHeads);
+  combine_kernel<D><<<grid, D, smem, st>>>(c);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
+}
+
+int launch_combine(const CombineArgs& c, int D, cudaStream_t st) {
+  if (c.rows == 0) return TQ4_OK;
+  switch (D) {
+    case 64: return launch_combine_t<64>(c, st);
+    case 96: return launch_combine_t<96>(c, st);
+    case 128: return launch_combine_t<128>(c, st);
+    case 256: return launch_combine_t<256>(c, st);
+  }
+  return TQ4_ERR_UNSUPPORTED;
 }
 
 template <int D>
