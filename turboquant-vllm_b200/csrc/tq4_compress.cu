@@ -116,8 +116,12 @@ compress_kernel(const CompressArgs a) {
     }
     __syncwarp();
 
-    // ---- rotation: acc[byte][even/odd][row] -------------------------------------------
+    // ---- rotation: acc[byte][even/odd][row]; k is reduced in four quarters combined as
+    //      (s0 + s1) + (s2 + s3) so the result does not depend on which kernel ran ---------
     float acc_e[NBL][kRowsPerWarp], acc_o[NBL][kRowsPerWarp];
+    float t_e[NBL][kRowsPerWarp], t_o[NBL][kRowsPerWarp];   // s0 + s1, later the total
+    float u_e[NBL][kRowsPerWarp], u_o[NBL][kRowsPerWarp];   // s0, later s2
+    constexpr int KQ = D / 4;
 #pragma unroll
     for (int i = 0; i < NBL; ++i)
 #pragma unroll
@@ -146,8 +150,26 @@ compress_kernel(const CompressArgs a) {
           acc_o[i][2] = fmaf(xq.z, po, acc_o[i][2]);
           acc_o[i][3] = fmaf(xq.w, po, acc_o[i][3]);
         }
+        const int kg = chunk * KC + kk + 1;  // quarter boundaries (uniform branch)
+        if (kg % KQ == 0) {
+          const int q = kg / KQ;  // quarters finished so far
+#pragma unroll
+          for (int i = 0; i < NBL; ++i)
+#pragma unroll
+            for (int r = 0; r < kRowsPerWarp; ++r) {
+              if (q == 1) { u_e[i][r] = acc_e[i][r]; u_o[i][r] = acc_o[i][r]; }
+              else if (q == 2) { t_e[i][r] = u_e[i][r] + acc_e[i][r]; t_o[i][r] = u_o[i][r] + acc_o[i][r]; }
+              else if (q == 3) { u_e[i][r] = acc_e[i][r]; u_o[i][r] = acc_o[i][r]; }
+              else { t_e[i][r] = t_e[i][r] + (u_e[i][r] + acc_e[i][r]); t_o[i][r] = t_o[i][r] + (u_o[i][r] + acc_o[i][r]); }
+              acc_e[i][r] = acc_o[i][r] = 0.f;
+            }
+        }
       }
     }
+#pragma unroll
+    for (int i = 0; i < NBL; ++i)
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) { acc_e[i][r] = t_e[i][r]; acc_o[i][r] = t_o[i][r]; }
     __syncwarp();
 
     // ---- bucketize, pack, store ---------------------------------------------------------
@@ -194,11 +216,124 @@ compress_kernel(const CompressArgs a) {
   }
 }
 
+// Small launches (decode: a few hundred to a few thousand rows): one CTA of four warps per row,
+// each warp reduces one quarter of k with Pi^T read straight from L1/L2; the four partial sums
+// are combined as (s0 + s1) + (s2 + s3), the same order the streaming kernel uses, so a row
+// compresses to the same bytes whichever kernel handles it.
+template <int D, typename T>
+__global__ void __launch_bounds__(128) compress_small_kernel(const CompressArgs a) {
+  using Cfg = CompressCfg<D>;
+  constexpr int HALF = Cfg::HALF, NBL = Cfg::NBL, XPL = Cfg::XPL, KQ = D / 4;
+  __shared__ float s_x[D];
+  __shared__ float s_part[3][2 * NBL][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = blockIdx.x;
+  const int64_t rows_per_src = a.n_tokens * a.num_heads;
+  const int src = (int)(row / rows_per_src);
+  const int64_t rem = row - (int64_t)src * rows_per_src;
+  const int64_t tok = rem / a.num_heads;
+  const int h = (int)(rem - tok * a.num_heads);
+  const T* xp = reinterpret_cast<const T*>(a.x[src]) + tok * a.token_stride[src] +
+                (int64_t)h * a.head_stride[src];
+  float xv[XPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < XPL; ++i) {
+    const int k = lane + 32 * i;
+    xv[i] = (k < D) ? to_float<T>(xp[k]) : 0.f;
+    ss = fmaf(xv[i], xv[i], ss);
+  }
+  ss = warp_sum(ss);
+  const float norm = sqrtf(ss);
+  const float den = norm + 1e-10f;
+  if (warp == 0) {
+#pragma unroll
+    for (int i = 0; i < XPL; ++i) {
+      const int k = lane + 32 * i;
+      if (k < D) s_x[k] = xv[i] / den;
+    }
+  }
+  __syncthreads();
+  float acc[2 * NBL];
+#pragma unroll
+  for (int i = 0; i < 2 * NBL; ++i) acc[i] = 0.f;
+  const int k0 = warp * KQ;
+  // explicit load batches: 8 k-steps of Pi^T (up to 32 independent loads) are in flight before
+  // the first FMA of the batch consumes them
+  static_assert(KQ % 8 == 0, "quarter of head_dim must be a multiple of 8");
+  for (int kb = 0; kb < KQ; kb += 8) {
+    float pe[8][NBL], po[8][NBL];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int i = 0; i < NBL; ++i) {
+        const int p = lane + 32 * i;
+        const int k = k0 + kb + u;
+        pe[u][i] = (p < HALF) ? __ldg(a.rot_even + k * HALF + p) : 0.f;
+        po[u][i] = (p < HALF) ? __ldg(a.rot_odd + k * HALF + p) : 0.f;
+      }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const float xk = s_x[k0 + kb + u];
+#pragma unroll
+      for (int i = 0; i < NBL; ++i) {
+        acc[2 * i] = fmaf(xk, pe[u][i], acc[2 * i]);
+        acc[2 * i + 1] = fmaf(xk, po[u][i], acc[2 * i + 1]);
+      }
+    }
+  }
+  if (warp > 0) {
+#pragma unroll
+    for (int i = 0; i < 2 * NBL; ++i) s_part[warp - 1][i][lane] = acc[i];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+#pragma unroll
+  for (int i = 0; i < 2 * NBL; ++i)
+    acc[i] = (acc[i] + s_part[0][i][lane]) + (s_part[1][i][lane] + s_part[2][i][lane]);
+
+  const float* b = a.bounds[src];
+  const int nb = a.n_bounds[src];
+  uint8_t* dst_idx;
+  float* dst_norm;
+  if (a.cache != nullptr) {
+    if (tok >= a.n_slots) return;
+    const int64_t slot = a.slot_mapping[tok];
+    if (slot < 0) return;
+    if (slot >= a.num_cache_slots) {
+      if (lane == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_SLOT);
+      return;
+    }
+    const RowLayout lay = row_layout(a.num_heads, D);
+    uint8_t* rowp = a.cache + slot * a.cache_token_stride;
+    dst_idx = rowp + (src == 0 ? lay.k_idx : lay.v_idx) + h * HALF;
+    dst_norm = reinterpret_cast<float*>(rowp + (src == 0 ? lay.k_norm : lay.v_norm) + h * 4);
+  } else {
+    dst_idx = a.packed_out + row * HALF;
+    dst_norm = a.norms_out + row;
+  }
+#pragma unroll
+  for (int i = 0; i < NBL; ++i) {
+    const int p = lane + 32 * i;
+    if (p < HALF)
+      dst_idx[p] =
+          (uint8_t)(((bucketize(acc[2 * i], b, nb) & 0xF) << 4) | (bucketize(acc[2 * i + 1], b, nb) & 0xF));
+  }
+  if (lane == 0) *dst_norm = norm;
+}
+
+constexpr int64_t kSmallRows = 8192;  // below this the one-warp-per-row kernel wins
+
 template <int D, typename T>
 int launch_compress(const CompressArgs& a, cudaStream_t st) {
   using Cfg = CompressCfg<D>;
   const int64_t total_rows = a.n_tokens * a.num_heads * a.n_sources;
   if (total_rows == 0) return TQ4_OK;
+  if (total_rows <= kSmallRows) {
+    compress_small_kernel<D, T><<<(unsigned)total_rows, 128, 0, st>>>(a);
+    TQ4_CHECK_LAUNCH();
+    return TQ4_OK;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(compress_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
