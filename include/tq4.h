@@ -38,7 +38,8 @@ typedef enum {
   TQ4_ERR_INVALID_ARG = 1, /* null pointer, negative size, misaligned pointer            */
   TQ4_ERR_UNSUPPORTED = 2, /* head_dim / group size / dtype outside the supported set    */
   TQ4_ERR_CUDA = 3,        /* a CUDA runtime call failed (launch configuration, ...)      */
-  TQ4_ERR_WORKSPACE = 4    /* workspace smaller than tq4_attention_workspace_bytes says  */
+  TQ4_ERR_WORKSPACE = 4,   /* workspace smaller than tq4_attention_workspace_bytes says  */
+  TQ4_ERR_STATIC_SCRATCH = 5 /* request exceeds the built-in scratch of tq4_paged_attention_static */
 } tq4_status;
 
 /* bits OR-ed into *err_flag by kernels */
@@ -180,6 +181,41 @@ int tq4_combine_partials(const float* parts_o, const float* parts_lse, int world
                          const float* rotation,
                          void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
                          void* stream);
+
+/*
+ * tq4_paged_attention without any caller-provided (or library-allocated) scratch.
+ * No counterpart in the reference.
+ *
+ * Some callers cannot hand over a workspace because they cannot allocate device memory at the
+ * point of the call: a serving engine that has already given every free byte of HBM to the KV
+ * cache, a plugin hook that runs after the host framework froze its memory pool, code that must
+ * not risk the implicit device synchronisation of cudaMalloc/cudaFree in a latency-critical loop.
+ * For them the library carries its own scratch: a fixed array of TQ4_STATIC_SCRATCH_BYTES in the
+ * library image (one copy per GPU that loads the library, held until the process exits).
+ *
+ * Same arguments and results as tq4_paged_attention minus lse_out / out_rotated / workspace.
+ *   - Requests whose tq4_attention_workspace_bytes() exceeds TQ4_STATIC_SCRATCH_BYTES return
+ *     TQ4_ERR_STATIC_SCRATCH (e.g. 32 query heads, head_dim 128: up to ~270 query rows).
+ *   - The entry point calls no cudaMalloc / cudaFree or any allocating routine.  Its FIRST call
+ *     on each device looks up the scratch address (cudaGetSymbolAddress, that device current);
+ *     make that first call outside of stream capture.
+ *   - All calls on a device share the one scratch area.  Nothing in it needs to be zero at entry
+ *     (every word a call reads was written earlier by the same call), but two calls whose kernels
+ *     overlap on the GPU (different streams) race on it: serialise them.
+ */
+#define TQ4_STATIC_SCRATCH_BYTES (32u << 20)
+int tq4_paged_attention_static(const void* q, int q_dtype, int64_t num_rows, int num_seqs,
+                               int num_q_heads, int num_kv_heads, int head_dim,
+                               int64_t q_token_stride, int64_t q_head_stride,
+                               const uint8_t* cache, int64_t cache_block_stride,
+                               int64_t cache_token_stride, int64_t num_blocks, int block_size,
+                               const int32_t* block_table, int64_t bt_stride,
+                               const int32_t* seq_lens, const int32_t* query_start_loc,
+                               const float* k_centroids, int n_k_centroids,
+                               const float* v_centroids, int n_v_centroids,
+                               const float* rotation, float sm_scale, int causal, int sliding_window,
+                               void* out, int out_dtype, int64_t out_token_stride,
+                               int64_t out_head_stride, int mode, int* err_flag, void* stream);
 
 /*
  * Per-kernel timing aid (no counterpart in the reference, which times with torch.cuda.Event

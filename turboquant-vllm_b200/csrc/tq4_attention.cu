@@ -674,6 +674,9 @@ extern "C" const char* tq4_status_string(int status) {
     case TQ4_ERR_UNSUPPORTED: return "unsupported head_dim / head grouping / dtype";
     case TQ4_ERR_CUDA: return "CUDA runtime error at launch";
     case TQ4_ERR_WORKSPACE: return "workspace too small";
+    case TQ4_ERR_STATIC_SCRATCH:
+      return "request needs more scratch than the built-in static area (TQ4_STATIC_SCRATCH_BYTES); "
+             "use tq4_paged_attention with a caller-provided workspace";
   }
   return "unknown status";
 }
@@ -828,4 +831,52 @@ extern "C" int tq4_combine_partials(const float* parts_o, const float* parts_lse
   c.out_token_stride = out_token_stride;
   c.out_head_stride = out_head_stride;
   return launch_combine(c, head_dim, (cudaStream_t)stream);
+}
+
+// ======================================================================================
+// Allocation-free variant: the scratch lives in the library image.
+// ======================================================================================
+// One fixed scratch area per GPU that loads the library, held until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[TQ4_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the CURRENT device.  In host code the symbol's name is
+// only a handle, never a device pointer, so the address is asked for once per device with
+// cudaGetSymbolAddress (while that device is current) and remembered.
+static int static_scratch_address(void** out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TQ4_ERR_CUDA;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return TQ4_ERR_CUDA;
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return TQ4_OK;
+}
+
+extern "C" int tq4_paged_attention_static(
+    const void* q, int q_dtype, int64_t num_rows, int num_seqs, int num_q_heads, int num_kv_heads,
+    int head_dim, int64_t q_token_stride, int64_t q_head_stride, const uint8_t* cache,
+    int64_t cache_block_stride, int64_t cache_token_stride, int64_t num_blocks, int block_size,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+    const int32_t* query_start_loc, const float* k_centroids, int n_k_centroids,
+    const float* v_centroids, int n_v_centroids, const float* rotation, float sm_scale, int causal,
+    int sliding_window, void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
+    int mode, int* err_flag, void* stream) {
+  if (num_rows < 0) return TQ4_ERR_INVALID_ARG;
+  if (num_rows == 0) return TQ4_OK;
+  const size_t need = tq4_attention_workspace_bytes(num_rows, num_q_heads, num_kv_heads, head_dim);
+  if (need == 0) return TQ4_ERR_UNSUPPORTED;
+  if (need > (size_t)TQ4_STATIC_SCRATCH_BYTES) return TQ4_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != TQ4_OK) return rc;
+  return tq4_paged_attention(q, q_dtype, num_rows, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                             q_token_stride, q_head_stride, cache, cache_block_stride,
+                             cache_token_stride, num_blocks, block_size, block_table, bt_stride,
+                             seq_lens, query_start_loc, k_centroids, n_k_centroids, v_centroids,
+                             n_v_centroids, rotation, sm_scale, causal, sliding_window, out, out_dtype,
+                             out_token_stride, out_head_stride, nullptr, 0, scratch,
+                             (size_t)TQ4_STATIC_SCRATCH_BYTES, mode, err_flag, stream);
 }

@@ -19,6 +19,7 @@ F32, F16, BF16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 DEV_BAD_SLOT, DEV_BAD_BLOCK, DEV_TIMEOUT = 1, 2, 4
+STATIC_SCRATCH_BYTES = 32 << 20
 
 # name -> (restype, argtypes); must list every symbol of include/tq4.h
 _SIGNATURES = {
@@ -44,6 +45,11 @@ _SIGNATURES = {
                                     c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
     "tq4_combine_partials": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                      c_void_p, c_int, c_int64, c_int64, c_void_p]),
+    "tq4_paged_attention_static": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
+                                           c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                           c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                           c_void_p, c_int, c_void_p, c_float, c_int, c_int,
+                                           c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "tq4_profile_start": (c_int, [c_int]),
     "tq4_profile_stop": (c_int, []),
     "tq4_profile_read": (c_int, [c_int, c_void_p, c_int]),
@@ -100,6 +106,8 @@ def check(status: int, what: str) -> None:
         msg = lib().tq4_status_string(status).decode()
         if status == 2:
             raise NotImplementedError(f"{what}: {msg}")
+        if status == 5:
+            raise ValueError(f"{what}: {msg}")
         raise RuntimeError(f"{what}: {msg} (tq4 status {status})")
 
 

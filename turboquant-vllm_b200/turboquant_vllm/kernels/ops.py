@@ -421,3 +421,53 @@ def combine_partials(
     )
     nv.check(st, "combine_partials")
     return out
+
+
+def paged_tq4_attention_static(
+    q: torch.Tensor,
+    kv_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    k_centroids: torch.Tensor,
+    v_centroids: torch.Tensor,
+    rotation: torch.Tensor,
+    num_kv_heads: int,
+    block_size: int,
+    out: torch.Tensor,
+    sm_scale: float | None = None,
+    *,
+    query_start_loc: torch.Tensor | None = None,
+    causal: bool = True,
+    sliding_window: int | None = None,
+    mode: int = 0,
+) -> torch.Tensor:
+    """``paged_tq4_attention`` for callers that must not allocate device memory.
+
+    Nothing is allocated here or in the library: ``out`` must be supplied, every tensor must
+    already be in the layout the kernel wants (no hidden ``.contiguous()`` copies), and the
+    scratch is a fixed area built into the library (``STATIC_SCRATCH_BYTES`` per GPU).  A request
+    that needs more scratch than that raises ``ValueError``.  Calls on one device share the area,
+    so they must not overlap on the GPU; make the first call on a device outside stream capture.
+    """
+    nv.require_cuda(q, kv_cache, block_table, seq_lens, k_centroids, v_centroids, rotation, out)
+    t, hq, d = q.shape
+    assert q.stride(2) == 1 and out.shape == (t, hq, d) and out.stride(2) == 1
+    assert kv_cache.dtype == torch.uint8 and kv_cache.stride(2) == 1
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    assert seq_lens.dtype == torch.int32 and seq_lens.is_contiguous()
+    assert rotation.dtype == torch.float32 and rotation.is_contiguous()
+    if query_start_loc is not None:
+        assert query_start_loc.dtype == torch.int32 and query_start_loc.is_contiguous()
+    st = nv.lib().tq4_paged_attention_static(
+        q.data_ptr(), nv.dtype_code(q.dtype), t, seq_lens.numel(), hq, num_kv_heads, d,
+        q.stride(0), q.stride(1),
+        kv_cache.data_ptr(), kv_cache.stride(0), kv_cache.stride(1), kv_cache.shape[0], block_size,
+        block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(), nv.ptr(query_start_loc),
+        k_centroids.data_ptr(), k_centroids.numel(), v_centroids.data_ptr(), v_centroids.numel(),
+        rotation.data_ptr(), float(1.0 / math.sqrt(d) if sm_scale is None else sm_scale),
+        int(bool(causal)), int(sliding_window or 0),
+        out.data_ptr(), nv.dtype_code(out.dtype), out.stride(0), out.stride(1),
+        mode, None, nv.stream_ptr(q.device),
+    )
+    nv.check(st, "paged_tq4_attention_static")
+    return out
