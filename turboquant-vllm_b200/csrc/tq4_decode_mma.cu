@@ -35,7 +35,7 @@ namespace tq4 {
 namespace {
 
 constexpr uint32_t kTableBytes = 65536;
-constexpr int kStages = 4;
+constexpr int kStages = 2;  // ring stages per warp, one PAIR of 16-token tiles each
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -198,7 +198,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   // ---- shared memory map: [rings A][64 KB table on a 64 KB boundary][rings B] ------------------
   const uint32_t base = smem_u32(smem_raw);
   const uint32_t tab = (base + (kTableBytes - 1)) & ~(kTableBytes - 1);
-  constexpr uint32_t kRing = kStages * kStage;
+  constexpr uint32_t kRing = kStages * 2 * kStage;  // each ring stage holds a pair of tiles
   const uint32_t n_a = (tab - base) / kRing;
   const uint32_t end = base + smem_total;
   const uint32_t ring =
@@ -332,9 +332,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
              (int64_t)(pc % a.block_size) * a.cache_token_stride;
     };
     // ---- issue the copies of one tile into ring stage st; returns 1 if its page is valid --------
-    auto issue_tile = [&](int tt, int blk, int st) -> uint32_t {
+    auto issue_tile = [&](int tt, int blk, uint32_t sb, uint32_t bar) -> uint32_t {
       const int pos0 = pos0_of(tt);
-      const uint32_t sb = ring + st * kStage;
       uint32_t ok = 1;
       if (TMA) {
         // four box copies by one lane: K rows, V rows, K-norm and V-norm columns of the 16 tokens
@@ -342,8 +341,6 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
         if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
         if (lane == 0) {
           const int inpage = bs_shift >= 0 ? (pos0 & (a.block_size - 1)) : (pos0 % a.block_size);
-          const uint32_t bar = bar0 + st * 8;
-          mbar_expect_tx(bar, C::kTmaTxBytes);
           tma_load_3d(sb, &tm_data, lay.k_idx + kvh * C::HALF, inpage, blk, bar);
           tma_load_3d(sb + C::kTmaV, &tm_data, lay.v_idx + kvh * C::HALF, inpage, blk, bar);
           tma_load_3d(sb + C::kTmaKN, &tm_norm, lay.k_norm + (kvh >> 2) * 16, inpage, blk, bar);
@@ -401,11 +398,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       return __ballot_sync(0xffffffffu, ok) & 0xFFFFu;
     };
 
-    // ---- one 16-token tile from ring stage st: scores, online softmax, PV ------------------------
-    auto compute_tile = [&](int st, int pos0, uint32_t okmask) {
-      const uint32_t sb = ring + st * kStage;
+    // ---- pieces of the per-tile work; sb = shared address of the tile's ring slot -----------------
+    // K side of one tile: raw dots of (token g, head c) and (token g+8, head c) per n-block
+    auto k_side = [&](uint32_t sb, float (&dots)[NB][2]) {
       uint32_t kw0[C::KW], kw1[C::KW];
-      float nrm[4];  // kn(g), kn(g+8), vn(g), vn(g+8)
       if (TMA) {
         const uint32_t ka = sb + g * C::HALF + c * C::KBY;
 #pragma unroll
@@ -413,20 +409,13 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
           lds_words<C::UK>(ka + u * C::UK, kw0 + u * (C::UK / 4));
           lds_words<C::UK>(ka + 8 * C::HALF + u * C::UK, kw1 + u * (C::UK / 4));
         }
-        const uint32_t na = sb + C::kTmaKN + g * 16 + (kvh & 3) * 4;
-        lds_words<4>(na, reinterpret_cast<uint32_t*>(nrm));
-        lds_words<4>(na + 128, reinterpret_cast<uint32_t*>(nrm + 1));
-        lds_words<4>(na + 256, reinterpret_cast<uint32_t*>(nrm + 2));
-        lds_words<4>(na + 384, reinterpret_cast<uint32_t*>(nrm + 3));
       } else {
 #pragma unroll
         for (int u = 0; u < C::NK; ++u) {
           lds_words<C::UK>(sb + u * 32 * C::UK + lane * C::UK, kw0 + u * (C::UK / 4));
           lds_words<C::UK>(sb + C::kOffK1 + u * 32 * C::UK + lane * C::UK, kw1 + u * (C::UK / 4));
         }
-        lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
       }
-
       float sacc[NB][2][4];  // two independent accumulation chains per n-block
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb)
@@ -450,9 +439,26 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
             mma16816(sacc[nb][1], a0, a1, a2, a3, qf[nb][2 * w + 1][0], qf[nb][2 * w + 1][1]);
         }
       }
-
-      // V words of tokens 2c, 2c+1, 2c+8, 2c+9 (loaded now, consumed after the softmax)
-      uint32_t vw[4][C::VW + C::VH];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        dots[nb][0] = (sacc[nb][0][0] + sacc[nb][1][0]) + (sacc[nb][0][1] + sacc[nb][1][1]);
+        dots[nb][1] = (sacc[nb][0][2] + sacc[nb][1][2]) + (sacc[nb][0][3] + sacc[nb][1][3]);
+      }
+    };
+    auto load_norms = [&](uint32_t sb, float (&nrm)[4]) {  // kn(g), kn(g+8), vn(g), vn(g+8)
+      if (TMA) {
+        const uint32_t na = sb + C::kTmaKN + g * 16 + (kvh & 3) * 4;
+        lds_words<4>(na, reinterpret_cast<uint32_t*>(nrm));
+        lds_words<4>(na + 128, reinterpret_cast<uint32_t*>(nrm + 1));
+        lds_words<4>(na + 256, reinterpret_cast<uint32_t*>(nrm + 2));
+        lds_words<4>(na + 384, reinterpret_cast<uint32_t*>(nrm + 3));
+      } else {
+        lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
+      }
+    };
+    // V side of one tile: O^T += V^T * Psplit^T with the tile's probability fragments
+    auto v_side = [&](uint32_t sb, const uint32_t (&pf)[NB][2]) {
+      uint32_t vw[4][C::VW + C::VH];  // tokens 2c, 2c+1, 2c+8, 2c+9
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (TMA) {
@@ -472,62 +478,6 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
           }
         }
       }
-
-      // (token g, head c) and (token g+8, head c); a tile strictly inside the row needs no masks
-      float kn0 = nrm[0], kn1 = nrm[1], vn0 = nrm[2], vn1 = nrm[3];
-      float lg0 = fmaxf(lg2_approx(vn0), -30.f), lg1 = fmaxf(lg2_approx(vn1), -30.f);
-      const bool full = pos0 >= kv_start && pos0 + kTileTokens <= kv_end && okmask == 0xFFFFu;
-      bool ok0 = true, ok1 = true;
-      if (!full) {
-        const int p0 = pos0 + g, p1 = p0 + 8;
-        ok0 = p0 >= kv_start && p0 < kv_end && ((okmask >> g) & 1u);
-        ok1 = p1 >= kv_start && p1 < kv_end && ((okmask >> (g + 8)) & 1u);
-        if (!ok0) { vn0 = 0.f; lg0 = -CUDART_INF_F; }
-        if (!ok1) { vn1 = 0.f; lg1 = -CUDART_INF_F; }
-      }
-      // Online softmax with a lazily updated reference: the running reference m only moves when
-      // the tile maximum exceeds it by more than 2^8, so accumulators are rescaled a handful of
-      // times per row; probabilities stay below 2^8 (exact in the fp16 hi/lo split).
-      uint32_t pf[NB][2];
-      float alpha[NB];
-      bool bump = false;
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        float s0 = ((sacc[nb][0][0] + sacc[nb][1][0]) + (sacc[nb][0][1] + sacc[nb][1][1])) * (fscale[nb] * kn0);
-        float s1 = ((sacc[nb][0][2] + sacc[nb][1][2]) + (sacc[nb][0][3] + sacc[nb][1][3])) * (fscale[nb] * kn1);
-        if (!full) {
-          s0 = ok0 ? s0 : -CUDART_INF_F;
-          s1 = ok1 ? s1 : -CUDART_INF_F;
-        }
-        float mt = fmaxf(s0 + lg0, s1 + lg1);
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
-        const bool up = mt > m[nb] + 8.f;  // also true for the first finite maximum (m = -inf)
-        const float m_new = up ? mt : m[nb];
-        const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
-        alpha[nb] = up ? ex2_approx(m[nb] - m_use) : 1.f;
-        bump |= up;
-        m[nb] = m_new;
-        const float e0 = ex2_approx(s0 - m_use), e1 = ex2_approx(s1 - m_use);
-        l[nb] = fmaf(l[nb], alpha[nb], e0 + e1);
-        pf[nb][0] = movmatrix_trans(split_h2(e0 * vn0));
-        pf[nb][1] = movmatrix_trans(split_h2(e1 * vn1));
-      }
-      if (__any_sync(0xffffffffu, bump)) {
-        asm volatile("" ::: "memory");  // keep this rare path a real branch
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-          // alpha == 1 where the reference did not move
-#pragma unroll
-          for (int i = 0; i < C::MB; ++i)
-#pragma unroll
-            for (int e = 0; e < 4; ++e)  // volatile asm: must not be hoisted out of the branch
-              asm volatile("mul.f32 %0, %0, %1;" : "+f"(acc[i][nb][e]) : "f"(alpha[nb]));
-        }
-      }
-
-      // V side: O^T += V^T * Psplit^T
 #pragma unroll
       for (int w = 0; w < C::VW + C::VH; ++w) {
         const uint32_t x0 = vw[0][w], y0 = vw[1][w], x1 = vw[2][w], y1 = vw[3][w];
@@ -551,33 +501,142 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       }
     };
 
-    // ---- stream the segment through the kStages-deep ring; block ids are fetched one issue ahead --
-    {
-      const int step = sh.TPC;
-      const int first = t + ts;
-      const int n_tiles = (first < seg_end && !dead) ? (seg_end - first + step - 1) / step : 0;
-      if (n_tiles > 0) {
-        int blkp[kStages];  // block ids of the first tiles, fetched together
+    // ---- one pair of consecutive tiles (32 tokens) from ring stage st -----------------------------
+    // okmask: bits 0-15 tile A, bits 16-31 tile B; has2 = tile B exists
+    auto compute_pair = [&](int st, int pos0, uint32_t okmask, bool has2) {
+      const uint32_t sbA = ring + st * (2 * kStage), sbB = sbA + kStage;
+      float dots[2][NB][2];
+      float nrm[2][4];
+      k_side(sbA, dots[0]);
+      load_norms(sbA, nrm[0]);
+      if (has2) {
+        k_side(sbB, dots[1]);
+        load_norms(sbB, nrm[1]);
+      }
+      // token slots of this lane: (tile u, half h) = position pos0 + 16u + g + 8h
+      float kn[2][2], vn[2][2], lg[2][2];
+      bool ok[2][2];
+      const int ntok = has2 ? 32 : 16;
+      const bool full = pos0 >= kv_start && pos0 + ntok <= kv_end &&
+                        okmask == (has2 ? 0xFFFFFFFFu : 0xFFFFu);
 #pragma unroll
-        for (int s = 0; s < kStages; ++s)
-          blkp[s] = (PAGE16 && s < n_tiles) ? __ldg(bt + page_of(pos0_of(first + s * step))) : 0;
-        uint32_t okbits = 0;  // bit i: page of tile k + i is valid
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          kn[u][h] = nrm[u][h];
+          vn[u][h] = nrm[u][2 + h];
+          ok[u][h] = u == 0 || has2;
+          if (!full && ok[u][h]) {
+            const int pp = pos0 + 16 * u + g + 8 * h;
+            ok[u][h] = pp >= kv_start && pp < kv_end && ((okmask >> (16 * u + g + 8 * h)) & 1u);
+          }
+          if (!ok[u][h]) vn[u][h] = 0.f;
+          lg[u][h] = ok[u][h] ? fmaxf(lg2_approx(vn[u][h]), -30.f) : -CUDART_INF_F;
+        }
+      // Online softmax with a lazily updated reference: m only moves when some score (shifted by
+      // log2 of its value norm) exceeds it by more than 2^8, so the cross-lane max reduction and
+      // the accumulator rescale run a handful of times per row; probabilities stay below 2^8.
+      float s[NB][2][2];
+      bool need = false;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            s[nb][u][h] = ok[u][h] ? dots[u][nb][h] * (fscale[nb] * kn[u][h]) : -CUDART_INF_F;
+            need |= s[nb][u][h] + lg[u][h] > m[nb] + 8.f;
+          }
+      if (__any_sync(0xffffffffu, need)) {
+        asm volatile("" ::: "memory");  // rare path: keep it a real branch
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          float mt = fmaxf(fmaxf(s[nb][0][0] + lg[0][0], s[nb][0][1] + lg[0][1]),
+                           fmaxf(s[nb][1][0] + lg[1][0], s[nb][1][1] + lg[1][1]));
+          mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 4));
+          mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
+          mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+          if (mt > m[nb] + 8.f) {  // uniform over the 8 lanes that share head c
+            const float alpha = m[nb] == -CUDART_INF_F ? 0.f : ex2_approx(m[nb] - mt);
+            m[nb] = mt;
+            l[nb] *= alpha;
+#pragma unroll
+            for (int i = 0; i < C::MB; ++i)
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                asm volatile("mul.f32 %0, %0, %1;" : "+f"(acc[i][nb][e]) : "f"(alpha));
+          }
+        }
+      }
+      uint32_t pf[2][NB][2];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        const float m_use = m[nb] == -CUDART_INF_F ? 0.f : m[nb];
+        float lsum = 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const float e = ex2_approx(s[nb][u][h] - m_use);
+            lsum += e;
+            if (u == 0 || has2) pf[u][nb][h] = movmatrix_trans(split_h2(e * vn[u][h]));
+          }
+        l[nb] += lsum;
+      }
+      v_side(sbA, pf[0]);
+      if (has2) v_side(sbB, pf[1]);
+    };
+
+    // ---- stream the segment: kStages ring stages of one tile pair each; block ids one pair ahead ----
+    {
+      const int step = 2 * sh.TPC;
+      const int first = t + 2 * ts;
+      const int n_pairs = (first < seg_end && !dead) ? (seg_end - first + step - 1) / step : 0;
+      auto blk_of = [&](int tt) -> int { return (PAGE16 && tt < seg_end) ? __ldg(bt + page_of(pos0_of(tt))) : 0; };
+      // issue both tiles of pair index pi into its ring stage; returns the pair's 2 validity bits
+      auto issue_pair = [&](int pi, int blk_a, int blk_b, uint32_t use) -> uint32_t {
+        const int ta = first + pi * step;
+        const bool two = ta + 1 < seg_end;
+        const uint32_t sb = ring + (use % kStages) * (2 * kStage);
+        const uint32_t bar = bar0 + (use % kStages) * 8;
+        if (TMA && lane == 0) mbar_expect_tx(bar, two ? 2 * C::kTmaTxBytes : C::kTmaTxBytes);
+        uint32_t okb = issue_tile(ta, blk_a, sb, bar);
+        if (two) okb |= issue_tile(ta + 1, blk_b, sb + kStage, bar) << 1;
+        if (!TMA) cp_async_commit();
+        return okb;
+      };
+      if (n_pairs > 0) {
+        uint32_t okbits = 0;  // 2 bits per in-flight pair, oldest first
 #pragma unroll
         for (int s = 0; s < kStages - 1; ++s) {
-          if (s < n_tiles) okbits |= issue_tile(first + s * step, blkp[s], (gk + s) % kStages) << s;
-          if (!TMA) cp_async_commit();
+          if (s < n_pairs)
+            okbits |= issue_pair(s, blk_of(first + s * step), blk_of(first + s * step + 1), gk + s) << (2 * s);
+          else if (!TMA)
+            cp_async_commit();
         }
-        int blk_next = blkp[kStages - 1];
-        for (int k = 0; k < n_tiles; ++k) {
+        int blk_a = blk_of(first + (kStages - 1) * step), blk_b = blk_of(first + (kStages - 1) * step + 1);
+        for (int k = 0; k < n_pairs; ++k) {
           const int kn = k + kStages - 1;
           if (TMA) __syncwarp();  // every lane has finished reading the stage about to be refilled
-          if (kn < n_tiles)
-            okbits |= issue_tile(first + kn * step, blk_next, (gk + kn) % kStages) << (kStages - 1);
-          if (!TMA) cp_async_commit();
-          if (PAGE16 && kn + 1 < n_tiles) blk_next = __ldg(bt + page_of(pos0_of(first + (kn + 1) * step)));
-          const int pos0 = pos0_of(first + k * step);
-          const uint32_t okmask = PAGE16 ? ((okbits & 1u) ? 0xFFFFu : 0u) : token_okmask(pos0);
-          okbits >>= 1;
+          if (kn < n_pairs)
+            okbits |= issue_pair(kn, blk_a, blk_b, gk + kn) << (2 * (kStages - 1));
+          else if (!TMA)
+            cp_async_commit();
+          if (kn + 1 < n_pairs) {
+            blk_a = blk_of(first + (kn + 1) * step);
+            blk_b = blk_of(first + (kn + 1) * step + 1);
+          }
+          const int ta = first + k * step;
+          const bool has2 = ta + 1 < seg_end;
+          const int pos0 = pos0_of(ta);
+          uint32_t okmask;
+          if (PAGE16) {
+            okmask = ((okbits & 1u) ? 0xFFFFu : 0u) | ((okbits & 2u) ? 0xFFFF0000u : 0u);
+          } else {
+            okmask = token_okmask(pos0);
+            if (has2) okmask |= token_okmask(pos0 + kTileTokens) << 16;
+          }
+          okbits >>= 2;
           const uint32_t use = gk + k;
           if (TMA) {
             if (!mbar_wait_bounded(bar0 + (use % kStages) * 8, (use / kStages) & 1u)) {
@@ -588,10 +647,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
           } else {
             cp_async_wait<kStages - 1>();
           }
-          compute_tile(use % kStages, pos0, okmask);
+          compute_pair(use % kStages, pos0, okmask, has2);
         }
         if (!TMA) cp_async_wait<0>();
-        gk += n_tiles;
+        gk += n_pairs;
       }
     }
 
@@ -677,7 +736,7 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return TQ4_ERR_CUDA;
     const int want = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
     const int stage = TMA ? C::kTmaStageBytes : C::kStageBytes;
-    if (want < (int)kTableBytes + WARPS * kStages * stage) return TQ4_ERR_UNSUPPORTED;
+    if (want < (int)kTableBytes + WARPS * kStages * 2 * stage) return TQ4_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
       return TQ4_ERR_CUDA;
     smem_total = want;
