@@ -231,6 +231,17 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   __syncthreads();
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
   const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
+  // Row g of the score MMA / k-slot of the PV MMA does not hold token g of the tile but token
+  // sigma(g): the permutation makes every shared-memory read of the TMA tiles (16-byte K chunks by
+  // row pairs, 8-byte V chunks by four rows) touch rows of both parities, which together with the
+  // 64-byte TMA swizzle spreads each access over all 32 banks.
+  auto sigma = [](int k) { return (int)((0x63724150u >> (4 * (k & 7))) & 7u) + (k & 8); };  // 0,5,1,4,2,7,3,6
+  const int rg = sigma(g), rc0 = sigma(2 * c), rc1 = sigma(2 * c + 1);
+  constexpr bool SWZ = TMA && D == 128;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
+  auto tile_off = [&](int row, int byte) -> uint32_t {  // offset of (row, byte) inside a [16][D/2] tile
+    return SWZ ? (uint32_t)(row * 64 + ((((byte >> 4) ^ (row >> 1)) & 3) << 4) + (byte & 15))
+               : (uint32_t)(row * C::HALF + byte);
+  };
   uint32_t gk = 0;      // tiles this warp has pushed through the ring (stage = gk % kStages)
   bool dead = false;    // a bounded wait gave up: stop issuing work, fall through to the end
 
@@ -355,19 +366,19 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
         const int inpage = bs_shift >= 0 ? (pos0 & (a.block_size - 1)) : (pos0 % a.block_size);
         const uint8_t* pb = a.cache + (int64_t)(ok ? blk : 0) * a.cache_block_stride +
                             (int64_t)inpage * a.cache_token_stride;
-        rk0 = pb + g * ts32;
+        rk0 = pb + rg * ts32;
         rk1 = rk0 + 8 * ts32;
-        rv[0] = pb + 2 * c * ts32;
-        rv[1] = rv[0] + ts32;
+        rv[0] = pb + rc0 * ts32;
+        rv[1] = pb + rc1 * ts32;
         rv[2] = rv[0] + 8 * ts32;
-        rv[3] = rv[2] + ts32;
+        rv[3] = rv[1] + 8 * ts32;
       } else {
-        rk0 = token_row(pos0 + g);
-        rk1 = token_row(pos0 + g + 8);
-        rv[0] = token_row(pos0 + 2 * c);
-        rv[1] = token_row(pos0 + 2 * c + 1);
-        rv[2] = token_row(pos0 + 2 * c + 8);
-        rv[3] = token_row(pos0 + 2 * c + 9);
+        rk0 = token_row(pos0 + rg);
+        rk1 = token_row(pos0 + rg + 8);
+        rv[0] = token_row(pos0 + rc0);
+        rv[1] = token_row(pos0 + rc1);
+        rv[2] = token_row(pos0 + rc0 + 8);
+        rv[3] = token_row(pos0 + rc1 + 8);
       }
 #pragma unroll
       for (int u = 0; u < C::NK; ++u) {
@@ -403,11 +414,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     auto k_side = [&](uint32_t sb, float (&dots)[NB][2]) {
       uint32_t kw0[C::KW], kw1[C::KW];
       if (TMA) {
-        const uint32_t ka = sb + g * C::HALF + c * C::KBY;
 #pragma unroll
         for (int u = 0; u < C::NK; ++u) {
-          lds_words<C::UK>(ka + u * C::UK, kw0 + u * (C::UK / 4));
-          lds_words<C::UK>(ka + 8 * C::HALF + u * C::UK, kw1 + u * (C::UK / 4));
+          lds_words<C::UK>(sb + tile_off(rg, c * C::KBY + u * C::UK), kw0 + u * (C::UK / 4));
+          lds_words<C::UK>(sb + tile_off(rg + 8, c * C::KBY + u * C::UK), kw1 + u * (C::UK / 4));
         }
       } else {
 #pragma unroll
@@ -447,7 +457,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     };
     auto load_norms = [&](uint32_t sb, float (&nrm)[4]) {  // kn(g), kn(g+8), vn(g), vn(g+8)
       if (TMA) {
-        const uint32_t na = sb + C::kTmaKN + g * 16 + (kvh & 3) * 4;
+        const uint32_t na = sb + C::kTmaKN + rg * 16 + (kvh & 3) * 4;
         lds_words<4>(na, reinterpret_cast<uint32_t*>(nrm));
         lds_words<4>(na + 128, reinterpret_cast<uint32_t*>(nrm + 1));
         lds_words<4>(na + 256, reinterpret_cast<uint32_t*>(nrm + 2));
@@ -462,10 +472,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (TMA) {
-          const int tok = 2 * c + (j & 1) + 8 * (j >> 1);
-          const uint32_t va = sb + C::kTmaV + tok * C::HALF + g * C::VBY;
+          const int tok = ((j & 1) ? rc1 : rc0) + 8 * (j >> 1);
 #pragma unroll
-          for (int u = 0; u < C::NV; ++u) lds_words<C::UV>(va + u * C::UV, vw[j] + u * (C::UV / 4));
+          for (int u = 0; u < C::NV; ++u)
+            lds_words<C::UV>(sb + C::kTmaV + tile_off(tok, g * C::VBY + u * C::UV), vw[j] + u * (C::UV / 4));
         } else {
           const uint32_t vb = sb + C::kOffV + j * C::kVTok;
 #pragma unroll
@@ -527,8 +537,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
           vn[u][h] = nrm[u][2 + h];
           ok[u][h] = u == 0 || has2;
           if (!full && ok[u][h]) {
-            const int pp = pos0 + 16 * u + g + 8 * h;
-            ok[u][h] = pp >= kv_start && pp < kv_end && ((okmask >> (16 * u + g + 8 * h)) & 1u);
+            const int pp = pos0 + 16 * u + rg + 8 * h;
+            ok[u][h] = pp >= kv_start && pp < kv_end && ((okmask >> (16 * u + rg + 8 * h)) & 1u);
           }
           if (!ok[u][h]) vn[u][h] = 0.f;
           lg[u][h] = ok[u][h] ? fmaxf(lg2_approx(vn[u][h]), -30.f) : -CUDART_INF_F;
@@ -707,7 +717,7 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-bool make_cache_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes) {
+bool make_cache_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes, bool swizzle64) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)a.cache_token_stride, (cuuint64_t)a.block_size,
@@ -716,7 +726,7 @@ bool make_cache_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes) {
   const cuuint32_t box[3] = {box_bytes, (cuuint32_t)kTileTokens, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(a.cache), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -744,7 +754,8 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   CUtensorMap tm_data, tm_norm;
   memset(&tm_data, 0, sizeof(tm_data));
   memset(&tm_norm, 0, sizeof(tm_norm));
-  if (TMA && (!make_cache_map(&tm_data, a, D / 2) || !make_cache_map(&tm_norm, a, 16))) return TQ4_ERR_CUDA;
+  if (TMA && (!make_cache_map(&tm_data, a, D / 2, D == 128) || !make_cache_map(&tm_norm, a, 16, false)))
+    return TQ4_ERR_CUDA;
   const int warps = a.sh.HPC * a.sh.TPC;
   kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total, tm_data, tm_norm);
   TQ4_CHECK_LAUNCH();
