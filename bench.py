@@ -285,9 +285,81 @@ def run_ours(args, rank, world, device):
         "compress_config": f"{nt} tokens x {hkv} KV heads, K and V, bf16 -> paged cache, one launch",
         "roofline": roofline, "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
     }
+    if rank == 0 and world == 1 and not args.no_bf16_baseline:
+        del wl["caches"][1:]  # free HBM for the bf16 copies
+        line["bf16_paged_decode"] = bf16_paged_decode_baseline(device, batch, hq, hkv)
+        if "ms" in line["bf16_paged_decode"]:
+            line["bf16_paged_decode"]["tq4_attention_path_ms"] = round(
+                sum(avg[k] for k in ("prologue", "attention", "combine")), 5)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_budget)
     return line
+
+
+# ----------------------------------------------------------------------------------------
+# comparison point: bf16 paged decode of the SAME (uncompressed) cache with a library kernel
+# ----------------------------------------------------------------------------------------
+def bf16_paged_decode_baseline(device, batch, hq, hkv, steps=50):
+    """FlashAttention-style paged decode on a bf16 cache of the same shape (library kernels:
+    vLLM's flash-attn build or FlashInfer).  Returns {"ms", "impl"} or {"error"}.  This is a
+    reference point for the compressed path, not part of the product."""
+    nblk = batch * CTX // BS
+    try:
+        gen = torch.Generator(device=device).manual_seed(3)
+        kc = torch.randn(nblk, BS, hkv, D, device=device, generator=gen).bfloat16()
+        vc = torch.randn(nblk, BS, hkv, D, device=device, generator=gen).bfloat16()
+        kc2, vc2 = kc.clone(), vc.clone()  # rotate two copies: working set 4.3 GB >> L2
+        q = torch.randn(batch, hq, D, device=device, generator=gen).bfloat16()
+        bt = torch.randperm(nblk, device=device, generator=gen).view(batch, CTX // BS).to(torch.int32)
+        sl = torch.full((batch,), CTX, dtype=torch.int32, device=device)
+        cu = torch.arange(batch + 1, dtype=torch.int32, device=device)
+        out = torch.empty_like(q)
+    except Exception as e:  # noqa: BLE001
+        return {"error": f"setup: {type(e).__name__}: {e}"[:200]}
+    errors = []
+
+    def time_it(fn):
+        for i in range(5):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    try:
+        from vllm.vllm_flash_attn import flash_attn_varlen_func
+
+        def fa(i):
+            k_, v_ = (kc, vc) if i % 2 == 0 else (kc2, vc2)
+            flash_attn_varlen_func(q=q, k=k_, v=v_, out=out, cu_seqlens_q=cu, max_seqlen_q=1,
+                                   seqused_k=sl, max_seqlen_k=CTX, softmax_scale=D ** -0.5, causal=True,
+                                   block_table=bt, fa_version=2)
+
+        return {"ms": round(time_it(fa), 5), "impl": "vllm flash_attn_varlen_func (FA2, paged bf16)"}
+    except Exception as e:  # noqa: BLE001
+        errors.append(f"vllm-fa: {type(e).__name__}: {e}"[:160])
+    try:
+        import flashinfer
+
+        ws = torch.empty(128 << 20, dtype=torch.uint8, device=device)
+        w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+        indptr = torch.arange(batch + 1, dtype=torch.int32, device=device) * (CTX // BS)
+        last = torch.full((batch,), BS, dtype=torch.int32, device=device)
+        w.plan(indptr, bt.reshape(-1).contiguous(), last, hq, hkv, D, BS, q_data_type=torch.bfloat16,
+               kv_data_type=torch.bfloat16)
+
+        def fi(i):
+            k_, v_ = (kc, vc) if i % 2 == 0 else (kc2, vc2)
+            w.run(q, (k_, v_), out=out)
+
+        return {"ms": round(time_it(fi), 5), "impl": "flashinfer BatchDecodeWithPagedKVCacheWrapper (bf16)"}
+    except Exception as e:  # noqa: BLE001
+        errors.append(f"flashinfer: {type(e).__name__}: {e}"[:160])
+    return {"error": " | ".join(errors)}
 
 
 # ----------------------------------------------------------------------------------------
@@ -383,6 +455,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4, help="distinct layer caches rotated per step")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-bf16-baseline", action="store_true")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

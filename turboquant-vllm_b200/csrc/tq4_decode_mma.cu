@@ -57,6 +57,15 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// first MMA of an accumulation chain: C = 0 (no zero-initialised accumulator registers needed)
+__device__ __forceinline__ void mma16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   uint32_t y;
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
@@ -428,25 +437,25 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       }
       float sacc[NB][2][4];  // two independent accumulation chains per n-block
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[nb][0][e] = sacc[nb][1][e] = 0.f;
-#pragma unroll
       for (int w = 0; w < C::KW; ++w) {
         const uint32_t w0 = kw0[w], w1 = kw1[w];
         {
           const uint32_t a0 = lut<0>(w0, lb_k), a2 = lut<1>(w0, lb_k);
           const uint32_t a1 = lut<0>(w1, lb_k), a3 = lut<1>(w1, lb_k);
 #pragma unroll
-          for (int nb = 0; nb < NB; ++nb)
-            mma16816(sacc[nb][0], a0, a1, a2, a3, qf[nb][2 * w][0], qf[nb][2 * w][1]);
+          for (int nb = 0; nb < NB; ++nb) {
+            if (w == 0) mma16816_zero(sacc[nb][0], a0, a1, a2, a3, qf[nb][0][0], qf[nb][0][1]);
+            else mma16816(sacc[nb][0], a0, a1, a2, a3, qf[nb][2 * w][0], qf[nb][2 * w][1]);
+          }
         }
         {
           const uint32_t a0 = lut<2>(w0, lb_k), a2 = lut<3>(w0, lb_k);
           const uint32_t a1 = lut<2>(w1, lb_k), a3 = lut<3>(w1, lb_k);
 #pragma unroll
-          for (int nb = 0; nb < NB; ++nb)
-            mma16816(sacc[nb][1], a0, a1, a2, a3, qf[nb][2 * w + 1][0], qf[nb][2 * w + 1][1]);
+          for (int nb = 0; nb < NB; ++nb) {
+            if (w == 0) mma16816_zero(sacc[nb][1], a0, a1, a2, a3, qf[nb][1][0], qf[nb][1][1]);
+            else mma16816(sacc[nb][1], a0, a1, a2, a3, qf[nb][2 * w + 1][0], qf[nb][2 * w + 1][1]);
+          }
         }
       }
 #pragma unroll
@@ -536,13 +545,24 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
           kn[u][h] = nrm[u][h];
           vn[u][h] = nrm[u][2 + h];
           ok[u][h] = u == 0 || has2;
-          if (!full && ok[u][h]) {
-            const int pp = pos0 + 16 * u + rg + 8 * h;
-            ok[u][h] = pp >= kv_start && pp < kv_end && ((okmask >> (16 * u + rg + 8 * h)) & 1u);
-          }
-          if (!ok[u][h]) vn[u][h] = 0.f;
-          lg[u][h] = ok[u][h] ? fmaxf(lg2_approx(vn[u][h]), -30.f) : -CUDART_INF_F;
         }
+      if (!has2) vn[1][0] = vn[1][1] = kn[1][0] = kn[1][1] = 0.f;  // nothing was loaded for tile B
+      if (!full) {  // first / last tiles of a row, missing second tile, bad page: per-token masks
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int pp = pos0 + 16 * u + rg + 8 * h;
+            ok[u][h] = (u == 0 || has2) && pp >= kv_start && pp < kv_end &&
+                       ((okmask >> (16 * u + rg + 8 * h)) & 1u);
+            if (!ok[u][h]) { vn[u][h] = 0.f; kn[u][h] = 0.f; }
+          }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          lg[u][h] = ok[u][h] ? fmaxf(lg2_approx(vn[u][h]), -30.f) : -CUDART_INF_F;
       // Online softmax with a lazily updated reference: m only moves when some score (shifted by
       // log2 of its value norm) exceeds it by more than 2^8, so the cross-lane max reduction and
       // the accumulator rescale run a handful of times per row; probabilities stay below 2^8.
