@@ -162,7 +162,7 @@ def run_ours(args, rank, world, device):
     from turboquant_vllm import _native as nv
     from turboquant_vllm.kernels import ops
 
-    wl = build_workload(device, world, args.layers)
+    wl = build_workload(device, args.emulate_world or world, args.layers)
     batch, hkv, hq = wl["batch"], wl["hkv"], wl["hq"]
     q = wl["q_host"].to(device)
     k_new, v_new = wl["k_host"].to(device), wl["v_host"].to(device)
@@ -456,6 +456,8 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bf16-baseline", action="store_true")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="tuning aid: run ONE rank's share of a W-GPU head-sharded job on this GPU")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -121,7 +121,7 @@ def test_growth_fused_mode_and_quality(cuda_lib):
     cos = torch.nn.functional.cosine_similarity(out_k.float().flatten(2), full.float().flatten(2), dim=-1)
     assert cos.min() > 0.98  # 4-bit reconstruction quality
     # symmetric codebook: V = -K reconstructs to (almost exactly) the negation
-    assert torch.allclose(out_v.float(), -out_k.float(), atol=2e-2)
+    assert torch.allclose(out_v.float(), -out_k.float(), atol=1e-2, rtol=1e-2)  # within one bf16 ulp
     # every append kept the earlier tokens' bytes
     kidx, knorm, _, _ = cc.get_compressed(0)
     first = C(DynamicCache(), head_dim=128, bits=4)._compress_tensor(cc.key_compressor, ks[0], nibble_packed=True)

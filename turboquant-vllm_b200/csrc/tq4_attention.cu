@@ -726,7 +726,7 @@ extern "C" int tq4_paged_attention(
   if (mode == 2 && !mma_ok) return TQ4_ERR_UNSUPPORTED;
   const bool use_mma = mode == 2 || (mode == 0 && mma_ok);
   if (use_mma)
-    make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC));
+    make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC, num_kv_heads));
   const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
   if (workspace_bytes < carve_plan(a.plan, nullptr, rows_cap, num_q_heads, head_dim, a.sh.TPC))
     return TQ4_ERR_WORKSPACE;

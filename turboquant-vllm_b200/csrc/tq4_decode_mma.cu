@@ -177,9 +177,11 @@ struct MmaCfg {
   static constexpr int kOffN = kOffV + 4 * kVTok;
   static constexpr int kStageBytes = kOffN + 32 * 16;
   // TMA stage: K tile [16 tok][D/2] | V tile [16 tok][D/2] | K-norm tile [16][16 B] | V-norm tile
-  static constexpr int kTmaV = 16 * HALF, kTmaKN = 32 * HALF, kTmaVN = 32 * HALF + 256;
-  static constexpr int kTmaStageBytes = 32 * HALF + 512;
-  static constexpr int kTmaTxBytes = 32 * HALF + 512;
+  // (VWIDE: the V box starts 0..12 bytes early, on a 16-byte boundary, and is 16 bytes wider)
+  static constexpr int kTmaV = 16 * HALF;
+  template <bool VWIDE> __host__ __device__ static constexpr int v_pitch() { return VWIDE ? HALF + 16 : HALF; }
+  template <bool VWIDE> __host__ __device__ static constexpr int tma_kn() { return 16 * HALF + 16 * v_pitch<VWIDE>(); }
+  template <bool VWIDE> __host__ __device__ static constexpr int tma_stage() { return tma_kn<VWIDE>() + 512; }
 };
 
 // byte offset (within a head's D/2 V bytes) of this thread's m-block i
@@ -189,13 +191,16 @@ __device__ __forceinline__ int v_byte_of_mblock(int g, int i) {
   return i < 4 * VW ? g * 4 * VW + i : 32 * VW + 2 * g + (i - 4 * VW);
 }
 
-template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS, bool TMA>
+template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS, bool TMA, bool VWIDE>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
                      const __grid_constant__ CUtensorMap tm_data,
+                     const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_norm) {
   using C = MmaCfg<D, ALIGNED>;
-  constexpr int kStage = TMA ? C::kTmaStageBytes : C::kStageBytes;
+  constexpr int kTmaKN = C::template tma_kn<VWIDE>(), kTmaVN = kTmaKN + 256;
+  constexpr int kTmaStage = C::template tma_stage<VWIDE>(), kVPitch = C::template v_pitch<VWIDE>();
+  constexpr int kStage = TMA ? kTmaStage : C::kStageBytes;
   const AttnShape& sh = a.sh;
   const AttnPlan& p = a.plan;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -246,7 +251,11 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   // 64-byte TMA swizzle spreads each access over all 32 banks.
   auto sigma = [](int k) { return (int)((0x63724150u >> (4 * (k & 7))) & 7u) + (k & 8); };  // 0,5,1,4,2,7,3,6
   const int rg = sigma(g), rc0 = sigma(2 * c), rc1 = sigma(2 * c + 1);
-  constexpr bool SWZ = TMA && D == 128;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
+  constexpr bool SWZ = TMA && D == 128 && !VWIDE;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
+  // byte offsets of this head's K norm / V indices / V norm relative to the 16-byte boundary below
+  const int kn_sub = (row_layout(sh.Hkv, D).k_norm + 4 * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15;
+  const int vn_sub = (row_layout(sh.Hkv, D).v_norm + 4 * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15;
+  const int v_sub = VWIDE ? ((row_layout(sh.Hkv, D).v_idx + C::HALF * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15) : 0;
   auto tile_off = [&](int row, int byte) -> uint32_t {  // offset of (row, byte) inside a [16][D/2] tile
     return SWZ ? (uint32_t)(row * 64 + ((((byte >> 4) ^ (row >> 1)) & 3) << 4) + (byte & 15))
                : (uint32_t)(row * C::HALF + byte);
@@ -362,9 +371,9 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
         if (lane == 0) {
           const int inpage = bs_shift >= 0 ? (pos0 & (a.block_size - 1)) : (pos0 % a.block_size);
           tma_load_3d(sb, &tm_data, lay.k_idx + kvh * C::HALF, inpage, blk, bar);
-          tma_load_3d(sb + C::kTmaV, &tm_data, lay.v_idx + kvh * C::HALF, inpage, blk, bar);
-          tma_load_3d(sb + C::kTmaKN, &tm_norm, lay.k_norm + (kvh >> 2) * 16, inpage, blk, bar);
-          tma_load_3d(sb + C::kTmaVN, &tm_norm, lay.v_norm + (kvh >> 2) * 16, inpage, blk, bar);
+          tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, (lay.v_idx + kvh * C::HALF) & ~15, inpage, blk, bar);
+          tma_load_3d(sb + kTmaKN, &tm_norm, (lay.k_norm + kvh * 4) & ~15, inpage, blk, bar);
+          tma_load_3d(sb + kTmaVN, &tm_norm, (lay.v_norm + kvh * 4) & ~15, inpage, blk, bar);
         }
         return ok;
       }
@@ -466,11 +475,11 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     };
     auto load_norms = [&](uint32_t sb, float (&nrm)[4]) {  // kn(g), kn(g+8), vn(g), vn(g+8)
       if (TMA) {
-        const uint32_t na = sb + C::kTmaKN + rg * 16 + (kvh & 3) * 4;
-        lds_words<4>(na, reinterpret_cast<uint32_t*>(nrm));
-        lds_words<4>(na + 128, reinterpret_cast<uint32_t*>(nrm + 1));
-        lds_words<4>(na + 256, reinterpret_cast<uint32_t*>(nrm + 2));
-        lds_words<4>(na + 384, reinterpret_cast<uint32_t*>(nrm + 3));
+        const uint32_t na = sb + kTmaKN + rg * 16;
+        lds_words<4>(na + kn_sub, reinterpret_cast<uint32_t*>(nrm));
+        lds_words<4>(na + 128 + kn_sub, reinterpret_cast<uint32_t*>(nrm + 1));
+        lds_words<4>(na + 256 + vn_sub, reinterpret_cast<uint32_t*>(nrm + 2));
+        lds_words<4>(na + 384 + vn_sub, reinterpret_cast<uint32_t*>(nrm + 3));
       } else {
         lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
       }
@@ -482,9 +491,15 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       for (int j = 0; j < 4; ++j) {
         if (TMA) {
           const int tok = ((j & 1) ? rc1 : rc0) + 8 * (j >> 1);
+          if (VWIDE) {  // 4-byte reads: the chunk may start on any 4-byte boundary
 #pragma unroll
-          for (int u = 0; u < C::NV; ++u)
-            lds_words<C::UV>(sb + C::kTmaV + tile_off(tok, g * C::VBY + u * C::UV), vw[j] + u * (C::UV / 4));
+            for (int u = 0; u < C::VW; ++u)
+              lds_words<4>(sb + C::kTmaV + tok * kVPitch + v_sub + g * C::VBY + 4 * u, vw[j] + u);
+          } else {
+#pragma unroll
+            for (int u = 0; u < C::NV; ++u)
+              lds_words<C::UV>(sb + C::kTmaV + tile_off(tok, g * C::VBY + u * C::UV), vw[j] + u * (C::UV / 4));
+          }
         } else {
           const uint32_t vb = sb + C::kOffV + j * C::kVTok;
 #pragma unroll
@@ -629,7 +644,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
         const bool two = ta + 1 < seg_end;
         const uint32_t sb = ring + (use % kStages) * (2 * kStage);
         const uint32_t bar = bar0 + (use % kStages) * 8;
-        if (TMA && lane == 0) mbar_expect_tx(bar, two ? 2 * C::kTmaTxBytes : C::kTmaTxBytes);
+        if (TMA && lane == 0) mbar_expect_tx(bar, two ? 2 * kTmaStage : kTmaStage);
         uint32_t okb = issue_tile(ta, blk_a, sb, bar);
         if (two) okb |= issue_tile(ta + 1, blk_b, sb + kStage, bar) << 1;
         if (!TMA) cp_async_commit();
@@ -750,14 +765,14 @@ bool make_cache_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes, bool 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, int NB, bool ALIGNED, bool PAGE16, bool TMA>
+template <int D, int NB, bool ALIGNED, bool PAGE16, bool TMA, bool VWIDE>
 int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
-  constexpr int WARPS = (D * NB <= 128) ? 16 : 8;
+  constexpr int WARPS = (D * NB <= 128) ? 16 : 8;  // upper bound; the launch uses HPC * TPC warps
   using C = MmaCfg<D, ALIGNED>;
   // All opt-in shared memory of the SM (one CTA per SM by design): the 64 KB table sits on a
   // 64 KB boundary of the shared window and whole rings are packed on both sides of it.
   static int smem_total = 0;
-  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA>;
+  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA, VWIDE>;
   if (smem_total == 0) {
     int dev = 0, optin = 0;
     cudaGetDevice(&dev);
@@ -765,19 +780,21 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return TQ4_ERR_CUDA;
     const int want = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
-    const int stage = TMA ? C::kTmaStageBytes : C::kStageBytes;
-    if (want < (int)kTableBytes + WARPS * kStages * 2 * stage) return TQ4_ERR_UNSUPPORTED;
+    const int stage = TMA ? C::template tma_stage<VWIDE>() : C::kStageBytes;
+    if (want < (int)kTableBytes + a.sh.HPC * a.sh.TPC * kStages * 2 * stage) return TQ4_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
       return TQ4_ERR_CUDA;
     smem_total = want;
   }
-  CUtensorMap tm_data, tm_norm;
+  CUtensorMap tm_data, tm_v, tm_norm;
   memset(&tm_data, 0, sizeof(tm_data));
+  memset(&tm_v, 0, sizeof(tm_v));
   memset(&tm_norm, 0, sizeof(tm_norm));
-  if (TMA && (!make_cache_map(&tm_data, a, D / 2, D == 128) || !make_cache_map(&tm_norm, a, 16, false)))
+  if (TMA && (!make_cache_map(&tm_data, a, D / 2, D == 128 && !VWIDE) ||
+              !make_cache_map(&tm_v, a, D / 2 + 16, false) || !make_cache_map(&tm_norm, a, 16, false)))
     return TQ4_ERR_CUDA;
   const int warps = a.sh.HPC * a.sh.TPC;
-  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total, tm_data, tm_norm);
+  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total, tm_data, tm_v, tm_norm);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
@@ -792,23 +809,31 @@ bool cache_aligned(const AttnShape& sh, const uint8_t* cache, int64_t bs, int64_
 
 // TMA boxes start on 16-byte boundaries of the token row: every region offset of every head must
 // be a multiple of 16 (true whenever the number of KV heads is a multiple of 4).
+// V indices of a head start on a 16-byte boundary of the row (true when Hkv is a multiple of 4);
+// otherwise the V box is fetched 16 bytes wider from the boundary below (VWIDE).
 bool cache_tma_ok(const AttnArgs& a) {
-  const RowLayout lay = row_layout(a.sh.Hkv, a.sh.D);
-  return cache_aligned(a.sh, a.cache, a.cache_block_stride, a.cache_token_stride) &&
-         a.block_size % kTileTokens == 0 && a.block_size <= 256 && lay.k_norm % 16 == 0 &&
-         lay.v_idx % 16 == 0 && lay.v_norm % 16 == 0 && (a.sh.D / 2) % 16 == 0 && a.sh.Hkv % 4 == 0 &&
+  return (uintptr_t)a.cache % 16 == 0 && a.cache_block_stride % 16 == 0 && a.cache_token_stride % 16 == 0 &&
+         a.block_size % kTileTokens == 0 && a.block_size <= 256 && (a.sh.D / 2) % 16 == 0 &&
+         a.cache_token_stride >= (int64_t)((row_data_bytes(a.sh.Hkv, a.sh.D) + 15) & ~15) &&
          a.num_blocks < (1ll << 31) && getenv("TQ4_NO_TMA") == nullptr && encode_tiled_fn() != nullptr;
+}
+bool cache_v_aligned16(const AttnArgs& a) {
+  const RowLayout lay = row_layout(a.sh.Hkv, a.sh.D);
+  return lay.v_idx % 16 == 0;
 }
 
 template <int D, int NB>
 int launch_mma_dn(const AttnArgs& a, cudaStream_t st) {
   const bool aligned = cache_aligned(a.sh, a.cache, a.cache_block_stride, a.cache_token_stride);
   const bool page16 = a.block_size % kTileTokens == 0;
-  if (D != 96 && cache_tma_ok(a)) return launch_mma_t<D, NB, true, true, (D != 96)>(a, st);
-  if (aligned && page16) return launch_mma_t<D, NB, true, true, false>(a, st);
-  if (aligned) return launch_mma_t<D, NB, true, false, false>(a, st);
-  if (page16) return launch_mma_t<D, NB, false, true, false>(a, st);
-  return launch_mma_t<D, NB, false, false, false>(a, st);
+  if (D != 96 && cache_tma_ok(a)) {
+    if (cache_v_aligned16(a)) return launch_mma_t<D, NB, true, true, (D != 96), false>(a, st);
+    return launch_mma_t<D, NB, true, true, (D != 96), (D != 96)>(a, st);
+  }
+  if (aligned && page16) return launch_mma_t<D, NB, true, true, false, false>(a, st);
+  if (aligned) return launch_mma_t<D, NB, true, false, false, false>(a, st);
+  if (page16) return launch_mma_t<D, NB, false, true, false, false>(a, st);
+  return launch_mma_t<D, NB, false, false, false, false>(a, st);
 }
 
 template <int D>
@@ -818,7 +843,10 @@ int launch_mma_d(const AttnArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-int mma_warps_per_cta(int D, int GC) { return (D * (GC <= 4 ? 1 : 2) <= 128) ? 16 : 8; }
+int mma_warps_per_cta(int D, int GC, int Hkv) {
+  if (D * (GC <= 4 ? 1 : 2) > 128) return 8;
+  return Hkv % 4 == 0 ? 16 : 12;  // wider V tiles need more ring space per warp
+}
 
 bool attention_mma_supported(const AttnShape& sh, int block_size, const uint8_t* cache,
                              int64_t block_stride, int64_t token_stride) {
