@@ -477,9 +477,9 @@ struct CombineArgs {
 
 constexpr int kCombMaxParts = 64;  // partials of one row merged per pass
 
-// One block per (row, 8 heads), D threads.  Pi is copied to shared memory asynchronously at
-// kernel entry and overlaps the merge of the row's partials; the merge weights of all
-// (partial, head) pairs are computed once into shared memory so that the accumulation loop
+// One block per 8 consecutive (row, head) vectors, D threads.  Pi is copied to shared memory
+// asynchronously at kernel entry and overlaps the merge of the partials; the merge weights of all
+// (partial, vector) pairs are computed once into shared memory so that the accumulation loop
 // issues nothing but independent loads.
 template <int D>
 __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
@@ -489,8 +489,12 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
   float* s_w = s_o + kCombHeads * D;                            // [kCombMaxParts][kCombHeads]
   float* s_m = s_w + kCombMaxParts * kCombHeads;                // [kCombHeads] running max
   float* s_l = s_m + kCombHeads;                                // [kCombHeads] running sum
-  const int r = blockIdx.x, h0 = blockIdx.y * kCombHeads, d = threadIdx.x;
-  const int nh = min(kCombHeads, a.Hq - h0);
+  __shared__ long long s_p0[kCombHeads];                        // first partial of the vector's row
+  __shared__ int s_np[kCombHeads], s_row[kCombHeads], s_head[kCombHeads];
+  const int d = threadIdx.x;
+  const int64_t v0 = (int64_t)blockIdx.x * kCombHeads;
+  const int64_t n_vec = (int64_t)a.rows * a.Hq;
+  const int nh = (int)min((int64_t)kCombHeads, n_vec - v0);
   constexpr float kLn2 = 0.6931471805599453f, kLog2e = 1.4426950408889634f;
   constexpr bool kStagePi = D <= 128;  // a 256 x 256 fp32 Pi does not fit in shared memory
   if (kStagePi && !a.out_rotated) {
@@ -501,31 +505,50 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   const bool sparse = a.slot_base != nullptr;
-  const int64_t p0 = sparse ? (int64_t)a.slot_base[r] * a.TPC : 0;
-  const int np = sparse ? (int)((int64_t)a.slot_base[r + 1] * a.TPC - p0) : a.world;
-  auto pidx = [&](int i) -> int64_t { return sparse ? p0 + i : (int64_t)i * a.rows + r; };
   const float mscale = sparse ? 1.f : kLog2e;  // dense partials carry a natural-log LSE
-
-  if (d < kCombHeads) { s_m[d] = -CUDART_INF_F; s_l[d] = 0.f; }
-  float o[kCombHeads];
+  if (d < kCombHeads) {
+    const int64_t v = v0 + d;
+    const int r = d < nh ? (int)(v / a.Hq) : 0;
+    s_row[d] = r;
+    s_head[d] = d < nh ? (int)(v - (int64_t)r * a.Hq) : 0;
+    // partials of row r: sparse = slot-major list [p0, p0 + np), dense = index w * rows + r
+    s_p0[d] = sparse ? (long long)a.slot_base[r] * a.TPC : (long long)r;
+    s_np[d] = d >= nh ? 0 : (sparse ? (a.slot_base[r + 1] - a.slot_base[r]) * a.TPC : a.world);
+    s_m[d] = -CUDART_INF_F;
+    s_l[d] = 0.f;
+  }
+  __syncthreads();
+  int np = 0;
 #pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh) o[hh] = 0.f;
+  for (int hh = 0; hh < kCombHeads; ++hh) np = max(np, s_np[hh]);
+  auto pidx = [&](int hh, int i) -> int64_t {
+    return sparse ? (int64_t)s_p0[hh] + i : (int64_t)i * a.rows + s_p0[hh];
+  };
+
+  float o[kCombHeads];
+  const float* po[kCombHeads];  // this thread's element of partial 0 of each vector
+  const int64_t pstride = (sparse ? (int64_t)1 : (int64_t)a.rows) * a.Hq * D;
+#pragma unroll
+  for (int hh = 0; hh < kCombHeads; ++hh) {
+    o[hh] = 0.f;
+    po[hh] = a.part_o + ((int64_t)s_p0[hh] * a.Hq + s_head[hh]) * D + d;
+  }
   for (int c0 = 0; c0 < np; c0 += kCombMaxParts) {
     const int nc = min(kCombMaxParts, np - c0);
     __syncthreads();
-    // (partial, head) pairs -> log2-domain maxima
-    for (int t = d; t < nc * kCombHeads; t += D) {
+    for (int t = d; t < nc * kCombHeads; t += D) {  // (partial, vector) -> log2-domain maximum
       const int i = t / kCombHeads, hh = t - i * kCombHeads;
-      s_w[t] = hh < nh ? __ldg(a.part_m + pidx(c0 + i) * a.Hq + h0 + hh) * mscale : -CUDART_INF_F;
+      s_w[t] = c0 + i < s_np[hh] ? __ldg(a.part_m + pidx(hh, c0 + i) * a.Hq + s_head[hh]) * mscale
+                                 : -CUDART_INF_F;
     }
     __syncthreads();
-    if (d < kCombHeads) {  // new running max of head d; rescale what was accumulated so far
+    if (d < kCombHeads) {  // new running max of vector d; rescale what was accumulated so far
       float M = s_m[d];
       for (int i = 0; i < nc; ++i) M = fmaxf(M, s_w[i * kCombHeads + d]);
       const float m_use = M == -CUDART_INF_F ? 0.f : M;
       const float resc = s_m[d] == -CUDART_INF_F ? 0.f : exp2f(s_m[d] - m_use);
       s_l[d] *= resc;
-      s_o[d] = resc;       // reuse s_o[0..7] to publish the rescale factor
+      s_o[d] = resc;  // s_o[0..7] publishes the rescale factors
       s_m[d] = M;
     }
     __syncthreads();
@@ -538,22 +561,20 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
       s_w[t] = exp2f(s_w[t] - (M == -CUDART_INF_F ? 0.f : M));  // 0 for empty partials
     }
     __syncthreads();
-    if (d < nh) {  // running sum of head d
+    if (d < nh) {  // running sum of vector d
       float L = s_l[d];
       for (int i = 0; i < nc; ++i) {
         const float w = s_w[i * kCombHeads + d];
-        if (w > 0.f) L = fmaf(sparse ? __ldg(a.part_l + pidx(c0 + i) * a.Hq + h0 + d) : 1.f, w, L);
+        if (w > 0.f) L = fmaf(sparse ? __ldg(a.part_l + pidx(d, c0 + i) * a.Hq + s_head[d]) : 1.f, w, L);
       }
       s_l[d] = L;
     }
-    // accumulate: independent loads, four partials in flight
 #pragma unroll 4
-    for (int i = 0; i < nc; ++i) {
-      const int64_t hi = pidx(c0 + i) * a.Hq + h0;
+    for (int i = 0; i < nc; ++i) {  // accumulate: independent loads, four partials in flight
 #pragma unroll
       for (int hh = 0; hh < kCombHeads; ++hh) {
         const float w = s_w[i * kCombHeads + hh];
-        if (hh < nh && w > 0.f) o[hh] = fmaf(__ldg(a.part_o + (hi + hh) * D + d), w, o[hh]);
+        if (w > 0.f) o[hh] = fmaf(__ldg(po[hh] + (int64_t)(c0 + i) * pstride), w, o[hh]);
       }
     }
   }
@@ -565,7 +586,7 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
   }
   if (d < nh && a.lse_out) {
     const float L = s_l[d], M = s_m[d];
-    a.lse_out[(int64_t)(r + a.row_offset) * a.Hq + h0 + d] =
+    a.lse_out[(int64_t)(s_row[d] + a.row_offset) * a.Hq + s_head[d]] =
         L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -600,8 +621,8 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
   for (int hh = 0; hh < kCombHeads; ++hh)
     if (hh < nh)
       store_from_float(a.out, a.out_dtype,
-                       (int64_t)(r + a.row_offset) * a.out_token_stride +
-                           (int64_t)(h0 + hh) * a.out_head_stride + d,
+                       (int64_t)(s_row[hh] + a.row_offset) * a.out_token_stride +
+                           (int64_t)s_head[hh] * a.out_head_stride + d,
                        acc[hh]);
 }
 
@@ -616,8 +637,8 @@ int launch_combine_t(const CombineArgs& c, cudaStream_t st) {
       return TQ4_ERR_CUDA;
     attr_set = true;
   }
-  dim3 grid(c.rows, (c.Hq + kCombHeads - 1) / kCombHeads);
-  combine_kernel<D><<<grid, D, smem, st>>>(c);
+  const int64_t n_vec = (int64_t)c.rows * c.Hq;
+  combine_kernel<D><<<(unsigned)((n_vec + kCombHeads - 1) / kCombHeads), D, smem, st>>>(c);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
