@@ -146,6 +146,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+// True in exactly one lane of a converged warp; tells the compiler that the guarded region is
+// single-threaded, so bulk-copy instructions inside it need no per-thread serialisation loop.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
                                             uint32_t bar) {
   asm volatile(
@@ -260,6 +271,13 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     return SWZ ? (uint32_t)(row * 64 + ((((byte >> 4) ^ (row >> 1)) & 3) << 4) + (byte & 15))
                : (uint32_t)(row * C::HALF + byte);
   };
+  // lane-constant byte offsets inside a TMA stage: K chunk of token sigma(g), V chunks of tokens
+  // sigma(2c) / sigma(2c+1), norm columns of token sigma(g); tokens +8 are a fixed distance further
+  const uint32_t o_k = tile_off(rg, c * C::KBY);
+  const uint32_t o_v0 = C::kTmaV + (VWIDE ? rc0 * kVPitch + v_sub + g * C::VBY : tile_off(rc0, g * C::VBY));
+  const uint32_t o_v1 = C::kTmaV + (VWIDE ? rc1 * kVPitch + v_sub + g * C::VBY : tile_off(rc1, g * C::VBY));
+  const uint32_t o_kn = kTmaKN + rg * 16 + kn_sub, o_vn = kTmaKN + 256 + rg * 16 + vn_sub;
+  constexpr uint32_t kRow8 = 8 * (SWZ ? 64 : C::HALF), kVRow8 = 8 * (VWIDE ? kVPitch : (SWZ ? 64 : C::HALF));
   uint32_t gk = 0;      // tiles this warp has pushed through the ring (stage = gk % kStages)
   bool dead = false;    // a bounded wait gave up: stop issuing work, fall through to the end
 
@@ -273,6 +291,9 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   if (t_begin >= t_end) return;
   const RowLayout lay = row_layout(sh.Hkv, D);
   const int k_off = lay.k_idx + kvh * C::HALF + c * C::KBY;  // this thread's K chunk
+  // x coordinates (bytes within a token row, 16-byte aligned) of this head's four TMA boxes
+  const int x_k = lay.k_idx + kvh * C::HALF, x_v = (lay.v_idx + kvh * C::HALF) & ~15;
+  const int x_kn = (lay.k_norm + kvh * 4) & ~15, x_vn = (lay.v_norm + kvh * 4) & ~15;
   const int kn_off = lay.k_norm + kvh * 4;
   const int vn_delta = lay.v_norm - lay.k_norm;              // V norm sits this far after the K norm
   const int v_off = lay.v_idx + kvh * C::HALF + g * 4 * C::VW;  // this thread's V word chunk
@@ -364,17 +385,9 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     auto issue_tile = [&](int tt, int blk, uint32_t sb, uint32_t bar) -> uint32_t {
       const int pos0 = pos0_of(tt);
       uint32_t ok = 1;
-      if (TMA) {
-        // four box copies by one lane: K rows, V rows, K-norm and V-norm columns of the 16 tokens
+      if (TMA) {  // the box copies themselves are issued by issue_pair under one election
         ok = blk >= 0 && blk < a.num_blocks;
         if (!ok && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
-        if (lane == 0) {
-          const int inpage = bs_shift >= 0 ? (pos0 & (a.block_size - 1)) : (pos0 % a.block_size);
-          tma_load_3d(sb, &tm_data, lay.k_idx + kvh * C::HALF, inpage, blk, bar);
-          tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, (lay.v_idx + kvh * C::HALF) & ~15, inpage, blk, bar);
-          tma_load_3d(sb + kTmaKN, &tm_norm, (lay.k_norm + kvh * 4) & ~15, inpage, blk, bar);
-          tma_load_3d(sb + kTmaVN, &tm_norm, (lay.v_norm + kvh * 4) & ~15, inpage, blk, bar);
-        }
         return ok;
       }
       const uint8_t *rk0, *rk1, *rv[4];
@@ -434,8 +447,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       if (TMA) {
 #pragma unroll
         for (int u = 0; u < C::NK; ++u) {
-          lds_words<C::UK>(sb + tile_off(rg, c * C::KBY + u * C::UK), kw0 + u * (C::UK / 4));
-          lds_words<C::UK>(sb + tile_off(rg + 8, c * C::KBY + u * C::UK), kw1 + u * (C::UK / 4));
+          // (a 16-byte chunk never straddles a swizzle unit: c * KBY + u * UK is a multiple of UK)
+          const uint32_t ku = o_k + u * C::UK;
+          lds_words<C::UK>(sb + ku, kw0 + u * (C::UK / 4));
+          lds_words<C::UK>(sb + ku + kRow8, kw1 + u * (C::UK / 4));
         }
       } else {
 #pragma unroll
@@ -475,11 +490,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     };
     auto load_norms = [&](uint32_t sb, float (&nrm)[4]) {  // kn(g), kn(g+8), vn(g), vn(g+8)
       if (TMA) {
-        const uint32_t na = sb + kTmaKN + rg * 16;
-        lds_words<4>(na + kn_sub, reinterpret_cast<uint32_t*>(nrm));
-        lds_words<4>(na + 128 + kn_sub, reinterpret_cast<uint32_t*>(nrm + 1));
-        lds_words<4>(na + 256 + vn_sub, reinterpret_cast<uint32_t*>(nrm + 2));
-        lds_words<4>(na + 384 + vn_sub, reinterpret_cast<uint32_t*>(nrm + 3));
+        lds_words<4>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm));
+        lds_words<4>(sb + o_kn + 128, reinterpret_cast<uint32_t*>(nrm + 1));
+        lds_words<4>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 2));
+        lds_words<4>(sb + o_vn + 128, reinterpret_cast<uint32_t*>(nrm + 3));
       } else {
         lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
       }
@@ -490,15 +504,13 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (TMA) {
-          const int tok = ((j & 1) ? rc1 : rc0) + 8 * (j >> 1);
+          const uint32_t vo = sb + ((j & 1) ? o_v1 : o_v0) + (j >> 1) * kVRow8;
           if (VWIDE) {  // 4-byte reads: the chunk may start on any 4-byte boundary
 #pragma unroll
-            for (int u = 0; u < C::VW; ++u)
-              lds_words<4>(sb + C::kTmaV + tok * kVPitch + v_sub + g * C::VBY + 4 * u, vw[j] + u);
+            for (int u = 0; u < C::VW; ++u) lds_words<4>(vo + 4 * u, vw[j] + u);
           } else {
 #pragma unroll
-            for (int u = 0; u < C::NV; ++u)
-              lds_words<C::UV>(sb + C::kTmaV + tile_off(tok, g * C::VBY + u * C::UV), vw[j] + u * (C::UV / 4));
+            for (int u = 0; u < C::NV; ++u) lds_words<C::UV>(vo + u * C::UV, vw[j] + u * (C::UV / 4));
           }
         } else {
           const uint32_t vb = sb + C::kOffV + j * C::kVTok;
@@ -537,47 +549,43 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
 
     // ---- one pair of consecutive tiles (32 tokens) from ring stage st -----------------------------
     // okmask: bits 0-15 tile A, bits 16-31 tile B; has2 = tile B exists
+    // A missing tile B (odd tail of a segment) is still run through the arithmetic on whatever its
+    // ring slot holds: every byte decodes to a finite centroid, and its tokens are masked below.
     auto compute_pair = [&](int st, int pos0, uint32_t okmask, bool has2) {
       const uint32_t sbA = ring + st * (2 * kStage), sbB = sbA + kStage;
       float dots[2][NB][2];
       float nrm[2][4];
       k_side(sbA, dots[0]);
       load_norms(sbA, nrm[0]);
-      if (has2) {
-        k_side(sbB, dots[1]);
-        load_norms(sbB, nrm[1]);
-      }
-      // token slots of this lane: (tile u, half h) = position pos0 + 16u + g + 8h
-      float kn[2][2], vn[2][2], lg[2][2];
-      bool ok[2][2];
-      const int ntok = has2 ? 32 : 16;
-      const bool full = pos0 >= kv_start && pos0 + ntok <= kv_end &&
-                        okmask == (has2 ? 0xFFFFFFFFu : 0xFFFFu);
+      k_side(sbB, dots[1]);
+      load_norms(sbB, nrm[1]);
+      // token slots of this lane: (tile u, half h) = position pos0 + 16u + sigma(g) + 8h
+      float kn[2][2], vn[2][2], lg[2][2], bias[2][2];
 #pragma unroll
       for (int u = 0; u < 2; ++u)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           kn[u][h] = nrm[u][h];
           vn[u][h] = nrm[u][2 + h];
-          ok[u][h] = u == 0 || has2;
+          bias[u][h] = 0.f;
         }
-      if (!has2) vn[1][0] = vn[1][1] = kn[1][0] = kn[1][1] = 0.f;  // nothing was loaded for tile B
+      const bool full = has2 && pos0 >= kv_start && pos0 + 2 * kTileTokens <= kv_end &&
+                        okmask == 0xFFFFFFFFu;
       if (!full) {  // first / last tiles of a row, missing second tile, bad page: per-token masks
 #pragma unroll
         for (int u = 0; u < 2; ++u)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int pp = pos0 + 16 * u + rg + 8 * h;
-            ok[u][h] = (u == 0 || has2) && pp >= kv_start && pp < kv_end &&
-                       ((okmask >> (16 * u + rg + 8 * h)) & 1u);
-            if (!ok[u][h]) { vn[u][h] = 0.f; kn[u][h] = 0.f; }
+            const bool ok = (u == 0 || has2) && pp >= kv_start && pp < kv_end &&
+                            ((okmask >> (16 * u + rg + 8 * h)) & 1u);
+            if (!ok) { vn[u][h] = 0.f; kn[u][h] = 0.f; bias[u][h] = -CUDART_INF_F; }
           }
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u)
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-          lg[u][h] = ok[u][h] ? fmaxf(lg2_approx(vn[u][h]), -30.f) : -CUDART_INF_F;
+        for (int h = 0; h < 2; ++h) lg[u][h] = fmaxf(lg2_approx(vn[u][h]), -30.f);
       // Online softmax with a lazily updated reference: m only moves when some score (shifted by
       // log2 of its value norm) exceeds it by more than 2^8, so the cross-lane max reduction and
       // the accumulator rescale run a handful of times per row; probabilities stay below 2^8.
@@ -589,7 +597,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
         for (int u = 0; u < 2; ++u)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            s[nb][u][h] = ok[u][h] ? dots[u][nb][h] * (fscale[nb] * kn[u][h]) : -CUDART_INF_F;
+            s[nb][u][h] = fmaf(dots[u][nb][h], fscale[nb] * kn[u][h], bias[u][h]);  // masked: -inf
             need |= s[nb][u][h] + lg[u][h] > m[nb] + 8.f;
           }
       if (__any_sync(0xffffffffu, need)) {
@@ -624,12 +632,12 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
           for (int h = 0; h < 2; ++h) {
             const float e = ex2_approx(s[nb][u][h] - m_use);
             lsum += e;
-            if (u == 0 || has2) pf[u][nb][h] = movmatrix_trans(split_h2(e * vn[u][h]));
+            pf[u][nb][h] = movmatrix_trans(split_h2(e * vn[u][h]));
           }
         l[nb] += lsum;
       }
       v_side(sbA, pf[0]);
-      if (has2) v_side(sbB, pf[1]);
+      v_side(sbB, pf[1]);
     };
 
     // ---- stream the segment: kStages ring stages of one tile pair each; block ids one pair ahead ----
@@ -644,9 +652,28 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
         const bool two = ta + 1 < seg_end;
         const uint32_t sb = ring + (use % kStages) * (2 * kStage);
         const uint32_t bar = bar0 + (use % kStages) * 8;
-        if (TMA && lane == 0) mbar_expect_tx(bar, two ? 2 * kTmaStage : kTmaStage);
         uint32_t okb = issue_tile(ta, blk_a, sb, bar);
         if (two) okb |= issue_tile(ta + 1, blk_b, sb + kStage, bar) << 1;
+        if (TMA) {
+          // four box copies per tile by one elected lane: K rows, V rows, K-norm and V-norm columns
+          const int pos_a = pos0_of(ta);
+          const int in_a = bs_shift >= 0 ? (pos_a & (a.block_size - 1)) : (pos_a % a.block_size);
+          const int in_b = bs_shift >= 0 ? ((pos_a + kTileTokens) & (a.block_size - 1))
+                                         : ((pos_a + kTileTokens) % a.block_size);
+          if (elect_one()) {
+            mbar_expect_tx(bar, two ? 2 * kTmaStage : kTmaStage);
+            tma_load_3d(sb, &tm_data, x_k, in_a, blk_a, bar);
+            tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_a, blk_a, bar);
+            tma_load_3d(sb + kTmaKN, &tm_norm, x_kn, in_a, blk_a, bar);
+            tma_load_3d(sb + kTmaVN, &tm_norm, x_vn, in_a, blk_a, bar);
+            if (two) {
+              tma_load_3d(sb + kStage, &tm_data, x_k, in_b, blk_b, bar);
+              tma_load_3d(sb + kStage + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_b, blk_b, bar);
+              tma_load_3d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, blk_b, bar);
+              tma_load_3d(sb + kStage + kTmaVN, &tm_norm, x_vn, in_b, blk_b, bar);
+            }
+          }
+        }
         if (!TMA) cp_async_commit();
         return okb;
       };
