@@ -165,6 +165,25 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            int w, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
+// shared-memory loads at base + compile-time offset (the offset lands in the instruction)
+template <int BYTES, int IMM>
+__device__ __forceinline__ void lds_imm(uint32_t base, uint32_t* out) {
+  if (BYTES == 16)
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3]) : "r"(base), "n"(IMM));
+  else if (BYTES == 8)
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2+%3];" : "=r"(out[0]), "=r"(out[1]) : "r"(base), "n"(IMM));
+  else
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(out[0]) : "r"(base), "n"(IMM));
+}
+
 template <int D, bool ALIGNED>
 struct MmaCfg {
   static constexpr int HALF = D / 2;
@@ -202,13 +221,18 @@ __device__ __forceinline__ int v_byte_of_mblock(int g, int i) {
   return i < 4 * VW ? g * 4 * VW + i : 32 * VW + 2 * g + (i - 4 * VW);
 }
 
-template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS, bool TMA, bool VWIDE>
+// BOX selects the TMA box scheme: 0 = four 3-D boxes per tile (K rows, V rows, K norms, V norms),
+// 1 = the same with a 16-byte wider V box (V region not 16-byte aligned), 2 = two 4-D boxes per
+// tile: the K and V halves of a token row have the same shape a fixed distance apart, so one box
+// with an extra "half" dimension fetches both index tiles, and one both norm tiles.
+template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS, bool TMA, int BOX>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
                      const __grid_constant__ CUtensorMap tm_data,
                      const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_norm) {
   using C = MmaCfg<D, ALIGNED>;
+  constexpr bool VWIDE = BOX == 1, MERGED = BOX == 2;
   constexpr int kTmaKN = C::template tma_kn<VWIDE>(), kTmaVN = kTmaKN + 256;
   constexpr int kTmaStage = C::template tma_stage<VWIDE>(), kVPitch = C::template v_pitch<VWIDE>();
   constexpr int kStage = TMA ? kTmaStage : C::kStageBytes;
@@ -448,9 +472,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
 #pragma unroll
         for (int u = 0; u < C::NK; ++u) {
           // (a 16-byte chunk never straddles a swizzle unit: c * KBY + u * UK is a multiple of UK)
-          const uint32_t ku = o_k + u * C::UK;
-          lds_words<C::UK>(sb + ku, kw0 + u * (C::UK / 4));
-          lds_words<C::UK>(sb + ku + kRow8, kw1 + u * (C::UK / 4));
+          lds_imm<C::UK, 0>(sb + o_k + u * C::UK, kw0 + u * (C::UK / 4));
+          lds_imm<C::UK, kRow8>(sb + o_k + u * C::UK, kw1 + u * (C::UK / 4));
         }
       } else {
 #pragma unroll
@@ -490,10 +513,15 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     };
     auto load_norms = [&](uint32_t sb, float (&nrm)[4]) {  // kn(g), kn(g+8), vn(g), vn(g+8)
       if (TMA) {
-        lds_words<4>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm));
-        lds_words<4>(sb + o_kn + 128, reinterpret_cast<uint32_t*>(nrm + 1));
-        lds_words<4>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 2));
-        lds_words<4>(sb + o_vn + 128, reinterpret_cast<uint32_t*>(nrm + 3));
+        lds_imm<4, 0>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm));
+        lds_imm<4, 128>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 1));
+        if (VWIDE) {  // the two norm regions may sit at different offsets inside their 16-byte columns
+          lds_imm<4, 0>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 2));
+          lds_imm<4, 128>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 3));
+        } else {
+          lds_imm<4, 256>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 2));
+          lds_imm<4, 384>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 3));
+        }
       } else {
         lds_words<16>(sb + C::kOffN + lane * 16, reinterpret_cast<uint32_t*>(nrm));
       }
@@ -504,13 +532,19 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (TMA) {
-          const uint32_t vo = sb + ((j & 1) ? o_v1 : o_v0) + (j >> 1) * kVRow8;
+          const uint32_t vo = sb + ((j & 1) ? o_v1 : o_v0);
           if (VWIDE) {  // 4-byte reads: the chunk may start on any 4-byte boundary
 #pragma unroll
-            for (int u = 0; u < C::VW; ++u) lds_words<4>(vo + 4 * u, vw[j] + u);
+            for (int u = 0; u < C::VW; ++u) {
+              if (j < 2) lds_imm<4, 0>(vo + 4 * u, vw[j] + u);
+              else lds_imm<4, kVRow8>(vo + 4 * u, vw[j] + u);
+            }
           } else {
 #pragma unroll
-            for (int u = 0; u < C::NV; ++u) lds_words<C::UV>(vo + u * C::UV, vw[j] + u * (C::UV / 4));
+            for (int u = 0; u < C::NV; ++u) {
+              if (j < 2) lds_imm<C::UV, 0>(vo + u * C::UV, vw[j] + u * (C::UV / 4));
+              else lds_imm<C::UV, kVRow8>(vo + u * C::UV, vw[j] + u * (C::UV / 4));
+            }
           }
         } else {
           const uint32_t vb = sb + C::kOffV + j * C::kVTok;
@@ -640,6 +674,85 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       v_side(sbB, pf[1]);
     };
 
+    // ---- stream the segment (TMA): two ring stages of one tile pair each ---------------------------
+    // Steady state per pair: one election issuing the next pair's boxes, two block-table reads
+    // for the pair after that, one bounded barrier wait, the arithmetic.  Positions advance by
+    // additions; block-table reads past the segment are clamped to its last tile (never issued).
+    if constexpr (TMA) {
+      static_assert(kStages == 2, "the TMA loop alternates between two stages");
+      const int step = 2 * sh.TPC;
+      const int first = t + 2 * ts;
+      const int n_pairs = (first < seg_end && !dead) ? (seg_end - first + step - 1) / step : 0;
+      if (n_pairs > 0) {
+        const int step_tok = step * kTileTokens;
+        const int last_pos = pos0_of(seg_end - 1);  // first token of the segment's last tile
+        const uint32_t nblk = (uint32_t)a.num_blocks;
+        const int bs_mask = a.block_size - 1;  // power of two (checked by the host)
+        auto load_blk = [&](int pos) -> int { return __ldg(bt + (min(pos, last_pos) >> bs_shift)); };
+        auto issue = [&](uint32_t st, int pos, int ba, int bb) -> uint32_t {
+          const bool two = pos + kTileTokens <= last_pos;
+          uint32_t okm = 0xFFFFFFFFu;
+          if ((uint32_t)ba >= nblk || (two && (uint32_t)bb >= nblk)) {  // rare: report, mask the tile
+            okm = ((uint32_t)ba < nblk ? 0xFFFFu : 0u) | ((uint32_t)bb < nblk ? 0xFFFF0000u : 0u);
+            if (a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+          }
+          const uint32_t sb = ring + st * (2 * kStage), bar = bar0 + st * 8;
+          const int in_a = pos & bs_mask, in_b = (pos + kTileTokens) & bs_mask;
+          if (elect_one()) {
+            mbar_expect_tx(bar, two ? 2 * kTmaStage : kTmaStage);
+            if (MERGED) {
+              tma_load_4d(sb, &tm_data, x_k, in_a, 0, ba, bar);
+              tma_load_4d(sb + kTmaKN, &tm_norm, x_kn, in_a, 0, ba, bar);
+              if (two) {
+                tma_load_4d(sb + kStage, &tm_data, x_k, in_b, 0, bb, bar);
+                tma_load_4d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, 0, bb, bar);
+              }
+            } else {
+              tma_load_3d(sb, &tm_data, x_k, in_a, ba, bar);
+              tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_a, ba, bar);
+              tma_load_3d(sb + kTmaKN, &tm_norm, x_kn, in_a, ba, bar);
+              tma_load_3d(sb + kTmaVN, &tm_norm, x_vn, in_a, ba, bar);
+              if (two) {
+                tma_load_3d(sb + kStage, &tm_data, x_k, in_b, bb, bar);
+                tma_load_3d(sb + kStage + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_b, bb, bar);
+                tma_load_3d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, bb, bar);
+                tma_load_3d(sb + kStage + kTmaVN, &tm_norm, x_vn, in_b, bb, bar);
+              }
+            }
+          }
+          return okm;
+        };
+        uint32_t st = gk & 1u, ph = (gk >> 1) & 1u;  // stage and barrier parity of the current pair
+        int pos_i = pos0_of(first), pos_c = pos_i;
+        int blk_a = load_blk(pos_i), blk_b = load_blk(pos_i + kTileTokens);
+        __syncwarp();
+        uint32_t ok_cur = issue(st, pos_i, blk_a, blk_b);
+        pos_i += step_tok;
+        blk_a = load_blk(pos_i);
+        blk_b = load_blk(pos_i + kTileTokens);
+        for (int k = 0; k < n_pairs; ++k) {
+          __syncwarp();  // every lane has finished reading the stage about to be refilled
+          uint32_t ok_next = 0xFFFFFFFFu;
+          if (k + 1 < n_pairs) {
+            ok_next = issue(st ^ 1u, pos_i, blk_a, blk_b);
+            pos_i += step_tok;
+            blk_a = load_blk(pos_i);
+            blk_b = load_blk(pos_i + kTileTokens);
+          }
+          if (!mbar_wait_bounded(bar0 + st * 8, ph)) {
+            if (lane == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
+            dead = true;
+            break;
+          }
+          compute_pair(st, pos_c, ok_cur, pos_c + kTileTokens <= last_pos);
+          pos_c += step_tok;
+          ok_cur = ok_next;
+          ph ^= st;
+          st ^= 1u;
+        }
+        gk += n_pairs;
+      }
+    } else
     // ---- stream the segment: kStages ring stages of one tile pair each; block ids one pair ahead ----
     {
       const int step = 2 * sh.TPC;
@@ -792,14 +905,32 @@ bool make_cache_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes, bool 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D, int NB, bool ALIGNED, bool PAGE16, bool TMA, bool VWIDE>
+// 4-D map over the paged cache: dims (bytes of one half of a token row, tokens in a block, half, blocks).
+// The K half [K indices | K norms] and the V half of a row have the same shape, H * (D/2 + 4) bytes apart.
+bool make_cache_map_halves(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes, bool swizzle64) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t half_bytes = (cuuint64_t)a.sh.Hkv * (a.sh.D / 2 + 4);
+  const cuuint64_t dims[4] = {half_bytes, (cuuint64_t)a.block_size, 2, (cuuint64_t)a.num_blocks};
+  const cuuint64_t strides[3] = {(cuuint64_t)a.cache_token_stride, half_bytes, (cuuint64_t)a.cache_block_stride};
+  const cuuint32_t box[4] = {box_bytes, (cuuint32_t)kTileTokens, 2, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t*>(a.cache), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+constexpr int kErrNoHalvesMap = -1000;  // internal: the 4-D map could not be encoded, use 3-D boxes
+
+template <int D, int NB, bool ALIGNED, bool PAGE16, bool TMA, int BOX>
 int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
+  constexpr bool VWIDE = BOX == 1;
   constexpr int WARPS = (D * NB <= 128) ? 16 : 8;  // upper bound; the launch uses HPC * TPC warps
   using C = MmaCfg<D, ALIGNED>;
   // All opt-in shared memory of the SM (one CTA per SM by design): the 64 KB table sits on a
   // 64 KB boundary of the shared window and whole rings are packed on both sides of it.
   static int smem_total = 0;
-  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA, VWIDE>;
+  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA, BOX>;
   if (smem_total == 0) {
     int dev = 0, optin = 0;
     cudaGetDevice(&dev);
@@ -817,9 +948,13 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   memset(&tm_data, 0, sizeof(tm_data));
   memset(&tm_v, 0, sizeof(tm_v));
   memset(&tm_norm, 0, sizeof(tm_norm));
-  if (TMA && (!make_cache_map(&tm_data, a, D / 2, D == 128 && !VWIDE) ||
-              !make_cache_map(&tm_v, a, D / 2 + 16, false) || !make_cache_map(&tm_norm, a, 16, false)))
+  if (TMA && BOX == 2) {
+    if (!make_cache_map_halves(&tm_data, a, D / 2, D == 128) || !make_cache_map_halves(&tm_norm, a, 16, false))
+      return kErrNoHalvesMap;
+  } else if (TMA && (!make_cache_map(&tm_data, a, D / 2, D == 128 && !VWIDE) ||
+                     !make_cache_map(&tm_v, a, D / 2 + 16, false) || !make_cache_map(&tm_norm, a, 16, false))) {
     return TQ4_ERR_CUDA;
+  }
   const int warps = a.sh.HPC * a.sh.TPC;
   kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total, tm_data, tm_v, tm_norm);
   TQ4_CHECK_LAUNCH();
@@ -840,7 +975,8 @@ bool cache_aligned(const AttnShape& sh, const uint8_t* cache, int64_t bs, int64_
 // otherwise the V box is fetched 16 bytes wider from the boundary below (VWIDE).
 bool cache_tma_ok(const AttnArgs& a) {
   return (uintptr_t)a.cache % 16 == 0 && a.cache_block_stride % 16 == 0 && a.cache_token_stride % 16 == 0 &&
-         a.block_size % kTileTokens == 0 && a.block_size <= 256 && (a.sh.D / 2) % 16 == 0 &&
+         a.block_size % kTileTokens == 0 && a.block_size <= 256 &&
+         (a.block_size & (a.block_size - 1)) == 0 && (a.sh.D / 2) % 16 == 0 &&
          a.cache_token_stride >= (int64_t)((row_data_bytes(a.sh.Hkv, a.sh.D) + 15) & ~15) &&
          a.num_blocks < (1ll << 31) && getenv("TQ4_NO_TMA") == nullptr && encode_tiled_fn() != nullptr;
 }
@@ -854,8 +990,16 @@ int launch_mma_dn(const AttnArgs& a, cudaStream_t st) {
   const bool aligned = cache_aligned(a.sh, a.cache, a.cache_block_stride, a.cache_token_stride);
   const bool page16 = a.block_size % kTileTokens == 0;
   if (D != 96 && cache_tma_ok(a)) {
-    if (cache_v_aligned16(a)) return launch_mma_t<D, NB, true, true, (D != 96), false>(a, st);
-    return launch_mma_t<D, NB, true, true, (D != 96), (D != 96)>(a, st);
+    if (cache_v_aligned16(a)) {
+      static bool halves_ok = true;  // cleared if the driver refuses the 4-D map
+      if (halves_ok) {
+        const int rc = launch_mma_t<D, NB, true, true, (D != 96), (D != 96) ? 2 : 0>(a, st);
+        if (rc != kErrNoHalvesMap) return rc;
+        halves_ok = false;
+      }
+      return launch_mma_t<D, NB, true, true, (D != 96), 0>(a, st);
+    }
+    return launch_mma_t<D, NB, true, true, (D != 96), (D != 96) ? 1 : 0>(a, st);
   }
   if (aligned && page16) return launch_mma_t<D, NB, true, true, false, false>(a, st);
   if (aligned) return launch_mma_t<D, NB, true, false, false, false>(a, st);
