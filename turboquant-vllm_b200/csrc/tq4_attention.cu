@@ -635,6 +635,9 @@ int launch_combine_t(const CombineArgs& c, cudaStream_t st) {
     if (cudaFuncSetAttribute(combine_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return TQ4_ERR_CUDA;
+    // same shared-memory carve-out as the attention kernel it follows: no reconfiguration between them
+    cudaFuncSetAttribute(combine_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     attr_set = true;
   }
   const int64_t n_vec = (int64_t)c.rows * c.Hq;
@@ -662,6 +665,8 @@ int launch_qrot_plan_t(const AttnArgs& a, cudaStream_t st) {
     if (cudaFuncSetAttribute(qrot_plan_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)Q::smem_bytes) != cudaSuccess)
       return TQ4_ERR_CUDA;
+    cudaFuncSetAttribute(qrot_plan_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     attr_set = true;
   }
   const int64_t n_vec = (int64_t)a.sh.rows * a.sh.Hq;

@@ -265,10 +265,12 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   }
   __syncthreads();
   {
-    uint32_t* t = reinterpret_cast<uint32_t*>(smem_raw + (tab - base));
-    for (int i = threadIdx.x; i < 256 * 64; i += blockDim.x) {
-      const int byte = i >> 6, w = (i >> 5) & 1;
-      t[i] = pack_h2(s_cent[w][byte >> 4], s_cent[w][byte & 15]);
+    // the 32 lane copies of an entry are contiguous: four per 16-byte store
+    uint4* t = reinterpret_cast<uint4*>(smem_raw + (tab - base));
+    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
+      const int byte = i >> 4, w = (i >> 3) & 1;
+      const uint32_t v = pack_h2(s_cent[w][byte >> 4], s_cent[w][byte & 15]);
+      t[i] = make_uint4(v, v, v, v);
     }
   }
   if (TMA && lane == 0) {
@@ -281,10 +283,14 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
   const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
   // Row g of the score MMA / k-slot of the PV MMA does not hold token g of the tile but token
-  // sigma(g): the permutation makes every shared-memory read of the TMA tiles (16-byte K chunks by
-  // row pairs, 8-byte V chunks by four rows) touch rows of both parities, which together with the
-  // 64-byte TMA swizzle spreads each access over all 32 banks.
-  auto sigma = [](int k) { return (int)((0x63724150u >> (4 * (k & 7))) & 7u) + (k & 8); };  // 0,5,1,4,2,7,3,6
+  // sigma(g).  With the 64-byte TMA swizzle a tile row r starts in bank 16 * (r & 1) and its
+  // 16-byte chunks are XORed with (r >> 1) & 3, so
+  //  * the 16-byte K reads of a quarter warp (rows sigma(2p), sigma(2p+1), all four chunks) need
+  //    two rows of different parity, and
+  //  * the 8-byte V reads of a half warp (rows sigma(2c) or sigma(2c+1) for c = 0..3, chunks 0-1
+  //    or 2-3) need four rows that differ in (bit 0, bit 2),
+  // which this permutation provides: every shared-memory read of a tile is conflict-free.
+  auto sigma = [](int k) { return (int)((0x65742130u >> (4 * (k & 7))) & 7u) + (k & 8); };  // 0,3,1,2,4,7,5,6
   const int rg = sigma(g), rc0 = sigma(2 * c), rc1 = sigma(2 * c + 1);
   constexpr bool SWZ = TMA && D == 128 && !VWIDE;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
   // byte offsets of this head's K norm / V indices / V norm relative to the 16-byte boundary below
