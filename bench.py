@@ -36,7 +36,7 @@ SEED = 0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant (attention) kernel
 # on this workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 309.8e6  # 304.24 MB read + 5.56 MB written (N = 1 workload)
 
 
 def measured_peak_gbs():
@@ -217,7 +217,8 @@ def run_ours(args, rank, world, device):
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (avg["attention"] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "frac": round(achieved / peak, 4),
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if alg_bytes == 285212672 else None,
                 "kernel": "paged TQ4 attention (streaming) kernel", "peak_kind": f"of {peak_kind}",
                 "algorithmic_bytes_per_launch": alg_bytes,
                 "kernel_ms": {k: (round(v, 5) if v is not None else None) for k, v in avg.items()},
