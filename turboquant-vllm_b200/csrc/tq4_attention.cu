@@ -9,20 +9,25 @@ namespace tq4 {
 // ======================================================================================
 // 1. Prologue: q_rot = q * Pi^T for every (row, head), and (last block) the tile plan.
 // ======================================================================================
-__device__ void build_plan(const AttnArgs& a) {
-  // One block.  Per row: visible key range, tiles; then two exclusive scans.
+// One block.  Phase 1 (inputs only, results in shared memory): per row the visible key range and
+// its tile count, an exclusive scan of the tiles, the tiles per CTA, the partial slots per row and
+// their scan.  Phase 2, after the preceding kernel has completed: the stores into the plan arrays.
+// s_work: 2 * rows ints of dynamic shared memory.
+__device__ void build_plan(const AttnArgs& a, int* s_work) {
   const AttnShape& sh = a.sh;
   const AttnPlan& p = a.plan;
   __shared__ int s_part[1024];
   __shared__ int s_total;
   const int rows = sh.rows;
+  int* s_tiles = s_work;        // [rows] tile count, then exclusive prefix
+  int* s_slots = s_work + rows; // [rows] slot count, then exclusive prefix
   const int per = (rows + blockDim.x - 1) / blockDim.x;
   const int r_lo = min(rows, (int)threadIdx.x * per), r_hi = min(rows, r_lo + per);
 
-  int local = 0;
-  for (int r = r_lo; r < r_hi; ++r) {
+  auto row_range = [&](int r, int& seq, int& start, int& end) {
     const int gr = r + sh.row_offset;
-    int seq, start = 0, end = 0;
+    start = 0;
+    end = 0;
     if (a.query_start_loc == nullptr) {
       seq = gr;
       if (seq < sh.num_seqs) {
@@ -52,13 +57,7 @@ __device__ void build_plan(const AttnArgs& a) {
         seq = 0;
       }
     }
-    p.kv_start[r] = start;
-    p.kv_end[r] = end;
-    p.row_seq[r] = seq;
-    const int nt = end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
-    p.tile_prefix[r] = nt;  // raw count for now
-    local += nt;
-  }
+  };
   auto block_exclusive_scan = [&](int mine) -> int {
     s_part[threadIdx.x] = mine;
     __syncthreads();
@@ -76,36 +75,53 @@ __device__ void build_plan(const AttnArgs& a) {
     __syncthreads();
     return base;
   };
+
+  int local = 0;
+  for (int r = r_lo; r < r_hi; ++r) {
+    int seq, start, end;
+    row_range(r, seq, start, end);
+    const int nt = end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
+    s_tiles[r] = nt;
+    local += nt;
+  }
   int run = block_exclusive_scan(local);
   for (int r = r_lo; r < r_hi; ++r) {
-    const int nt = p.tile_prefix[r];
-    p.tile_prefix[r] = run;
+    const int nt = s_tiles[r];
+    s_tiles[r] = run;
     run += nt;
   }
   const int total = s_total;
   const int tps = max(1, (total + sh.ctas - 1) / sh.ctas);
-  if (threadIdx.x == 0) {
-    p.tile_prefix[rows] = total;
-    p.scalars[0] = total;
-    p.scalars[1] = tps;
-  }
   __syncthreads();
   local = 0;
   for (int r = r_lo; r < r_hi; ++r) {
-    const int b = p.tile_prefix[r];
-    const int e = p.tile_prefix[r + 1];
+    const int b = s_tiles[r];
+    const int e = r + 1 < rows ? s_tiles[r + 1] : total;
     const int n = e > b ? (e - 1) / tps - b / tps + 1 : 0;
-    p.slot_base[r] = n;
+    s_slots[r] = n;
     local += n;
   }
   __syncthreads();
   run = block_exclusive_scan(local);
+  const int total_slots = s_total;
+
+  pdl_wait();
   for (int r = r_lo; r < r_hi; ++r) {
-    const int n = p.slot_base[r];
+    int seq, start, end;
+    row_range(r, seq, start, end);
+    p.kv_start[r] = start;
+    p.kv_end[r] = end;
+    p.row_seq[r] = seq;
+    p.tile_prefix[r] = s_tiles[r];
     p.slot_base[r] = run;
-    run += n;
+    run += s_slots[r];
   }
-  if (threadIdx.x == 0) p.slot_base[rows] = s_total;
+  if (threadIdx.x == 0) {
+    p.tile_prefix[rows] = total;
+    p.scalars[0] = total;
+    p.scalars[1] = tps;
+    p.slot_base[rows] = total_slots;
+  }
 }
 
 template <int D>
@@ -115,7 +131,9 @@ struct QrotCfg {
   static constexpr int VPG = 4;                         // vectors per group (small: many blocks)
   static constexpr int VB = G * VPG;                    // (row, head) vectors per block
   static constexpr int THREADS = G * D;
-  static constexpr size_t smem_bytes = ((size_t)D * (DC + 1) + (size_t)D * VB) * sizeof(float);
+  static constexpr size_t rot_bytes = ((size_t)D * (DC + 1) + (size_t)D * VB) * sizeof(float);
+  static constexpr size_t plan_bytes = 2 * (size_t)kMaxRowsPerLaunch * sizeof(int);  // planning block
+  static constexpr size_t smem_bytes = rot_bytes > plan_bytes ? rot_bytes : plan_bytes;
 };
 
 // q_rot[v][j] = sum_d q[v][d] * Pi[j][d].  Pi is staged once per block, transposed into a padded
@@ -124,12 +142,13 @@ struct QrotCfg {
 template <int D>
 __global__ void __launch_bounds__(QrotCfg<D>::THREADS) qrot_plan_kernel(const AttnArgs a) {
   using Q = QrotCfg<D>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
   if (blockIdx.x == gridDim.x - 1) {  // the planning block
-    build_plan(a);
+    build_plan(a, reinterpret_cast<int*>(smem_raw));
     return;
   }
   constexpr int DC = Q::DC, VB = Q::VB, VPG = Q::VPG, PITCH = DC + 1;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
   float* s_pi = reinterpret_cast<float*>(smem_raw);  // [D][DC + 1]
   float* s_q = s_pi + D * PITCH;                     // [D][VB], v swizzled by d
   const AttnShape& sh = a.sh;
@@ -204,6 +223,7 @@ __global__ void __launch_bounds__(QrotCfg<D>::THREADS) qrot_plan_kernel(const At
       }
     }
   }
+  pdl_wait();  // the scratch may still be read by the attention kernel of the previous call
 #pragma unroll
   for (int v = 0; v < VPG; ++v) {
     const int64_t vec = v0 + grp * VPG + v;
@@ -242,6 +262,8 @@ attention_fp32_kernel(const AttnArgs a) {
     lut_v[threadIdx.x] = threadIdx.x < a.n_v_centroids ? a.v_centroids[threadIdx.x] : 0.f;
   }
   __syncthreads();
+  pdl_trigger();
+  pdl_wait();  // plan, rotated queries and cache come from the preceding kernels
 
   const int c = blockIdx.x % sh.ctas, slice = blockIdx.x / sh.ctas;
   const int vh = slice * sh.HPC + warp % sh.HPC, ts = warp / sh.HPC;
@@ -426,7 +448,9 @@ int launch_fp32_t(const AttnArgs& a, cudaStream_t st) {
     attr_set = true;
   }
   const int warps = a.sh.HPC * a.sh.TPC;
-  attention_fp32_kernel<D, GC><<<a.sh.ctas * a.sh.n_slices, warps * 32, smem, st>>>(a);
+  if (launch_kernel(attention_fp32_kernel<D, GC>, dim3(a.sh.ctas * a.sh.n_slices), dim3(warps * 32), smem, st,
+                    true, a) != cudaSuccess)
+    return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
@@ -504,6 +528,7 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
                    "l"(a.rotation + (size_t)i * 4) : "memory");
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
+  pdl_wait();  // the partials and the plan come from the kernels before this one
   const bool sparse = a.slot_base != nullptr;
   const float mscale = sparse ? 1.f : kLog2e;  // dense partials carry a natural-log LSE
   if (d < kCombHeads) {
@@ -641,7 +666,9 @@ int launch_combine_t(const CombineArgs& c, cudaStream_t st) {
     attr_set = true;
   }
   const int64_t n_vec = (int64_t)c.rows * c.Hq;
-  combine_kernel<D><<<(unsigned)((n_vec + kCombHeads - 1) / kCombHeads), D, smem, st>>>(c);
+  if (launch_kernel(combine_kernel<D>, dim3((unsigned)((n_vec + kCombHeads - 1) / kCombHeads)), dim3(D), smem,
+                    st, true, c) != cudaSuccess)
+    return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
@@ -671,7 +698,9 @@ int launch_qrot_plan_t(const AttnArgs& a, cudaStream_t st) {
   }
   const int64_t n_vec = (int64_t)a.sh.rows * a.sh.Hq;
   const unsigned grid = (unsigned)((n_vec + Q::VB - 1) / Q::VB) + 1;
-  qrot_plan_kernel<D><<<grid, Q::THREADS, Q::smem_bytes, st>>>(a);
+  if (launch_kernel(qrot_plan_kernel<D>, dim3(grid), dim3(Q::THREADS), Q::smem_bytes, st, true, a) !=
+      cudaSuccess)
+    return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }

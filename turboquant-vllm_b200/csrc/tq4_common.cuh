@@ -23,6 +23,36 @@ namespace tq4 {
 void prof_begin(int kind, cudaStream_t st);
 void prof_end(int kind, cudaStream_t st);
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// The kernels of one decode step (cache write, query rotation + plan, attention, merge) are launched
+// back to back.  A kernel that calls pdl_trigger() lets the next launch in the stream start before it
+// has finished, if that launch was made with launch_kernel(..., pdl = true); the dependent kernel
+// calls pdl_wait() before it reads or writes anything a predecessor touches: after the wait, the
+// preceding kernel has completed and its stores are visible.  Rules kept by every kernel here:
+//  * before pdl_wait() a kernel only reads caller inputs (q, centroids, Pi, seq_lens) and writes
+//    shared memory or registers;
+//  * a kernel launched with pdl = true calls pdl_wait() on every path before it exits, so its own
+//    completion implies the completion of everything before it in the stream.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool pdl_enabled();  // false if TQ4_NO_PDL is set in the environment
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t st, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __host__ __device__ inline bool supported_head_dim(int d) {
   return d == 64 || d == 96 || d == 128 || d == 256;
 }

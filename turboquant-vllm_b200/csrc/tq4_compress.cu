@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(128) compress_small_kernel(const CompressArgs 
   constexpr int HALF = Cfg::HALF, NBL = Cfg::NBL, XPL = Cfg::XPL, KQ = D / 4;
   __shared__ float s_x[D];
   __shared__ float s_part[3][2 * NBL][32];
+  pdl_trigger();  // the query-rotation kernel that follows in a decode step does not depend on this one
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = blockIdx.x;
   const int64_t rows_per_src = a.n_tokens * a.num_heads;

@@ -253,6 +253,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   const uint32_t ring =
       warp < (int)n_a ? base + warp * kRing : tab + kTableBytes + (warp - n_a) * kRing;
   if (tab + kTableBytes > end || ring + kRing > end) {  // the host sized smem_total to fit
+    pdl_wait();
     if (threadIdx.x == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
     return;
   }
@@ -280,6 +281,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  // everything above used only caller inputs and shared memory; from here on the kernel reads the
+  // plan, the rotated queries and the cache, which the preceding kernels produce
+  pdl_trigger();
+  pdl_wait();
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
   const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
   // Row g of the score MMA / k-slot of the PV MMA does not hold token g of the tile but token
@@ -962,7 +967,9 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     return TQ4_ERR_CUDA;
   }
   const int warps = a.sh.HPC * a.sh.TPC;
-  kern<<<a.sh.ctas * a.sh.n_slices, warps * 32, smem_total, st>>>(a, (uint32_t)smem_total, tm_data, tm_v, tm_norm);
+  if (launch_kernel(kern, dim3(a.sh.ctas * a.sh.n_slices), dim3(warps * 32), (size_t)smem_total, st, true, a,
+                    (uint32_t)smem_total, tm_data, tm_v, tm_norm) != cudaSuccess)
+    return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }

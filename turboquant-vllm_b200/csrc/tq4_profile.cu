@@ -1,5 +1,6 @@
 // Optional per-kernel timing: CUDA events recorded on the launching stream around each
 // kernel class, read back after the measured region.  Off by default (zero overhead).
+#include <cstdlib>
 #include <vector>
 
 #include "tq4_common.cuh"
@@ -22,6 +23,11 @@ void prof_end(int kind, cudaStream_t st) {
   if (!g_prof.on || g_prof.count[kind] >= g_prof.cap) return;
   cudaEventRecord(g_prof.ev[kind][1][g_prof.count[kind]], st);
   ++g_prof.count[kind];
+}
+
+bool pdl_enabled() {
+  static const bool on = getenv("TQ4_NO_PDL") == nullptr;
+  return on;
 }
 
 }  // namespace tq4
