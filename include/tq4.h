@@ -169,6 +169,40 @@ int tq4_paged_attention(const void* q, int q_dtype, int64_t num_rows, int num_se
                         int* err_flag, void* stream);
 
 /*
+ * One decode step of a layer: tq4_write_paged of the new tokens followed by tq4_paged_attention,
+ * with the cache write folded into the attention's first kernel (query rotation + tile plan), so
+ * the step costs three launches instead of four.  Arguments are the union of the two calls
+ * (same meaning and checks); the cache must be block-major contiguous
+ * (cache_block_stride == block_size * cache_token_stride), which makes the flat slot
+ * s = block * block_size + offset of slot_mapping address row s at cache + s * cache_token_stride.
+ * n_tokens == 0 reduces to tq4_paged_attention, num_rows == 0 to tq4_write_paged.  Writes of more
+ * than a few thousand vectors and head_dim 256 run the separate write kernel first.
+ * Replaces: the body of TQ4AttentionImpl.forward for a decode batch,
+ *           src/turboquant_vllm/vllm/tq4_backend.py (_compress_and_store + _fused_decode_path).
+ */
+int tq4_write_and_attention(const void* key, const void* value, int kv_dtype, int64_t n_tokens,
+                            int64_t k_token_stride, int64_t k_head_stride,
+                            int64_t v_token_stride, int64_t v_head_stride,
+                            const int64_t* slot_mapping, int64_t n_slots,
+                            const float* rot_t_even, const float* rot_t_odd,
+                            const float* k_boundaries, int n_k_boundaries,
+                            const float* v_boundaries, int n_v_boundaries,
+                            const void* q, int q_dtype, int64_t num_rows, int num_seqs,
+                            int num_q_heads, int num_kv_heads, int head_dim,
+                            int64_t q_token_stride, int64_t q_head_stride,
+                            uint8_t* cache, int64_t cache_block_stride, int64_t cache_token_stride,
+                            int64_t num_blocks, int block_size,
+                            const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* seq_lens, const int32_t* query_start_loc,
+                            const float* k_centroids, int n_k_centroids,
+                            const float* v_centroids, int n_v_centroids,
+                            const float* rotation, float sm_scale, int causal, int sliding_window,
+                            void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
+                            float* lse_out, int out_rotated,
+                            void* workspace, size_t workspace_bytes, int mode,
+                            int* err_flag, void* stream);
+
+/*
  * Merge `world` per-shard partial results of a sequence-split (split-KV) attention and
  * un-rotate: parts_o fp32 [world, num_rows, Hq, D] (each normalised, rotated space),
  * parts_lse fp32 [world, num_rows, Hq] (natural log; -inf = shard saw no key).

@@ -274,3 +274,44 @@ def test_decode_full_size_properties(ops, mode):
     for i in (0, 37):
         ref = O.paged_decode_fp32(q[i:i + 1].cpu(), cache.cpu(), bt[i:i + 1].cpu(), [ctx], pr.kc, pr.vc, pr.rot, h_kv)
         _check(out[i:i + 1], ref)
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("hq,hkv,d,bs,kbits,vbits,dtype", [
+    (32, 8, 128, 16, 4, 4, torch.bfloat16), (8, 2, 64, 32, 4, 3, torch.float16),
+    (12, 4, 96, 16, 4, 4, torch.float32), (8, 4, 256, 16, 4, 4, torch.bfloat16),
+])
+def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, vbits, dtype, mode):
+    """The fused step (cache write folded into the attention's first kernel) must leave the same
+    cache bytes and return the same output, bit for bit, as tq4_write_paged + attention."""
+    pr = Prims(d, kbits, vbits)
+    p = pr.cuda()
+    seq_lens = [70, 33, 129, 1, 16]
+    case = build_paged_case(seq_lens, hkv, d, bs, pr, seed=3 * hq + d, padded=True)
+    n = len(seq_lens)
+    gen = torch.Generator().manual_seed(9)
+    q = torch.randn(n, hq, d, generator=gen).to(dtype).cuda()
+    k_new = (torch.randn(n, hkv, d, generator=gen) * 2).to(dtype).cuda()
+    v_new = torch.randn(n, hkv, d, generator=gen).to(dtype).cuda()
+    # the new token of sequence i overwrites its last position (already counted in seq_lens)
+    bt = case["block_table"]
+    slots = torch.tensor([int(bt[i, (s - 1) // bs]) * bs + (s - 1) % bs for i, s in enumerate(seq_lens)])
+    slots[3] = -1  # a padding entry: skipped by both paths
+    common = dict(block_table=bt.cuda(), seq_lens=case["seq_lens"].cuda(), k_centroids=p["kc"],
+                  v_centroids=p["vc"], rotation=p["rot"], num_kv_heads=hkv, block_size=bs,
+                  out_dtype=torch.float32)
+    cache_a, cache_b = case["cache"].cuda(), case["cache"].cuda()
+    ops.tq4_write_paged(k_new, v_new, cache_a, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"])
+    out_a = _run(ops, mode, q=q, kv_cache=cache_a, **common)
+    out_b = _run(ops, mode, q=q, kv_cache=cache_b, **common,
+                 write=(k_new, v_new, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"]))
+    torch.cuda.synchronize()
+    assert torch.equal(cache_a, cache_b)
+    assert torch.equal(out_a, out_b)
+    assert not torch.equal(cache_a.cpu(), case["cache"])  # the write did change the cache
+    # and both agree with the oracle applied to the oracle-written cache
+    ref_cache = case["cache"].clone()
+    keep = slots >= 0
+    O.write_paged(k_new.cpu()[keep], v_new.cpu()[keep], ref_cache, slots[keep], pr.rot, pr.kb, pr.vb)
+    ref = O.paged_decode_fp32(q.cpu(), ref_cache, bt, seq_lens, pr.kc, pr.vc, pr.rot, hkv)
+    _check(out_b, ref)

@@ -231,6 +231,220 @@ __global__ void __launch_bounds__(QrotCfg<D>::THREADS) qrot_plan_kernel(const At
   }
 }
 
+// --------------------------------------------------------------------------------------
+// Fused prologue (head_dim <= 128): ONE launch rotates every query vector of the call and, when
+// the call carries new tokens, compresses their K and V vectors into the paged cache; an extra
+// block builds the tile plan.  Pi is staged once per block into shared memory ([j][d], padded
+// pitch) and reused by all vectors of the block; a group of D threads handles four vectors at a
+// time (thread j owns output coordinate j of each).
+//
+// The write part keeps the arithmetic contract of the compress kernels bit for bit
+// (tq4_compress.cu): squared norm by lane-strided FMAs + butterfly reduction, IEEE division by
+// (norm + 1e-10), four quarter-length FMA chains in ascending k combined as (s0 + s1) + (s2 + s3).
+// --------------------------------------------------------------------------------------
+template <int D>
+struct PrologueCfg {
+  static constexpr int G = 512 / D;       // thread groups per block
+  static constexpr int THREADS = G * D;
+  static constexpr int VC = 4;            // vectors per group per pass
+  static constexpr int PITCH = D + 1;
+  static constexpr size_t rot_bytes =
+      ((size_t)D * PITCH + (size_t)G * D * VC + (size_t)G * VC) * sizeof(float);
+  static constexpr size_t plan_bytes = 2 * (size_t)kMaxRowsPerLaunch * sizeof(int);
+  static constexpr size_t smem_bytes = rot_bytes > plan_bytes ? rot_bytes : plan_bytes;
+};
+
+template <int D>
+__global__ void __launch_bounds__(PrologueCfg<D>::THREADS)
+prologue_kernel(const AttnArgs a, const CompressArgs w, const int has_attn, const int has_write) {
+  using P = PrologueCfg<D>;
+  constexpr int G = P::G, VC = P::VC, PITCH = P::PITCH, HALF = D / 2, KQ = D / 4, XPL = D / 32;
+  static_assert(D % 32 == 0 && KQ % 8 == 0, "head_dim must be a multiple of 32");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_trigger();
+  if (has_attn && blockIdx.x == gridDim.x - 1) {  // the planning block
+    build_plan(a, reinterpret_cast<int*>(smem_raw));
+    return;
+  }
+  const int n_rot_blocks = (int)gridDim.x - (has_attn ? 1 : 0);
+  float* s_pi = reinterpret_cast<float*>(smem_raw);               // [D][D + 1]
+  float4* s_x = reinterpret_cast<float4*>(s_pi + D * PITCH);      // [G][D] four vectors per entry
+  float* s_nrm = reinterpret_cast<float*>(s_x + G * D);           // [G][VC]
+  const int tid = threadIdx.x, grp = tid / D, j = tid - grp * D;
+
+  // ---- stage Pi (rows = output coordinate) ---------------------------------------------------
+  if (has_attn) {
+    constexpr int N4 = D * D / 4;
+    for (int i0 = 0; i0 < N4; i0 += P::THREADS * 8) {
+      float4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * P::THREADS + tid;
+        if (i < N4) x[u] = __ldg(reinterpret_cast<const float4*>(a.rotation) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * P::THREADS + tid;
+        if (i < N4) {
+          const int jj = i / (D / 4), c4 = i - jj * (D / 4);
+          float* dst = s_pi + jj * PITCH + 4 * c4;
+          dst[0] = x[u].x; dst[1] = x[u].y; dst[2] = x[u].z; dst[3] = x[u].w;
+        }
+      }
+    }
+  } else {  // write only: the caller gave Pi^T split into even / odd output columns
+    for (int i = tid; i < D * HALF; i += P::THREADS) {
+      const int k = i / HALF, pp = i - k * HALF;
+      s_pi[(2 * pp) * PITCH + k] = __ldg(w.rot_even + i);
+      s_pi[(2 * pp + 1) * PITCH + k] = __ldg(w.rot_odd + i);
+    }
+  }
+  __syncthreads();
+
+  const int64_t n_q = has_attn ? (int64_t)a.sh.rows * a.sh.Hq : 0;
+  const int64_t rows_per_src = has_write ? w.n_tokens * w.num_heads : 0;
+  const int64_t n_w = rows_per_src * (has_write ? w.n_sources : 0);
+  const int64_t cq = (n_q + VC - 1) / VC, cw = (n_w + VC - 1) / VC;
+  auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(D) : "memory"); };
+  float4* gx = s_x + grp * D;
+  const float* prow = s_pi + j * PITCH;
+
+  for (int64_t c = (int64_t)blockIdx.x * G + grp; c < cq + cw; c += (int64_t)n_rot_blocks * G) {
+    const bool is_w = c >= cq;
+    const int64_t v0 = (is_w ? c - cq : c) * VC;
+    const int64_t nv = is_w ? n_w : n_q;
+    float xr[VC];
+#pragma unroll
+    for (int v = 0; v < VC; ++v) {
+      const int64_t vec = v0 + v;
+      xr[v] = 0.f;
+      if (vec < nv) {
+        if (!is_w) {
+          const int64_t row = vec / a.sh.Hq + a.sh.row_offset;
+          const int h = (int)(vec % a.sh.Hq);
+          xr[v] = load_as_float(a.q, a.q_dtype, row * a.q_token_stride + h * a.q_head_stride + j);
+        } else {
+          const int src = (int)(vec / rows_per_src);
+          const int64_t rem = vec - (int64_t)src * rows_per_src;
+          const int64_t tok = rem / w.num_heads;
+          const int h = (int)(rem - tok * w.num_heads);
+          xr[v] = load_as_float(w.x[src], w.x_dtype,
+                                tok * w.token_stride[src] + (int64_t)h * w.head_stride[src] + j);
+        }
+      }
+    }
+    gx[j] = make_float4(xr[0], xr[1], xr[2], xr[3]);
+    group_sync();
+    if (is_w) {
+      const int wv = j >> 5, lane = j & 31;
+      for (int v = wv; v < VC; v += D / 32) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < XPL; ++i) {
+          const float xk = reinterpret_cast<const float*>(gx + lane + 32 * i)[v];
+          ss = fmaf(xk, xk, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_nrm[grp * VC + v] = sqrtf(ss);
+      }
+      group_sync();
+#pragma unroll
+      for (int v = 0; v < VC; ++v) xr[v] = xr[v] / (s_nrm[grp * VC + v] + 1e-10f);
+      gx[j] = make_float4(xr[0], xr[1], xr[2], xr[3]);
+      group_sync();
+    }
+    float acc[4][VC];
+#pragma unroll
+    for (int qq = 0; qq < 4; ++qq)
+#pragma unroll
+      for (int v = 0; v < VC; ++v) acc[qq][v] = 0.f;
+#pragma unroll
+    for (int qq = 0; qq < 4; ++qq) {
+#pragma unroll 8
+      for (int dd = 0; dd < KQ; ++dd) {
+        const int d = qq * KQ + dd;
+        const float pv = prow[d];
+        const float4 xv = gx[d];
+        acc[qq][0] = fmaf(xv.x, pv, acc[qq][0]);
+        acc[qq][1] = fmaf(xv.y, pv, acc[qq][1]);
+        acc[qq][2] = fmaf(xv.z, pv, acc[qq][2]);
+        acc[qq][3] = fmaf(xv.w, pv, acc[qq][3]);
+      }
+    }
+    float y[VC];
+#pragma unroll
+    for (int v = 0; v < VC; ++v) y[v] = (acc[0][v] + acc[1][v]) + (acc[2][v] + acc[3][v]);
+
+    pdl_wait();  // nothing before this point wrote global memory
+    if (!is_w) {
+#pragma unroll
+      for (int v = 0; v < VC; ++v)
+        if (v0 + v < nv) a.plan.q_rot[(v0 + v) * D + j] = y[v];
+    } else {
+      const RowLayout lay = row_layout(w.num_heads, D);
+#pragma unroll
+      for (int v = 0; v < VC; ++v) {
+        const int64_t vec = v0 + v;
+        if (vec >= nv) continue;  // uniform over the group
+        const int src = (int)(vec / rows_per_src);
+        const int64_t rem = vec - (int64_t)src * rows_per_src;
+        const int64_t tok = rem / w.num_heads;
+        const int h = (int)(rem - tok * w.num_heads);
+        const int idx = bucketize(y[v], w.bounds[src], w.n_bounds[src]);
+        const int lo = __shfl_down_sync(0xffffffffu, idx, 1);
+        uint8_t* dst_idx;
+        float* dst_norm;
+        if (w.cache != nullptr) {
+          if (tok >= w.n_slots) continue;
+          const int64_t slot = w.slot_mapping[tok];
+          if (slot < 0) continue;
+          if (slot >= w.num_cache_slots) {
+            if (j == 0 && w.err_flag) atomicOr(w.err_flag, TQ4_DEV_BAD_SLOT);
+            continue;
+          }
+          uint8_t* rowp = w.cache + slot * w.cache_token_stride;
+          dst_idx = rowp + (src == 0 ? lay.k_idx : lay.v_idx) + h * HALF;
+          dst_norm = reinterpret_cast<float*>(rowp + (src == 0 ? lay.k_norm : lay.v_norm) + h * 4);
+        } else {
+          dst_idx = w.packed_out + vec * HALF;
+          dst_norm = w.norms_out + vec;
+        }
+        if (!(j & 1)) dst_idx[j >> 1] = (uint8_t)((idx << 4) | lo);
+        if (j == 0) *dst_norm = s_nrm[grp * VC + v];
+      }
+    }
+    group_sync();  // the group's staging area is reused by its next pass
+  }
+  pdl_wait();
+}
+
+template <int D>
+int launch_prologue_t(const AttnArgs* a, const CompressArgs* w, cudaStream_t st) {
+  using P = PrologueCfg<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(prologue_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)P::smem_bytes) != cudaSuccess)
+      return TQ4_ERR_CUDA;
+    cudaFuncSetAttribute(prologue_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    attr_set = true;
+  }
+  const int64_t n_q = a ? (int64_t)a->sh.rows * a->sh.Hq : 0;
+  const int64_t n_w = w ? w->n_tokens * w->num_heads * w->n_sources : 0;
+  const int64_t chunks = (n_q + P::VC - 1) / P::VC + (n_w + P::VC - 1) / P::VC;
+  int64_t blocks = (chunks + P::G - 1) / P::G;
+  if (blocks > sm_count()) blocks = sm_count();
+  if (blocks < 1) blocks = 1;
+  static const AttnArgs no_attn{};
+  static const CompressArgs no_write{};
+  if (launch_kernel(prologue_kernel<D>, dim3((unsigned)blocks + (a ? 1 : 0)), dim3(P::THREADS), P::smem_bytes,
+                    st, true, a ? *a : no_attn, w ? *w : no_write, a ? 1 : 0, w ? 1 : 0) != cudaSuccess)
+    return TQ4_ERR_CUDA;
+  TQ4_CHECK_LAUNCH();
+  return TQ4_OK;
+}
+
 // ======================================================================================
 // 2. fp32 CUDA-core streaming kernel (any supported head_dim, any group size).
 // ======================================================================================
@@ -705,12 +919,21 @@ int launch_qrot_plan_t(const AttnArgs& a, cudaStream_t st) {
   return TQ4_OK;
 }
 
-int launch_qrot_plan(const AttnArgs& a, cudaStream_t st) {
-  switch (a.sh.D) {
-    case 64: return launch_qrot_plan_t<64>(a, st);
-    case 96: return launch_qrot_plan_t<96>(a, st);
-    case 128: return launch_qrot_plan_t<128>(a, st);
-    case 256: return launch_qrot_plan_t<256>(a, st);
+// Prologue of an attention call (a != nullptr) and / or cache write of a few new tokens
+// (w != nullptr) in one launch; head_dim 256 (Pi does not fit in shared memory) and large writes
+// use the separate kernels.
+int launch_prologue(const AttnArgs* a, const CompressArgs* w, int head_dim, cudaStream_t st) {
+  if (w && (head_dim > 128 || w->n_tokens * w->num_heads * w->n_sources > kSmallRows)) {
+    const int rc = dispatch_compress(*w, head_dim, w->x_dtype, st);
+    if (rc != TQ4_OK) return rc;
+    w = nullptr;
+  }
+  if (!a && !w) return TQ4_OK;
+  switch (head_dim) {
+    case 64: return launch_prologue_t<64>(a, w, st);
+    case 96: return launch_prologue_t<96>(a, w, st);
+    case 128: return launch_prologue_t<128>(a, w, st);
+    case 256: return launch_qrot_plan_t<256>(*a, st);
   }
   return TQ4_ERR_UNSUPPORTED;
 }
@@ -748,7 +971,10 @@ extern "C" size_t tq4_attention_workspace_bytes(int64_t max_query_rows, int num_
   return a > b ? a : b;
 }
 
-extern "C" int tq4_paged_attention(
+// Shared body of tq4_paged_attention and tq4_write_and_attention: `wr` (optional) is a cache write
+// of new tokens that must land before the attention reads the cache.
+static int attention_impl(
+    const tq4::CompressArgs* wr,
     const void* q, int q_dtype, int64_t num_rows, int num_seqs, int num_q_heads, int num_kv_heads,
     int head_dim, int64_t q_token_stride, int64_t q_head_stride, const uint8_t* cache,
     int64_t cache_block_stride, int64_t cache_token_stride, int64_t num_blocks, int block_size,
@@ -767,7 +993,7 @@ extern "C" int tq4_paged_attention(
     return TQ4_ERR_UNSUPPORTED;
   AttnArgs a{};
   if (!make_shape(a.sh, num_q_heads, num_kv_heads, head_dim)) return TQ4_ERR_UNSUPPORTED;
-  if (num_rows == 0) return TQ4_OK;
+  if (num_rows == 0) return wr ? launch_prologue(nullptr, wr, head_dim, (cudaStream_t)stream) : TQ4_OK;
   if (!q || !cache || !block_table || !seq_lens || !k_centroids || !v_centroids || !rotation ||
       !out || !workspace)
     return TQ4_ERR_INVALID_ARG;
@@ -830,7 +1056,7 @@ extern "C" int tq4_paged_attention(
     a.sh.rows = (int)((num_rows - r0) < kMaxRowsPerLaunch ? (num_rows - r0) : kMaxRowsPerLaunch);
     a.sh.row_offset = (int)r0;
     prof_begin(TQ4_PROF_PROLOGUE, st);
-    int rc = launch_qrot_plan(a, st);
+    int rc = launch_prologue(&a, r0 == 0 ? wr : nullptr, head_dim, st);
     prof_end(TQ4_PROF_PROLOGUE, st);
     if (rc != TQ4_OK) return rc;
     prof_begin(TQ4_PROF_ATTENTION, st);
@@ -859,6 +1085,88 @@ extern "C" int tq4_paged_attention(
     if (rc != TQ4_OK) return rc;
   }
   return TQ4_OK;
+}
+
+extern "C" int tq4_paged_attention(
+    const void* q, int q_dtype, int64_t num_rows, int num_seqs, int num_q_heads, int num_kv_heads,
+    int head_dim, int64_t q_token_stride, int64_t q_head_stride, const uint8_t* cache,
+    int64_t cache_block_stride, int64_t cache_token_stride, int64_t num_blocks, int block_size,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+    const int32_t* query_start_loc, const float* k_centroids, int n_k_centroids,
+    const float* v_centroids, int n_v_centroids, const float* rotation, float sm_scale, int causal,
+    int sliding_window, void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
+    float* lse_out, int out_rotated, void* workspace, size_t workspace_bytes, int mode,
+    int* err_flag, void* stream) {
+  return attention_impl(nullptr, q, q_dtype, num_rows, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                        q_token_stride, q_head_stride, cache, cache_block_stride, cache_token_stride,
+                        num_blocks, block_size, block_table, bt_stride, seq_lens, query_start_loc,
+                        k_centroids, n_k_centroids, v_centroids, n_v_centroids, rotation, sm_scale,
+                        causal, sliding_window, out, out_dtype, out_token_stride, out_head_stride,
+                        lse_out, out_rotated, workspace, workspace_bytes, mode, err_flag, stream);
+}
+
+extern "C" int tq4_write_and_attention(
+    const void* key, const void* value, int kv_dtype, int64_t n_tokens, int64_t k_token_stride,
+    int64_t k_head_stride, int64_t v_token_stride, int64_t v_head_stride,
+    const int64_t* slot_mapping, int64_t n_slots, const float* rot_t_even, const float* rot_t_odd,
+    const float* k_boundaries, int n_k_boundaries, const float* v_boundaries, int n_v_boundaries,
+    const void* q, int q_dtype, int64_t num_rows, int num_seqs, int num_q_heads, int num_kv_heads,
+    int head_dim, int64_t q_token_stride, int64_t q_head_stride, uint8_t* cache,
+    int64_t cache_block_stride, int64_t cache_token_stride, int64_t num_blocks, int block_size,
+    const int32_t* block_table, int64_t bt_stride, const int32_t* seq_lens,
+    const int32_t* query_start_loc, const float* k_centroids, int n_k_centroids,
+    const float* v_centroids, int n_v_centroids, const float* rotation, float sm_scale, int causal,
+    int sliding_window, void* out, int out_dtype, int64_t out_token_stride, int64_t out_head_stride,
+    float* lse_out, int out_rotated, void* workspace, size_t workspace_bytes, int mode,
+    int* err_flag, void* stream) {
+  using namespace tq4;
+  if (n_tokens < 0 || n_slots < 0 || num_kv_heads <= 0 || block_size <= 0 || num_blocks < 0)
+    return TQ4_ERR_INVALID_ARG;
+  if (!supported_head_dim(head_dim) || kv_dtype < 0 || kv_dtype > 2) return TQ4_ERR_UNSUPPORTED;
+  if (n_k_boundaries < 0 || n_k_boundaries > TQ4_MAX_BOUNDARIES || n_v_boundaries < 0 ||
+      n_v_boundaries > TQ4_MAX_BOUNDARIES)
+    return TQ4_ERR_UNSUPPORTED;
+  CompressArgs w{};
+  const CompressArgs* wr = nullptr;
+  if (n_tokens > 0 && n_slots > 0) {
+    if (!key || !value || !slot_mapping || !rot_t_even || !rot_t_odd || !k_boundaries || !v_boundaries ||
+        !cache)
+      return TQ4_ERR_INVALID_ARG;
+    if (((uintptr_t)rot_t_even | (uintptr_t)rot_t_odd) & 15) return TQ4_ERR_INVALID_ARG;
+    if (((uintptr_t)cache & 3) || (cache_token_stride & 3) ||
+        cache_token_stride < row_data_bytes(num_kv_heads, head_dim) ||
+        cache_block_stride != (int64_t)block_size * cache_token_stride)  // flat slots = block-major rows
+      return TQ4_ERR_INVALID_ARG;
+    w.x[0] = key;
+    w.x[1] = value;
+    w.token_stride[0] = k_token_stride;
+    w.head_stride[0] = k_head_stride;
+    w.token_stride[1] = v_token_stride;
+    w.head_stride[1] = v_head_stride;
+    w.bounds[0] = k_boundaries;
+    w.n_bounds[0] = n_k_boundaries;
+    w.bounds[1] = v_boundaries;
+    w.n_bounds[1] = n_v_boundaries;
+    w.n_tokens = n_tokens < n_slots ? n_tokens : n_slots;
+    w.num_heads = num_kv_heads;
+    w.n_sources = 2;
+    w.x_dtype = kv_dtype;
+    w.rot_even = rot_t_even;
+    w.rot_odd = rot_t_odd;
+    w.cache = cache;
+    w.slot_mapping = slot_mapping;
+    w.n_slots = n_slots;
+    w.cache_token_stride = cache_token_stride;
+    w.num_cache_slots = num_blocks * block_size;
+    w.err_flag = err_flag;
+    wr = &w;
+  }
+  return attention_impl(wr, q, q_dtype, num_rows, num_seqs, num_q_heads, num_kv_heads, head_dim,
+                        q_token_stride, q_head_stride, cache, cache_block_stride, cache_token_stride,
+                        num_blocks, block_size, block_table, bt_stride, seq_lens, query_start_loc,
+                        k_centroids, n_k_centroids, v_centroids, n_v_centroids, rotation, sm_scale,
+                        causal, sliding_window, out, out_dtype, out_token_stride, out_head_stride,
+                        lse_out, out_rotated, workspace, workspace_bytes, mode, err_flag, stream);
 }
 
 extern "C" int tq4_combine_partials(const float* parts_o, const float* parts_lse, int world,

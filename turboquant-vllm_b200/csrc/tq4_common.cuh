@@ -135,4 +135,32 @@ inline int sm_count() {
   return n;
 }
 
+// Arguments of the compress / cache-write kernels (tq4_compress.cu) and of the write part of the
+// fused prologue kernel (tq4_attention.cu).
+struct CompressArgs {
+  // sources: [0] = K (or the only tensor), [1] = V (paged write only)
+  const void* x[2];
+  int64_t token_stride[2], head_stride[2];
+  const float* bounds[2];
+  int n_bounds[2];
+  int64_t n_tokens;
+  int num_heads;
+  int n_sources;  // 1 or 2
+  int x_dtype;    // TQ4_F32 / TQ4_F16 / TQ4_BF16 of both sources (read by the fused prologue kernel)
+  const float* rot_even;
+  const float* rot_odd;
+  // contiguous destination
+  uint8_t* packed_out;
+  float* norms_out;
+  // paged destination (cache != nullptr selects it)
+  uint8_t* cache;
+  const int64_t* slot_mapping;
+  int64_t n_slots, cache_token_stride, num_cache_slots;
+  int* err_flag;
+};
+
+// rows at or below this count are handled by the small-launch kernels
+constexpr int64_t kSmallRows = 8192;
+int dispatch_compress(const CompressArgs& a, int head_dim, int dtype, cudaStream_t st);
+
 }  // namespace tq4

@@ -10,27 +10,6 @@
 
 namespace tq4 {
 
-struct CompressArgs {
-  // sources: [0] = K (or the only tensor), [1] = V (paged write only)
-  const void* x[2];
-  int64_t token_stride[2], head_stride[2];
-  const float* bounds[2];
-  int n_bounds[2];
-  int64_t n_tokens;
-  int num_heads;
-  int n_sources;  // 1 or 2
-  const float* rot_even;
-  const float* rot_odd;
-  // contiguous destination
-  uint8_t* packed_out;
-  float* norms_out;
-  // paged destination (cache != nullptr selects it)
-  uint8_t* cache;
-  const int64_t* slot_mapping;
-  int64_t n_slots, cache_token_stride, num_cache_slots;
-  int* err_flag;
-};
-
 constexpr int kWarps = 8;
 constexpr int kRowsPerWarp = 4;
 
@@ -323,7 +302,6 @@ __global__ void __launch_bounds__(128) compress_small_kernel(const CompressArgs 
   if (lane == 0) *dst_norm = norm;
 }
 
-constexpr int64_t kSmallRows = 8192;  // below this the one-warp-per-row kernel wins
 
 template <int D, typename T>
 int launch_compress(const CompressArgs& a, cudaStream_t st) {
@@ -409,6 +387,7 @@ extern "C" int tq4_compress_rows(const void* x, int x_dtype, int64_t n_tokens, i
   a.packed_out = packed_out;
   a.norms_out = norms_out;
   tq4::prof_begin(TQ4_PROF_COMPRESS, (cudaStream_t)stream);
+  a.x_dtype = x_dtype;
   const int rc = tq4::dispatch_compress(a, head_dim, x_dtype, (cudaStream_t)stream);
   tq4::prof_end(TQ4_PROF_COMPRESS, (cudaStream_t)stream);
   return rc;
@@ -474,6 +453,7 @@ extern "C" int tq4_write_paged(const void* key, const void* value, int kv_dtype,
   a.num_cache_slots = num_cache_slots;
   a.err_flag = err_flag;
   tq4::prof_begin(TQ4_PROF_WRITE, (cudaStream_t)stream);
+  a.x_dtype = kv_dtype;
   const int rc = tq4::dispatch_compress(a, head_dim, kv_dtype, (cudaStream_t)stream);
   tq4::prof_end(TQ4_PROF_WRITE, (cudaStream_t)stream);
   return rc;

@@ -43,6 +43,14 @@ _SIGNATURES = {
                                     c_void_p, c_int, c_void_p, c_float, c_int, c_int,
                                     c_void_p, c_int, c_int64, c_int64, c_void_p, c_int,
                                     c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
+    "tq4_write_and_attention": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                        c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,
+                                        c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                        c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_int, c_void_p, c_float, c_int, c_int,
+                                        c_void_p, c_int, c_int64, c_int64, c_void_p, c_int,
+                                        c_void_p, c_size_t, c_int, c_void_p, c_void_p]),
     "tq4_combine_partials": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                      c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "tq4_paged_attention_static": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int,

@@ -11,6 +11,7 @@ from turboquant_vllm.kernels.ops import (
     tq4_decompress,
     tq4_decompress_cache,
     tq4_pack_rotated,
+    tq4_write_and_attention,
     tq4_write_paged,
 )
 
@@ -25,5 +26,6 @@ __all__ = [
     "tq4_decompress",
     "tq4_decompress_cache",
     "tq4_pack_rotated",
+    "tq4_write_and_attention",
     "tq4_write_paged",
 ]

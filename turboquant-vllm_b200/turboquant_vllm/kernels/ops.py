@@ -240,8 +240,13 @@ def paged_tq4_attention(
     out_rotated: bool = False,
     workspace: torch.Tensor | None = None,
     mode: int = 0,
+    write: tuple | None = None,
 ) -> torch.Tensor:
     """Attention of ``q [T, Hq, D]`` over the packed paged cache.
+
+    ``write = (key, value, slot_mapping, rotation_T_even, rotation_T_odd, k_boundaries,
+    v_boundaries)``: first store these new tokens into the cache (as :func:`tq4_write_paged`),
+    folded into the attention's first kernel -- see :func:`tq4_write_and_attention`.
 
     ``query_start_loc=None``: decode, row i is the one new token of sequence i.  Otherwise
     int32 ``[num_seqs + 1]`` offsets of each sequence's query chunk (bottom-right aligned
@@ -273,7 +278,24 @@ def paged_tq4_attention(
     ws = workspace if workspace is not None else _workspace(q.device, need)
     if ws.numel() * ws.element_size() < need:
         raise ValueError(f"workspace has {ws.numel() * ws.element_size()} bytes, {need} needed")
-    st = nv.lib().tq4_paged_attention(
+    wargs: tuple = ()
+    if write is not None:
+        key, value, slot_mapping, rot_even, rot_odd, k_bounds, v_bounds = write
+        nv.require_cuda(key, value, slot_mapping, rot_even, rot_odd, k_bounds, v_bounds)
+        assert kv_cache.is_contiguous(), "the fused write addresses flat slots: block-major contiguous cache"
+        assert key.shape == value.shape and key.dtype == value.dtype and key.shape[1:] == (num_kv_heads, d)
+        key = _inner_contiguous(key)
+        value = _inner_contiguous(value)
+        if slot_mapping.dtype != torch.int64:
+            slot_mapping = slot_mapping.to(torch.int64)
+        slot_mapping = slot_mapping.contiguous()
+        wargs = (key.data_ptr(), value.data_ptr(), nv.dtype_code(key.dtype), key.shape[0],
+                 key.stride(0), key.stride(1), value.stride(0), value.stride(1),
+                 slot_mapping.data_ptr(), slot_mapping.numel(), rot_even.data_ptr(), rot_odd.data_ptr(),
+                 k_bounds.data_ptr(), k_bounds.numel(), v_bounds.data_ptr(), v_bounds.numel())
+    entry = nv.lib().tq4_write_and_attention if write is not None else nv.lib().tq4_paged_attention
+    st = entry(
+        *wargs,
         q.data_ptr(), nv.dtype_code(q.dtype), t, seq_lens.numel(), hq, num_kv_heads, d,
         q.stride(0), q.stride(1),
         kv_cache.data_ptr(), kv_cache.stride(0), kv_cache.stride(1), kv_cache.shape[0], block_size,
@@ -287,6 +309,36 @@ def paged_tq4_attention(
     )
     nv.check(st, "paged_tq4_attention")
     return out
+
+
+def tq4_write_and_attention(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    rotation_T_even: torch.Tensor,
+    rotation_T_odd: torch.Tensor,
+    k_boundaries: torch.Tensor,
+    v_boundaries: torch.Tensor,
+    q: torch.Tensor,
+    kv_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    k_centroids: torch.Tensor,
+    v_centroids: torch.Tensor,
+    rotation: torch.Tensor,
+    num_kv_heads: int,
+    block_size: int,
+    sm_scale: float | None = None,
+    **kwargs,
+) -> torch.Tensor:
+    """One decode step of a layer: :func:`tq4_write_paged` of the new tokens, then
+    :func:`paged_tq4_attention`, in three launches (the cache write rides in the kernel that rotates
+    the queries and plans the tiles).  Same results, bit for bit, as the two calls in sequence."""
+    return paged_tq4_attention(
+        q, kv_cache, block_table, seq_lens, k_centroids, v_centroids, rotation, num_kv_heads,
+        block_size, sm_scale,
+        write=(key, value, slot_mapping, rotation_T_even, rotation_T_odd, k_boundaries, v_boundaries),
+        **kwargs)
 
 
 def fused_paged_tq4_decode(
