@@ -169,11 +169,18 @@ def run_ours(args, rank, world, device):
     out = torch.empty(batch, hq, D, dtype=torch.bfloat16, device=device)
     ws = torch.empty(ops.attention_workspace_bytes(batch, hq, hkv, D), dtype=torch.uint8, device=device)
 
+    sm_scale = 1.0 / (D ** 0.5)
+
     def step(i, q_=q, k_=k_new, v_=v_new, slots_=wl["new_slots"], bt_=wl["block_table"], sl_=wl["seq_lens"]):
         cache = wl["caches"][i % args.layers]
-        ops.tq4_write_paged(k_, v_, cache, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"])
-        ops.fused_paged_tq4_decode(q_, cache, bt_, sl_, wl["kc"], wl["rot"], hkv, D, BS, None, out,
-                                   v_centroids=wl["vc"], workspace=ws, mode=args.mode)
+        if args.separate_write:
+            ops.tq4_write_paged(k_, v_, cache, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"])
+            ops.fused_paged_tq4_decode(q_, cache, bt_, sl_, wl["kc"], wl["rot"], hkv, D, BS, None, out,
+                                       v_centroids=wl["vc"], workspace=ws, mode=args.mode)
+        else:  # one call: the write rides in the attention's first kernel (3 launches)
+            ops.tq4_write_and_attention(k_, v_, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"],
+                                        q_, cache, bt_, sl_, wl["kc"], wl["vc"], wl["rot"], hkv, BS,
+                                        sm_scale, out=out, workspace=ws, mode=args.mode)
 
     def barrier():
         if world > 1:
@@ -321,7 +328,8 @@ def run_ours(args, rank, world, device):
         "hbm_gbs": round(alg_bytes / (ms_step * 1e-3) / 1e9, 1),
         "compress_mtok_s": round(compress_mtok_s, 3),
         "compress_config": f"{nt} tokens x {hkv} KV heads, K and V, bf16 -> paged cache, one launch",
-        "roofline": roofline, "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": (4 if args.separate_write else 3) * args.steps,
+        "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_bf16_baseline:
         del wl["caches"][1:]  # free HBM for the bf16 copies
@@ -494,6 +502,8 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bf16-baseline", action="store_true")
+    ap.add_argument("--separate-write", action="store_true",
+                    help="tq4_write_paged + attention as two calls (4 launches) instead of the fused step")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (no CUDA graph)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: run ONE rank's share of a W-GPU head-sharded job on this GPU")

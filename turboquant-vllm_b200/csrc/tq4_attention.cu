@@ -16,7 +16,7 @@ namespace tq4 {
 __device__ void build_plan(const AttnArgs& a, int* s_work) {
   const AttnShape& sh = a.sh;
   const AttnPlan& p = a.plan;
-  __shared__ int s_part[1024];
+  __shared__ int s_part[32];
   __shared__ int s_total;
   const int rows = sh.rows;
   int* s_tiles = s_work;        // [rows] tile count, then exclusive prefix
@@ -58,20 +58,31 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
       }
     }
   };
+  // exclusive scan over the block's threads (shuffle scan per warp + scan of the warp totals);
+  // s_total receives the sum
   auto block_exclusive_scan = [&](int mine) -> int {
-    s_part[threadIdx.x] = mine;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) s_part[wid] = incl;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int run = 0;
-      for (int i = 0; i < (int)blockDim.x; ++i) {
-        const int v = s_part[i];
-        s_part[i] = run;
-        run += v;
+    if (wid == 0) {
+      const int tot = lane < nw ? s_part[lane] : 0;
+      int winc = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += up;
       }
-      s_total = run;
+      if (lane < nw) s_part[lane] = winc - tot;  // exclusive warp offsets
+      if (lane == 31) s_total = winc;
     }
     __syncthreads();
-    const int base = s_part[threadIdx.x];
+    const int base = s_part[wid] + incl - mine;
     __syncthreads();
     return base;
   };
@@ -234,9 +245,10 @@ __global__ void __launch_bounds__(QrotCfg<D>::THREADS) qrot_plan_kernel(const At
 // --------------------------------------------------------------------------------------
 // Fused prologue (head_dim <= 128): ONE launch rotates every query vector of the call and, when
 // the call carries new tokens, compresses their K and V vectors into the paged cache; an extra
-// block builds the tile plan.  Pi is staged once per block into shared memory ([j][d], padded
-// pitch) and reused by all vectors of the block; a group of D threads handles four vectors at a
-// time (thread j owns output coordinate j of each).
+// block builds the tile plan.  Pi^T is staged once per block into shared memory ([d][j]); one WARP
+// handles four vectors at a time as a 4 x D strip of the product X * Pi^T, each lane a 4 x 4
+// register tile (four vectors x four consecutive output coordinates), so a step of the reduction
+// is two 16-byte shared loads and 16 FMAs, and nothing but warp-level synchronisation is needed.
 //
 // The write part keeps the arithmetic contract of the compress kernels bit for bit
 // (tq4_compress.cu): squared norm by lane-strided FMAs + butterfly reduction, IEEE division by
@@ -244,12 +256,10 @@ __global__ void __launch_bounds__(QrotCfg<D>::THREADS) qrot_plan_kernel(const At
 // --------------------------------------------------------------------------------------
 template <int D>
 struct PrologueCfg {
-  static constexpr int G = 512 / D;       // thread groups per block
-  static constexpr int THREADS = G * D;
-  static constexpr int VC = 4;            // vectors per group per pass
-  static constexpr int PITCH = D + 1;
-  static constexpr size_t rot_bytes =
-      ((size_t)D * PITCH + (size_t)G * D * VC + (size_t)G * VC) * sizeof(float);
+  static constexpr int WARPS = 8;
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int VC = 4;            // vectors per warp per pass
+  static constexpr size_t rot_bytes = ((size_t)D * D + (size_t)WARPS * D * VC) * sizeof(float);
   static constexpr size_t plan_bytes = 2 * (size_t)kMaxRowsPerLaunch * sizeof(int);
   static constexpr size_t smem_bytes = rot_bytes > plan_bytes ? rot_bytes : plan_bytes;
 };
@@ -258,8 +268,8 @@ template <int D>
 __global__ void __launch_bounds__(PrologueCfg<D>::THREADS)
 prologue_kernel(const AttnArgs a, const CompressArgs w, const int has_attn, const int has_write) {
   using P = PrologueCfg<D>;
-  constexpr int G = P::G, VC = P::VC, PITCH = P::PITCH, HALF = D / 2, KQ = D / 4, XPL = D / 32;
-  static_assert(D % 32 == 0 && KQ % 8 == 0, "head_dim must be a multiple of 32");
+  constexpr int VC = P::VC, HALF = D / 2, KQ = D / 4, XPL = D / 32;
+  static_assert(D % 32 == 0 && D <= 128 && KQ % 8 == 0, "head_dim must be a multiple of 32, at most 128");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_trigger();
   if (has_attn && blockIdx.x == gridDim.x - 1) {  // the planning block
@@ -267,131 +277,161 @@ prologue_kernel(const AttnArgs a, const CompressArgs w, const int has_attn, cons
     return;
   }
   const int n_rot_blocks = (int)gridDim.x - (has_attn ? 1 : 0);
-  float* s_pi = reinterpret_cast<float*>(smem_raw);               // [D][D + 1]
-  float4* s_x = reinterpret_cast<float4*>(s_pi + D * PITCH);      // [G][D] four vectors per entry
-  float* s_nrm = reinterpret_cast<float*>(s_x + G * D);           // [G][VC]
-  const int tid = threadIdx.x, grp = tid / D, j = tid - grp * D;
+  float* s_pit = reinterpret_cast<float*>(smem_raw);                    // [D][D]: s_pit[d][j] = Pi[j][d]
+  float4* s_x = reinterpret_cast<float4*>(s_pit + D * D);               // [WARPS][D] four vectors per entry
+  __shared__ float s_bounds[2][16];  // sorted boundaries of K and V, padded with +inf
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (has_write && tid < 32) {
+    const int src = tid >> 4, i = tid & 15;
+    s_bounds[src][i] = (src < w.n_sources && i < w.n_bounds[src]) ? w.bounds[src][i] : CUDART_INF_F;
+  }
 
-  // ---- stage Pi (rows = output coordinate) ---------------------------------------------------
+  // ---- stage Pi^T ------------------------------------------------------------------------------
   if (has_attn) {
+    // thread -> (4 consecutive d of row j), consecutive threads = consecutive j: conflict-free stores
     constexpr int N4 = D * D / 4;
     for (int i0 = 0; i0 < N4; i0 += P::THREADS * 8) {
       float4 x[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int i = i0 + u * P::THREADS + tid;
-        if (i < N4) x[u] = __ldg(reinterpret_cast<const float4*>(a.rotation) + i);
+        const int c4 = i / D, jj = i - c4 * D;
+        if (i < N4) x[u] = __ldg(reinterpret_cast<const float4*>(a.rotation + (size_t)jj * D) + c4);
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int i = i0 + u * P::THREADS + tid;
+        const int c4 = i / D, jj = i - c4 * D;
         if (i < N4) {
-          const int jj = i / (D / 4), c4 = i - jj * (D / 4);
-          float* dst = s_pi + jj * PITCH + 4 * c4;
-          dst[0] = x[u].x; dst[1] = x[u].y; dst[2] = x[u].z; dst[3] = x[u].w;
+          float* dst = s_pit + (4 * c4) * D + jj;
+          dst[0] = x[u].x; dst[D] = x[u].y; dst[2 * D] = x[u].z; dst[3 * D] = x[u].w;
         }
       }
     }
   } else {  // write only: the caller gave Pi^T split into even / odd output columns
     for (int i = tid; i < D * HALF; i += P::THREADS) {
       const int k = i / HALF, pp = i - k * HALF;
-      s_pi[(2 * pp) * PITCH + k] = __ldg(w.rot_even + i);
-      s_pi[(2 * pp + 1) * PITCH + k] = __ldg(w.rot_odd + i);
+      s_pit[k * D + 2 * pp] = __ldg(w.rot_even + i);
+      s_pit[k * D + 2 * pp + 1] = __ldg(w.rot_odd + i);
     }
   }
   __syncthreads();
 
-  const int64_t n_q = has_attn ? (int64_t)a.sh.rows * a.sh.Hq : 0;
-  const int64_t rows_per_src = has_write ? w.n_tokens * w.num_heads : 0;
-  const int64_t n_w = rows_per_src * (has_write ? w.n_sources : 0);
-  const int64_t cq = (n_q + VC - 1) / VC, cw = (n_w + VC - 1) / VC;
-  auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(grp + 1), "n"(D) : "memory"); };
-  float4* gx = s_x + grp * D;
-  const float* prow = s_pi + j * PITCH;
+  // vector counts fit 32 bits (rows <= kMaxRowsPerLaunch, writes <= kSmallRows): no 64-bit divisions
+  const int n_q = has_attn ? a.sh.rows * a.sh.Hq : 0;
+  const int rows_per_src = has_write ? (int)w.n_tokens * w.num_heads : 0;
+  const int n_w = rows_per_src * (has_write ? w.n_sources : 0);
+  const int cq = (n_q + VC - 1) / VC, cw = (n_w + VC - 1) / VC;
+  float4* gx = s_x + warp * D;
+  const bool jact = 4 * lane < D;                       // this lane owns outputs 4*lane .. 4*lane+3
+  const float4* pcol = reinterpret_cast<const float4*>(s_pit) + (jact ? lane : 0);  // + d * (D/4)
+  // (source, token, head) of write vector `vec`
+  auto w_coords = [&](int vec, int& src, int& tok, int& h) {
+    src = vec >= rows_per_src ? 1 : 0;
+    const unsigned rem = (unsigned)(vec - src * rows_per_src);
+    tok = (int)(rem / (unsigned)w.num_heads);
+    h = (int)(rem - (unsigned)tok * (unsigned)w.num_heads);
+  };
 
-  for (int64_t c = (int64_t)blockIdx.x * G + grp; c < cq + cw; c += (int64_t)n_rot_blocks * G) {
+  for (int c = (int)blockIdx.x * P::WARPS + warp; c < cq + cw; c += n_rot_blocks * P::WARPS) {
     const bool is_w = c >= cq;
-    const int64_t v0 = (is_w ? c - cq : c) * VC;
-    const int64_t nv = is_w ? n_w : n_q;
-    float xr[VC];
+    const int v0 = (is_w ? c - cq : c) * VC;
+    const int nv = is_w ? n_w : n_q;
+    // ---- load: lane l holds elements l, l+32, ... of each of the four vectors -------------------
+    float xr[XPL][VC];
+    const int dt = is_w ? w.x_dtype : a.q_dtype;
+    const void* base[VC];
 #pragma unroll
     for (int v = 0; v < VC; ++v) {
-      const int64_t vec = v0 + v;
-      xr[v] = 0.f;
+      const int vec = v0 + v;
+      base[v] = nullptr;
       if (vec < nv) {
         if (!is_w) {
-          const int64_t row = vec / a.sh.Hq + a.sh.row_offset;
-          const int h = (int)(vec % a.sh.Hq);
-          xr[v] = load_as_float(a.q, a.q_dtype, row * a.q_token_stride + h * a.q_head_stride + j);
+          const unsigned rr = (unsigned)vec / (unsigned)a.sh.Hq;
+          const int h = (int)((unsigned)vec - rr * (unsigned)a.sh.Hq);
+          base[v] = byte_offset(a.q, dt, ((int64_t)rr + a.sh.row_offset) * a.q_token_stride +
+                                             h * a.q_head_stride + lane);
         } else {
-          const int src = (int)(vec / rows_per_src);
-          const int64_t rem = vec - (int64_t)src * rows_per_src;
-          const int64_t tok = rem / w.num_heads;
-          const int h = (int)(rem - tok * w.num_heads);
-          xr[v] = load_as_float(w.x[src], w.x_dtype,
-                                tok * w.token_stride[src] + (int64_t)h * w.head_stride[src] + j);
+          int src, tok, h;
+          w_coords(vec, src, tok, h);
+          base[v] = byte_offset(w.x[src], dt, (int64_t)tok * w.token_stride[src] +
+                                                  (int64_t)h * w.head_stride[src] + lane);
         }
       }
     }
-    gx[j] = make_float4(xr[0], xr[1], xr[2], xr[3]);
-    group_sync();
+    if (dt == TQ4_F32) load_strip<float, XPL, VC>(base, xr);
+    else if (dt == TQ4_F16) load_strip<__half, XPL, VC>(base, xr);
+    else load_strip<__nv_bfloat16, XPL, VC>(base, xr);
+    float nrm[VC];
     if (is_w) {
-      const int wv = j >> 5, lane = j & 31;
-      for (int v = wv; v < VC; v += D / 32) {
+#pragma unroll
+      for (int v = 0; v < VC; ++v) {
         float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < XPL; ++i) {
-          const float xk = reinterpret_cast<const float*>(gx + lane + 32 * i)[v];
-          ss = fmaf(xk, xk, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) s_nrm[grp * VC + v] = sqrtf(ss);
+        for (int i = 0; i < XPL; ++i) ss = fmaf(xr[i][v], xr[i][v], ss);
+        nrm[v] = sqrtf(warp_sum(ss));
+        const float den = nrm[v] + 1e-10f;
+#pragma unroll
+        for (int i = 0; i < XPL; ++i) xr[i][v] = xr[i][v] / den;
       }
-      group_sync();
-#pragma unroll
-      for (int v = 0; v < VC; ++v) xr[v] = xr[v] / (s_nrm[grp * VC + v] + 1e-10f);
-      gx[j] = make_float4(xr[0], xr[1], xr[2], xr[3]);
-      group_sync();
     }
-    float acc[4][VC];
+    __syncwarp();  // the previous pass has finished reading the staging strip
 #pragma unroll
-    for (int qq = 0; qq < 4; ++qq)
+    for (int i = 0; i < XPL; ++i) gx[lane + 32 * i] = make_float4(xr[i][0], xr[i][1], xr[i][2], xr[i][3]);
+    __syncwarp();
+
+    // ---- y[v][4*lane + jj] = sum_d x[v][d] * Pi[4*lane + jj][d] as (s0 + s1) + (s2 + s3): the two
+    // quarter chains of a half advance together (32 independent accumulators); loops stay rolled,
+    // a launch of a few thousand vectors runs this code once per warp and pays for its size
+    float y[VC][4];
+#pragma unroll 1
+    for (int hf = 0; hf < 2; ++hf) {
+      float sa[VC][4], sb[VC][4];
 #pragma unroll
-      for (int v = 0; v < VC; ++v) acc[qq][v] = 0.f;
+      for (int v = 0; v < VC; ++v)
 #pragma unroll
-    for (int qq = 0; qq < 4; ++qq) {
-#pragma unroll 8
+        for (int jj = 0; jj < 4; ++jj) sa[v][jj] = sb[v][jj] = 0.f;
+      const float4* pa = pcol + (2 * hf) * KQ * (D / 4);
+      const float4* xa = gx + (2 * hf) * KQ;
+#pragma unroll 4
       for (int dd = 0; dd < KQ; ++dd) {
-        const int d = qq * KQ + dd;
-        const float pv = prow[d];
-        const float4 xv = gx[d];
-        acc[qq][0] = fmaf(xv.x, pv, acc[qq][0]);
-        acc[qq][1] = fmaf(xv.y, pv, acc[qq][1]);
-        acc[qq][2] = fmaf(xv.z, pv, acc[qq][2]);
-        acc[qq][3] = fmaf(xv.w, pv, acc[qq][3]);
-      }
-    }
-    float y[VC];
+        const float4 p0 = pa[dd * (D / 4)], x0 = xa[dd];
+        const float4 p1 = pa[(KQ + dd) * (D / 4)], x1 = xa[KQ + dd];
+        const float xs0[VC] = {x0.x, x0.y, x0.z, x0.w}, ps0[4] = {p0.x, p0.y, p0.z, p0.w};
+        const float xs1[VC] = {x1.x, x1.y, x1.z, x1.w}, ps1[4] = {p1.x, p1.y, p1.z, p1.w};
 #pragma unroll
-    for (int v = 0; v < VC; ++v) y[v] = (acc[0][v] + acc[1][v]) + (acc[2][v] + acc[3][v]);
+        for (int v = 0; v < VC; ++v)
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            sa[v][jj] = fmaf(xs0[v], ps0[jj], sa[v][jj]);
+            sb[v][jj] = fmaf(xs1[v], ps1[jj], sb[v][jj]);
+          }
+      }
+#pragma unroll
+      for (int v = 0; v < VC; ++v)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          y[v][jj] = hf == 0 ? sa[v][jj] + sb[v][jj] : y[v][jj] + (sa[v][jj] + sb[v][jj]);
+    }
 
     pdl_wait();  // nothing before this point wrote global memory
     if (!is_w) {
 #pragma unroll
       for (int v = 0; v < VC; ++v)
-        if (v0 + v < nv) a.plan.q_rot[(v0 + v) * D + j] = y[v];
+        if (v0 + v < nv && jact)
+          *reinterpret_cast<float4*>(a.plan.q_rot + (int64_t)(v0 + v) * D + 4 * lane) =
+              make_float4(y[v][0], y[v][1], y[v][2], y[v][3]);
     } else {
       const RowLayout lay = row_layout(w.num_heads, D);
 #pragma unroll
       for (int v = 0; v < VC; ++v) {
-        const int64_t vec = v0 + v;
-        if (vec >= nv) continue;  // uniform over the group
-        const int src = (int)(vec / rows_per_src);
-        const int64_t rem = vec - (int64_t)src * rows_per_src;
-        const int64_t tok = rem / w.num_heads;
-        const int h = (int)(rem - tok * w.num_heads);
-        const int idx = bucketize(y[v], w.bounds[src], w.n_bounds[src]);
-        const int lo = __shfl_down_sync(0xffffffffu, idx, 1);
+        const int vec = v0 + v;
+        if (vec >= nv) continue;
+        int src, tok, h;
+        w_coords(vec, src, tok, h);
+        const float* bd = s_bounds[src];
+        const unsigned b0 = (unsigned)((bucketize_sorted16(y[v][0], bd) << 4) | bucketize_sorted16(y[v][1], bd));
+        const unsigned b1 = (unsigned)((bucketize_sorted16(y[v][2], bd) << 4) | bucketize_sorted16(y[v][3], bd));
         uint8_t* dst_idx;
         float* dst_norm;
         if (w.cache != nullptr) {
@@ -399,21 +439,21 @@ prologue_kernel(const AttnArgs a, const CompressArgs w, const int has_attn, cons
           const int64_t slot = w.slot_mapping[tok];
           if (slot < 0) continue;
           if (slot >= w.num_cache_slots) {
-            if (j == 0 && w.err_flag) atomicOr(w.err_flag, TQ4_DEV_BAD_SLOT);
+            if (lane == 0 && w.err_flag) atomicOr(w.err_flag, TQ4_DEV_BAD_SLOT);
             continue;
           }
           uint8_t* rowp = w.cache + slot * w.cache_token_stride;
           dst_idx = rowp + (src == 0 ? lay.k_idx : lay.v_idx) + h * HALF;
           dst_norm = reinterpret_cast<float*>(rowp + (src == 0 ? lay.k_norm : lay.v_norm) + h * 4);
         } else {
-          dst_idx = w.packed_out + vec * HALF;
+          dst_idx = w.packed_out + (int64_t)vec * HALF;
           dst_norm = w.norms_out + vec;
         }
-        if (!(j & 1)) dst_idx[j >> 1] = (uint8_t)((idx << 4) | lo);
-        if (j == 0) *dst_norm = s_nrm[grp * VC + v];
+        // bytes 2*lane, 2*lane+1 of the head's packed row (2-byte aligned: rows start on 4 bytes)
+        if (jact) *reinterpret_cast<uint16_t*>(dst_idx + 2 * lane) = (uint16_t)(b0 | (b1 << 8));
+        if (lane == 0) *dst_norm = nrm[v];
       }
     }
-    group_sync();  // the group's staging area is reused by its next pass
   }
   pdl_wait();
 }
@@ -433,8 +473,8 @@ int launch_prologue_t(const AttnArgs* a, const CompressArgs* w, cudaStream_t st)
   const int64_t n_q = a ? (int64_t)a->sh.rows * a->sh.Hq : 0;
   const int64_t n_w = w ? w->n_tokens * w->num_heads * w->n_sources : 0;
   const int64_t chunks = (n_q + P::VC - 1) / P::VC + (n_w + P::VC - 1) / P::VC;
-  int64_t blocks = (chunks + P::G - 1) / P::G;
-  if (blocks > sm_count()) blocks = sm_count();
+  int64_t blocks = (chunks + P::WARPS - 1) / P::WARPS;
+  if (blocks > 2 * (int64_t)sm_count()) blocks = 2 * (int64_t)sm_count();
   if (blocks < 1) blocks = 1;
   static const AttnArgs no_attn{};
   static const CompressArgs no_write{};
@@ -715,24 +755,28 @@ struct CombineArgs {
 
 constexpr int kCombMaxParts = 64;  // partials of one row merged per pass
 
-// One block per 8 consecutive (row, head) vectors, D threads.  Pi is copied to shared memory
-// asynchronously at kernel entry and overlaps the merge of the partials; the merge weights of all
-// (partial, vector) pairs are computed once into shared memory so that the accumulation loop
-// issues nothing but independent loads.
+constexpr int kCombFastParts = 8;   // up to this many partials per vector take the one-round-trip path
+
+// Batches of 8 consecutive (row, head) vectors, D threads, a block walks batches grid-stride.
+// Pi is copied to shared memory asynchronously at kernel entry (once per block) and overlaps the
+// merge of the partials.  Typical decode rows have at most 8 partials: then every load of a batch
+// (8 x 8 accumulator elements per thread, the 64 maxima and sums by the first 64 threads) is issued
+// before anything is consumed, so a batch costs two dependent memory round trips.  Rows with more
+// partials go through passes of 64 partials with the merge weights staged in shared memory.
 template <int D>
 __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
+  static_assert(D >= kCombHeads * kCombFastParts, "the fast path loads one (vector, partial) pair per thread");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* s_pi = reinterpret_cast<float*>(smem_raw);            // [D][D] (D <= 128 only)
-  float* s_o = s_pi + (D <= 128 ? D * D : 0);                   // [kCombHeads][D]
+  float* s_o = s_pi + (D <= 128 ? D * D : 0);                   // [D][kCombHeads]
   float* s_w = s_o + kCombHeads * D;                            // [kCombMaxParts][kCombHeads]
   float* s_m = s_w + kCombMaxParts * kCombHeads;                // [kCombHeads] running max
   float* s_l = s_m + kCombHeads;                                // [kCombHeads] running sum
   __shared__ long long s_p0[kCombHeads];                        // first partial of the vector's row
   __shared__ int s_np[kCombHeads], s_row[kCombHeads], s_head[kCombHeads];
   const int d = threadIdx.x;
-  const int64_t v0 = (int64_t)blockIdx.x * kCombHeads;
   const int64_t n_vec = (int64_t)a.rows * a.Hq;
-  const int nh = (int)min((int64_t)kCombHeads, n_vec - v0);
+  const int64_t n_batches = (n_vec + kCombHeads - 1) / kCombHeads;
   constexpr float kLn2 = 0.6931471805599453f, kLog2e = 1.4426950408889634f;
   constexpr bool kStagePi = D <= 128;  // a 256 x 256 fp32 Pi does not fit in shared memory
   if (kStagePi && !a.out_rotated) {
@@ -745,124 +789,178 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
   pdl_wait();  // the partials and the plan come from the kernels before this one
   const bool sparse = a.slot_base != nullptr;
   const float mscale = sparse ? 1.f : kLog2e;  // dense partials carry a natural-log LSE
-  if (d < kCombHeads) {
-    const int64_t v = v0 + d;
-    const int r = d < nh ? (int)(v / a.Hq) : 0;
-    s_row[d] = r;
-    s_head[d] = d < nh ? (int)(v - (int64_t)r * a.Hq) : 0;
-    // partials of row r: sparse = slot-major list [p0, p0 + np), dense = index w * rows + r
-    s_p0[d] = sparse ? (long long)a.slot_base[r] * a.TPC : (long long)r;
-    s_np[d] = d >= nh ? 0 : (sparse ? (a.slot_base[r + 1] - a.slot_base[r]) * a.TPC : a.world);
-    s_m[d] = -CUDART_INF_F;
-    s_l[d] = 0.f;
-  }
-  __syncthreads();
-  int np = 0;
-#pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh) np = max(np, s_np[hh]);
-  auto pidx = [&](int hh, int i) -> int64_t {
-    return sparse ? (int64_t)s_p0[hh] + i : (int64_t)i * a.rows + s_p0[hh];
-  };
-
-  float o[kCombHeads];
-  const float* po[kCombHeads];  // this thread's element of partial 0 of each vector
   const int64_t pstride = (sparse ? (int64_t)1 : (int64_t)a.rows) * a.Hq * D;
+
+  for (int64_t batch = blockIdx.x; batch < n_batches; batch += gridDim.x) {
+    const int64_t v0 = batch * kCombHeads;
+    const int nh = (int)min((int64_t)kCombHeads, n_vec - v0);
+    if (d < kCombHeads) {
+      const int64_t v = v0 + d;
+      const int r = d < nh ? (int)(v / a.Hq) : 0;
+      s_row[d] = r;
+      s_head[d] = d < nh ? (int)(v - (int64_t)r * a.Hq) : 0;
+      // partials of row r: sparse = slot-major list [p0, p0 + np), dense = index w * rows + r
+      s_p0[d] = sparse ? (long long)a.slot_base[r] * a.TPC : (long long)r;
+      s_np[d] = d >= nh ? 0 : (sparse ? (a.slot_base[r + 1] - a.slot_base[r]) * a.TPC : a.world);
+      s_m[d] = -CUDART_INF_F;
+      s_l[d] = 0.f;
+    }
+    __syncthreads();
+    int np = 0;
 #pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh) {
-    o[hh] = 0.f;
-    po[hh] = a.part_o + ((int64_t)s_p0[hh] * a.Hq + s_head[hh]) * D + d;
-  }
-  for (int c0 = 0; c0 < np; c0 += kCombMaxParts) {
-    const int nc = min(kCombMaxParts, np - c0);
-    __syncthreads();
-    for (int t = d; t < nc * kCombHeads; t += D) {  // (partial, vector) -> log2-domain maximum
-      const int i = t / kCombHeads, hh = t - i * kCombHeads;
-      s_w[t] = c0 + i < s_np[hh] ? __ldg(a.part_m + pidx(hh, c0 + i) * a.Hq + s_head[hh]) * mscale
-                                 : -CUDART_INF_F;
-    }
-    __syncthreads();
-    if (d < kCombHeads) {  // new running max of vector d; rescale what was accumulated so far
-      float M = s_m[d];
-      for (int i = 0; i < nc; ++i) M = fmaxf(M, s_w[i * kCombHeads + d]);
-      const float m_use = M == -CUDART_INF_F ? 0.f : M;
-      const float resc = s_m[d] == -CUDART_INF_F ? 0.f : exp2f(s_m[d] - m_use);
-      s_l[d] *= resc;
-      s_o[d] = resc;  // s_o[0..7] publishes the rescale factors
-      s_m[d] = M;
-    }
-    __syncthreads();
+    for (int hh = 0; hh < kCombHeads; ++hh) np = max(np, s_np[hh]);
+    auto pidx = [&](int hh, int i) -> int64_t {
+      return sparse ? (int64_t)s_p0[hh] + i : (int64_t)i * a.rows + s_p0[hh];
+    };
+    const float* po[kCombHeads];  // this thread's element of partial 0 of each vector
 #pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh) o[hh] *= s_o[hh];
-    __syncthreads();
-    for (int t = d; t < nc * kCombHeads; t += D) {
-      const int hh = t % kCombHeads;
-      const float M = s_m[hh];
-      s_w[t] = exp2f(s_w[t] - (M == -CUDART_INF_F ? 0.f : M));  // 0 for empty partials
-    }
-    __syncthreads();
-    if (d < nh) {  // running sum of vector d
-      float L = s_l[d];
-      for (int i = 0; i < nc; ++i) {
-        const float w = s_w[i * kCombHeads + d];
-        if (w > 0.f) L = fmaf(sparse ? __ldg(a.part_l + pidx(d, c0 + i) * a.Hq + s_head[d]) : 1.f, w, L);
+    for (int hh = 0; hh < kCombHeads; ++hh)
+      po[hh] = a.part_o + ((int64_t)s_p0[hh] * a.Hq + s_head[hh]) * D + d;
+
+    if (np <= kCombFastParts) {
+      // ---- every load of the batch in flight at once --------------------------------------------
+      float ov[kCombHeads][kCombFastParts];
+#pragma unroll
+      for (int hh = 0; hh < kCombHeads; ++hh)
+#pragma unroll
+        for (int i = 0; i < kCombFastParts; ++i)
+          ov[hh][i] = i < s_np[hh] ? __ldg(po[hh] + (int64_t)i * pstride) : 0.f;
+      if (d < kCombHeads * kCombFastParts) {
+        const int i = d / kCombHeads, hh = d - i * kCombHeads;
+        const bool valid = i < s_np[hh];
+        const int64_t idx = valid ? pidx(hh, i) * a.Hq + s_head[hh] : 0;
+        s_w[d] = valid ? __ldg(a.part_m + idx) * mscale : -CUDART_INF_F;              // [i][hh]
+        s_w[kCombHeads * kCombFastParts + d] = valid ? (sparse ? __ldg(a.part_l + idx) : 1.f) : 0.f;
       }
-      s_l[d] = L;
-    }
-#pragma unroll 4
-    for (int i = 0; i < nc; ++i) {  // accumulate: independent loads, four partials in flight
+      __syncthreads();
+      float res[kCombHeads];
 #pragma unroll
       for (int hh = 0; hh < kCombHeads; ++hh) {
-        const float w = s_w[i * kCombHeads + hh];
-        if (w > 0.f) o[hh] = fmaf(__ldg(po[hh] + (int64_t)(c0 + i) * pstride), w, o[hh]);
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int i = 0; i < kCombFastParts; ++i) M = fmaxf(M, s_w[i * kCombHeads + hh]);
+        const float m_use = M == -CUDART_INF_F ? 0.f : M;
+        float L = 0.f, o = 0.f;
+#pragma unroll
+        for (int i = 0; i < kCombFastParts; ++i) {
+          const float w = exp2f(s_w[i * kCombHeads + hh] - m_use);  // 0 for empty partials
+          L = fmaf(s_w[kCombHeads * kCombFastParts + i * kCombHeads + hh], w, L);
+          o = fmaf(ov[hh][i], w, o);
+        }
+        res[hh] = (hh < nh && L > 0.f) ? o / L : 0.f;
+        if (d == hh && hh < nh && a.lse_out)
+          a.lse_out[(int64_t)(s_row[hh] + a.row_offset) * a.Hq + s_head[hh]] =
+              L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
       }
-    }
-  }
-  __syncthreads();
-#pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh) {
-    const float L = s_l[hh];
-    s_o[hh * D + d] = (hh < nh && L > 0.f) ? o[hh] / L : 0.f;
-  }
-  if (d < nh && a.lse_out) {
-    const float L = s_l[d], M = s_m[d];
-    a.lse_out[(int64_t)(s_row[d] + a.row_offset) * a.Hq + s_head[d]] =
-        L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
-  }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  __syncthreads();
-  float acc[kCombHeads];
-  if (a.out_rotated) {
-#pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = s_o[hh * D + d];
-  } else {
-#pragma unroll
-    for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = 0.f;
-    if (kStagePi) {
-#pragma unroll 8
-      for (int j = 0; j < D; ++j) {
-        const float pv = s_pi[j * D + d];
-#pragma unroll
-        for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh * D + j], pv, acc[hh]);
-      }
+      float4* so4 = reinterpret_cast<float4*>(s_o + d * kCombHeads);  // s_o is [D][8 vectors]
+      so4[0] = make_float4(res[0], res[1], res[2], res[3]);
+      so4[1] = make_float4(res[4], res[5], res[6], res[7]);
     } else {
-      for (int j0 = 0; j0 < D; j0 += 16) {  // column d of Pi from L2, 16 loads in flight
-        float pv[16];
+      float o[kCombHeads];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) pv[u] = __ldg(a.rotation + (size_t)(j0 + u) * D + d);
+      for (int hh = 0; hh < kCombHeads; ++hh) o[hh] = 0.f;
+      for (int c0 = 0; c0 < np; c0 += kCombMaxParts) {
+        const int nc = min(kCombMaxParts, np - c0);
+        __syncthreads();
+        for (int t = d; t < nc * kCombHeads; t += D) {  // (partial, vector) -> log2-domain maximum
+          const int i = t / kCombHeads, hh = t - i * kCombHeads;
+          s_w[t] = c0 + i < s_np[hh] ? __ldg(a.part_m + pidx(hh, c0 + i) * a.Hq + s_head[hh]) * mscale
+                                     : -CUDART_INF_F;
+        }
+        __syncthreads();
+        if (d < kCombHeads) {  // new running max of vector d; rescale what was accumulated so far
+          float M = s_m[d];
+          for (int i = 0; i < nc; ++i) M = fmaxf(M, s_w[i * kCombHeads + d]);
+          const float m_use = M == -CUDART_INF_F ? 0.f : M;
+          const float resc = s_m[d] == -CUDART_INF_F ? 0.f : exp2f(s_m[d] - m_use);
+          s_l[d] *= resc;
+          s_o[d] = resc;  // s_o[0..7] publishes the rescale factors
+          s_m[d] = M;
+        }
+        __syncthreads();
 #pragma unroll
-        for (int u = 0; u < 16; ++u)
+        for (int hh = 0; hh < kCombHeads; ++hh) o[hh] *= s_o[hh];
+        __syncthreads();
+        for (int t = d; t < nc * kCombHeads; t += D) {
+          const int hh = t % kCombHeads;
+          const float M = s_m[hh];
+          s_w[t] = exp2f(s_w[t] - (M == -CUDART_INF_F ? 0.f : M));  // 0 for empty partials
+        }
+        __syncthreads();
+        if (d < nh) {  // running sum of vector d
+          float L = s_l[d];
+          for (int i = 0; i < nc; ++i) {
+            const float w = s_w[i * kCombHeads + d];
+            if (w > 0.f) L = fmaf(sparse ? __ldg(a.part_l + pidx(d, c0 + i) * a.Hq + s_head[d]) : 1.f, w, L);
+          }
+          s_l[d] = L;
+        }
+#pragma unroll 4
+        for (int i = 0; i < nc; ++i) {  // accumulate: independent loads, four partials in flight
 #pragma unroll
-          for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = fmaf(s_o[hh * D + j0 + u], pv[u], acc[hh]);
+          for (int hh = 0; hh < kCombHeads; ++hh) {
+            const float w = s_w[i * kCombHeads + hh];
+            if (w > 0.f) o[hh] = fmaf(__ldg(po[hh] + (int64_t)(c0 + i) * pstride), w, o[hh]);
+          }
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int hh = 0; hh < kCombHeads; ++hh) {
+        const float L = s_l[hh];
+        o[hh] = (hh < nh && L > 0.f) ? o[hh] / L : 0.f;
+      }
+      float4* so4 = reinterpret_cast<float4*>(s_o + d * kCombHeads);
+      so4[0] = make_float4(o[0], o[1], o[2], o[3]);
+      so4[1] = make_float4(o[4], o[5], o[6], o[7]);
+      if (d < nh && a.lse_out) {
+        const float L = s_l[d], M = s_m[d];
+        a.lse_out[(int64_t)(s_row[d] + a.row_offset) * a.Hq + s_head[d]] =
+            L > 0.f ? (M + log2f(L)) * kLn2 : -CUDART_INF_F;
       }
     }
-  }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float acc[kCombHeads];
+    if (a.out_rotated) {
 #pragma unroll
-  for (int hh = 0; hh < kCombHeads; ++hh)
-    if (hh < nh)
-      store_from_float(a.out, a.out_dtype,
-                       (int64_t)(s_row[hh] + a.row_offset) * a.out_token_stride +
-                           (int64_t)s_head[hh] * a.out_head_stride + d,
-                       acc[hh]);
+      for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = s_o[d * kCombHeads + hh];
+    } else {
+#pragma unroll
+      for (int hh = 0; hh < kCombHeads; ++hh) acc[hh] = 0.f;
+      if (kStagePi) {
+#pragma unroll 8
+        for (int j = 0; j < D; ++j) {
+          const float pv = s_pi[j * D + d];
+          const float4 oa = *reinterpret_cast<const float4*>(s_o + j * kCombHeads);
+          const float4 ob = *reinterpret_cast<const float4*>(s_o + j * kCombHeads + 4);
+          acc[0] = fmaf(oa.x, pv, acc[0]); acc[1] = fmaf(oa.y, pv, acc[1]);
+          acc[2] = fmaf(oa.z, pv, acc[2]); acc[3] = fmaf(oa.w, pv, acc[3]);
+          acc[4] = fmaf(ob.x, pv, acc[4]); acc[5] = fmaf(ob.y, pv, acc[5]);
+          acc[6] = fmaf(ob.z, pv, acc[6]); acc[7] = fmaf(ob.w, pv, acc[7]);
+        }
+      } else {
+        for (int j0 = 0; j0 < D; j0 += 16) {  // column d of Pi from L2, 16 loads in flight
+          float pv[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) pv[u] = __ldg(a.rotation + (size_t)(j0 + u) * D + d);
+#pragma unroll
+          for (int u = 0; u < 16; ++u)
+#pragma unroll
+            for (int hh = 0; hh < kCombHeads; ++hh)
+              acc[hh] = fmaf(s_o[(j0 + u) * kCombHeads + hh], pv[u], acc[hh]);
+        }
+      }
+    }
+#pragma unroll
+    for (int hh = 0; hh < kCombHeads; ++hh)
+      if (hh < nh)
+        store_from_float(a.out, a.out_dtype,
+                         (int64_t)(s_row[hh] + a.row_offset) * a.out_token_stride +
+                             (int64_t)s_head[hh] * a.out_head_stride + d,
+                         acc[hh]);
+    __syncthreads();  // s_o, s_w and the per-vector entries are rewritten by the next batch
+  }
 }
 
 template <int D>
@@ -880,8 +978,9 @@ int launch_combine_t(const CombineArgs& c, cudaStream_t st) {
     attr_set = true;
   }
   const int64_t n_vec = (int64_t)c.rows * c.Hq;
-  if (launch_kernel(combine_kernel<D>, dim3((unsigned)((n_vec + kCombHeads - 1) / kCombHeads)), dim3(D), smem,
-                    st, true, c) != cudaSuccess)
+  int64_t grid = (n_vec + kCombHeads - 1) / kCombHeads;
+  if (grid > 3 * (int64_t)sm_count()) grid = 3 * (int64_t)sm_count();
+  if (launch_kernel(combine_kernel<D>, dim3((unsigned)grid), dim3(D), smem, st, true, c) != cudaSuccess)
     return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;

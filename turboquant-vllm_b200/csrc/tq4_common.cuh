@@ -124,6 +124,31 @@ __device__ __forceinline__ int bucketize(float y, const float* __restrict__ b, i
   return idx;
 }
 
+// The same count by binary search over ASCENDING boundaries padded to 15 entries with +inf
+// (entry 15 is never read): four compares.  NaN compares false at every step -> 0.
+__device__ __forceinline__ int bucketize_sorted16(float y, const float* b) {
+  int lo = (y > b[7]) ? 8 : 0;
+  lo += (y > b[lo + 3]) ? 4 : 0;
+  lo += (y > b[lo + 1]) ? 2 : 0;
+  lo += (y > b[lo]) ? 1 : 0;
+  return lo;
+}
+
+// address of element i of an array of dtype-coded elements
+__device__ __forceinline__ const void* byte_offset(const void* p, int dtype, int64_t i) {
+  return reinterpret_cast<const char*>(p) + i * (dtype == TQ4_F32 ? 4 : 2);
+}
+
+// out[i][v] = element 32*i of the strip starting at base[v] (nullptr -> zeros), converted to fp32
+template <typename T, int N, int V>
+__device__ __forceinline__ void load_strip(const void* const (&base)[V], float (&out)[N][V]) {
+#pragma unroll
+  for (int v = 0; v < V; ++v)
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      out[i][v] = base[v] ? to_float<T>(reinterpret_cast<const T*>(base[v])[32 * i]) : 0.f;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (n == 0) {
