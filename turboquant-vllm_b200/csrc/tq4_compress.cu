@@ -6,6 +6,8 @@
 // src/turboquant_vllm/quantizer.py:139-149): norm = sqrt(sum x^2) in fp32,
 // xn = x / (norm + 1e-10) with IEEE division, y = xn * Pi^T with fp32 FMA accumulation in
 // ascending k, idx = #{boundary < y}, byte = idx_even << 4 | idx_odd.
+#include <math_constants.h>
+
 #include "tq4_common.cuh"
 
 namespace tq4 {
@@ -34,8 +36,22 @@ compress_kernel(const CompressArgs a) {
   float* s_odd = s_even + KC * HALF;                              // [KC][HALF]
   float4* s_x = reinterpret_cast<float4*>(s_odd + KC * HALF);     // [kWarps][D] (4 rows each)
 
+  __shared__ float s_bounds[2][16];  // ascending boundaries of each source, padded with +inf
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    const int src = threadIdx.x >> 4, i = threadIdx.x & 15;
+    s_bounds[src][i] = (src < a.n_sources && i < a.n_bounds[src]) ? a.bounds[src][i] : CUDART_INF_F;
+  }
   float4* xw = s_x + warp * D;
+  // (source, token, head) of a row; row counts fit 32 bits (checked by the host)
+  const unsigned rows_per_src32 = (unsigned)(a.n_tokens * a.num_heads);
+  auto row_coords = [&](int64_t row, int& src, int64_t& tok, int& h) {
+    src = (uint64_t)row >= rows_per_src32 ? 1 : 0;
+    const unsigned rem = (unsigned)row - (src ? rows_per_src32 : 0u);
+    const unsigned t = rem / (unsigned)a.num_heads;
+    tok = t;
+    h = (int)(rem - t * (unsigned)a.num_heads);
+  };
   const int64_t rows_per_src = a.n_tokens * a.num_heads;
   const int64_t total_rows = rows_per_src * a.n_sources;
   const int64_t n_tiles = (total_rows + kRowsPerWarp - 1) / kRowsPerWarp;
@@ -68,10 +84,9 @@ compress_kernel(const CompressArgs a) {
       float xv[XPL];
       float ss = 0.f;
       if (row < total_rows) {
-        const int src = (int)(row / rows_per_src);
-        const int64_t rem = row - (int64_t)src * rows_per_src;
-        const int64_t tok = rem / a.num_heads;
-        const int h = (int)(rem - tok * a.num_heads);
+        int src, h;
+        int64_t tok;
+        row_coords(row, src, tok, h);
         const T* xp = reinterpret_cast<const T*>(a.x[src]) + tok * a.token_stride[src] +
                       (int64_t)h * a.head_stride[src];
 #pragma unroll
@@ -156,12 +171,10 @@ compress_kernel(const CompressArgs a) {
     for (int r = 0; r < kRowsPerWarp; ++r) {
       const int64_t row = row0 + r;
       if (row >= total_rows) continue;
-      const int src = (int)(row / rows_per_src);
-      const int64_t rem = row - (int64_t)src * rows_per_src;
-      const int64_t tok = rem / a.num_heads;
-      const int h = (int)(rem - tok * a.num_heads);
-      const float* b = a.bounds[src];
-      const int nb = a.n_bounds[src];
+      int src, h;
+      int64_t tok;
+      row_coords(row, src, tok, h);
+      const float* b = s_bounds[src];
       uint8_t* dst_idx;
       float* dst_norm;
       if (a.cache != nullptr) {
@@ -184,8 +197,8 @@ compress_kernel(const CompressArgs a) {
       for (int i = 0; i < NBL; ++i) {
         const int p = lane + 32 * i;
         if (p < HALF) {
-          const int ie = bucketize(acc_e[i][r], b, nb);
-          const int io = bucketize(acc_o[i][r], b, nb);
+          const int ie = bucketize_sorted16(acc_e[i][r], b);
+          const int io = bucketize_sorted16(acc_o[i][r], b);
           dst_idx[p] = (uint8_t)(((ie & 0xF) << 4) | (io & 0xF));
         }
       }
@@ -205,14 +218,19 @@ __global__ void __launch_bounds__(128) compress_small_kernel(const CompressArgs 
   constexpr int HALF = Cfg::HALF, NBL = Cfg::NBL, XPL = Cfg::XPL, KQ = D / 4;
   __shared__ float s_x[D];
   __shared__ float s_part[3][2 * NBL][32];
+  __shared__ float s_b[16];  // ascending boundaries of this row's source, padded with +inf
   pdl_trigger();  // the query-rotation kernel that follows in a decode step does not depend on this one
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t row = blockIdx.x;
   const int64_t rows_per_src = a.n_tokens * a.num_heads;
-  const int src = (int)(row / rows_per_src);
-  const int64_t rem = row - (int64_t)src * rows_per_src;
-  const int64_t tok = rem / a.num_heads;
-  const int h = (int)(rem - tok * a.num_heads);
+  const int src = row >= rows_per_src ? 1 : 0;
+  const unsigned rem = (unsigned)(row - (src ? rows_per_src : 0));
+  const int64_t tok = rem / (unsigned)a.num_heads;
+  const int h = (int)(rem - (unsigned)tok * (unsigned)a.num_heads);
+  if (threadIdx.x >= 32 && threadIdx.x < 48) {
+    const int i = threadIdx.x - 32;
+    s_b[i] = i < a.n_bounds[src] ? a.bounds[src][i] : CUDART_INF_F;
+  }
   const T* xp = reinterpret_cast<const T*>(a.x[src]) + tok * a.token_stride[src] +
                 (int64_t)h * a.head_stride[src];
   float xv[XPL];
@@ -272,8 +290,7 @@ __global__ void __launch_bounds__(128) compress_small_kernel(const CompressArgs 
   for (int i = 0; i < 2 * NBL; ++i)
     acc[i] = (acc[i] + s_part[0][i][lane]) + (s_part[1][i][lane] + s_part[2][i][lane]);
 
-  const float* b = a.bounds[src];
-  const int nb = a.n_bounds[src];
+  const float* b = s_b;
   uint8_t* dst_idx;
   float* dst_norm;
   if (a.cache != nullptr) {
@@ -297,7 +314,7 @@ __global__ void __launch_bounds__(128) compress_small_kernel(const CompressArgs 
     const int p = lane + 32 * i;
     if (p < HALF)
       dst_idx[p] =
-          (uint8_t)(((bucketize(acc[2 * i], b, nb) & 0xF) << 4) | (bucketize(acc[2 * i + 1], b, nb) & 0xF));
+          (uint8_t)((bucketize_sorted16(acc[2 * i], b) << 4) | bucketize_sorted16(acc[2 * i + 1], b));
   }
   if (lane == 0) *dst_norm = norm;
 }
@@ -308,6 +325,7 @@ int launch_compress(const CompressArgs& a, cudaStream_t st) {
   using Cfg = CompressCfg<D>;
   const int64_t total_rows = a.n_tokens * a.num_heads * a.n_sources;
   if (total_rows == 0) return TQ4_OK;
+  if (total_rows > 0x7fffffffll) return TQ4_ERR_INVALID_ARG;  // the kernels index rows with 32 bits
   if (total_rows <= kSmallRows) {
     compress_small_kernel<D, T><<<(unsigned)total_rows, 128, 0, st>>>(a);
     TQ4_CHECK_LAUNCH();

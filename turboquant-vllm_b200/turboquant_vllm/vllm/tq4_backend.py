@@ -409,9 +409,16 @@ class TQ4AttentionImpl(FlashAttentionImpl):
         left = sw[0] if isinstance(sw, (tuple, list)) else sw
         return int(left) + 1 if left is not None and left >= 0 else 0
 
-    def _fused_attention(self, query, kv_cache, attn_metadata, output, *, decode: bool):
+    def _fused_attention(self, query, kv_cache, attn_metadata, output, *, decode: bool, write=None):
         n = attn_metadata.num_actual_tokens
         ws = self._cg_workspace if n <= self._cg_workspace_rows else None
+        if write is not None and not kv_cache.is_contiguous():
+            self._compress_and_store(write[0], write[1], kv_cache, write[2])  # strided cache view
+            write = None
+        if write is not None:
+            key, value, slot_mapping = write
+            write = (key, value, slot_mapping, self._tq4_rot_T_even, self._tq4_rot_T_odd,
+                     self._k_boundaries, self._v_boundaries)
         ops.paged_tq4_attention(
             query[:n], kv_cache, attn_metadata.block_table, attn_metadata.seq_lens,
             self._k_centroids, self._v_centroids, self._tq4_rotation, self.num_kv_heads,
@@ -419,15 +426,17 @@ class TQ4AttentionImpl(FlashAttentionImpl):
             query_start_loc=None if decode else attn_metadata.query_start_loc,
             causal=bool(getattr(attn_metadata, "causal", True)),
             sliding_window=self._sliding_window_tokens(),
-            out=output[:n], workspace=ws,
+            out=output[:n], workspace=ws, write=write,
         )
         return output
 
     def _fused_decode_path(self, query, key, value, kv_cache, attn_metadata, output):
-        """Uniform single-token decode: fused write + fused paged attention (2 + 2 launches)."""
+        """Uniform single-token decode in three launches: the cache write of the new tokens rides in
+        the kernel that rotates the queries and plans the tiles, then attention and the merge."""
+        write = None
         if key is not None and value is not None:
-            self._compress_and_store(key, value, kv_cache, attn_metadata.slot_mapping)
-        return self._fused_attention(query, kv_cache, attn_metadata, output, decode=True)
+            write = (key, value, attn_metadata.slot_mapping)
+        return self._fused_attention(query, kv_cache, attn_metadata, output, decode=True, write=write)
 
     def _int8_prefill_path(self, query, key, value, kv_cache, attn_metadata, output):
         """Chunked prefill / mixed batches on the fused kernel (multi-sequence, prefix-aware).
