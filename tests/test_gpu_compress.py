@@ -202,8 +202,8 @@ def test_write_then_read_roundtrip_full_size(ops):
 
 @pytest.mark.parametrize("d", [64, 96, 128, 256])
 def test_small_and_streaming_kernels_agree_bitwise(ops, d):
-    """A vector compresses to the same bytes and norm whether it arrives in a decode-sized call
-    (one-CTA-per-row kernel) or a prefill-sized call (streaming kernel)."""
+    """A vector compresses to the same norm and (FMA kernels: the same bytes) whether it arrives in
+    a decode-sized call (one-CTA-per-row kernel) or a prefill-sized call (streaming kernel)."""
     pr = Prims(d)
     p = pr.cuda()
     x, _ = O.synthetic_kv(2048, 8, d, seed=31, dtype=torch.bfloat16)  # 16384 rows -> streaming kernel
@@ -211,4 +211,10 @@ def test_small_and_streaming_kernels_agree_bitwise(ops, d):
     big_p, big_n = ops.tq4_compress(x, p["even"], p["odd"], p["kb"])
     for s0 in (0, 1024):
         sm_p, sm_n = ops.tq4_compress(x[s0:s0 + 512], p["even"], p["odd"], p["kb"])  # 4096 rows -> small kernel
-        assert torch.equal(sm_p, big_p[s0:s0 + 512]) and torch.equal(sm_n, big_n[s0:s0 + 512])
+        assert torch.equal(sm_n, big_n[s0:s0 + 512])
+        if d == 128:
+            # large inputs at head_dim 128 rotate on the tensor cores (split TF32): same norms, and
+            # indices that differ only for coordinates within ~1e-7 of a bucket boundary
+            assert index_mismatch(sm_p, big_p[s0:s0 + 512]) <= MAX_INDEX_MISMATCH
+        else:
+            assert torch.equal(sm_p, big_p[s0:s0 + 512])

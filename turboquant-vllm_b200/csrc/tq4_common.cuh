@@ -187,5 +187,8 @@ struct CompressArgs {
 // rows at or below this count are handled by the small-launch kernels
 constexpr int64_t kSmallRows = 8192;
 int dispatch_compress(const CompressArgs& a, int head_dim, int dtype, cudaStream_t st);
+// tensor-core (tcgen05) compress kernel for large inputs at head_dim 128 (tq4_compress_tc.cu)
+bool compress_tc_eligible(const CompressArgs& a, int head_dim, int dtype);
+int launch_compress_tc(const CompressArgs& a, int dtype, cudaStream_t st);
 
 }  // namespace tq4
