@@ -12,7 +12,7 @@
 //
 // Data flow per tile (one persistent CTA per SM, 256 threads; thread = (row, half of the columns)):
 //   norm of the row (both threads of a row, redundantly)                      CUDA cores
-//   x^ = x / (norm + 1e-10), split, stored K-major with the 128-byte swizzle   CUDA cores -> smem
+//   x^ = x * (1 / (norm + 1e-10)), split, stored K-major with the 128-byte swizzle   CUDA cores -> smem
 //   48 x tcgen05.mma 128x128x8 over two K-steps of 64, D in 128 TMEM columns   tensor cores
 //   tcgen05.ld of the thread's 64 columns, bucketize, pack, store              CUDA cores
 // Pi (hi and lo) stays resident in shared memory: 2 x 64 KB.  Every wait is bounded.
@@ -219,7 +219,8 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
         for (int l = 0; l < o; ++l) p[l] = p[l] + p[l + o];
       nrm = sqrtf(p[0]);
     }
-    const float den = nrm + 1e-10f;
+    // one IEEE division per row; x * (1 / den) is within an ulp of x / den, far below the TF32 split error
+    const float inv_den = 1.f / (nrm + 1e-10f);
 
     // ---- two K-steps of 64: this thread fills K-block (2 * step + half) of A into buffer `half` ----
     bool ok = true;
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
       for (int c = 0; c < 8; ++c) {
         float hi[4], lo[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) split_tf32(x[4 * c + e] / den, hi[e], lo[e]);
+        for (int e = 0; e < 4; ++e) split_tf32(x[4 * c + e] * inv_den, hi[e], lo[e]);
         const uint32_t off = swz(row_in_tile, c);
         *reinterpret_cast<float4*>(a_hi + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
         *reinterpret_cast<float4*>(a_lo + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
