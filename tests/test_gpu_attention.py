@@ -44,7 +44,7 @@ def _run(ops, mode, **kw):
     try:
         return ops.paged_tq4_attention(mode=mode, **kw)
     except NotImplementedError:
-        if mode == 2:
+        if mode in (2, 3):
             pytest.skip("tensor-core kernel does not cover this shape")
         raise
 
@@ -64,7 +64,7 @@ def test_decode_golden(ops, golden, tag, mode):
     assert ops.read_and_clear_errors(out.device) == 0
 
 
-@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("mode", MODES + [3])
 @pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7"])
 @pytest.mark.parametrize("window", [None, 9])
 def test_prefill_golden(ops, golden, tag, window, mode):
@@ -152,6 +152,27 @@ def test_decode_reference_signature_and_out(ops, mode):
     assert r is buf and torch.equal(buf, a)
     ref = O.paged_decode_fp32(q.cpu(), case["cache"], case["block_table"], seq_lens, pr.kc, pr.vc, pr.rot, 4)
     assert cosine(a.float().cpu(), ref) > 0.999
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 4), (4, 4), (32, 4)])
+def test_prefill_tensor_core_kernel(ops, hq, hkv):
+    """tcgen05 chunked-prefill kernel (mode 3): blocks of 128 / G query rows per CTA, several tiles,
+    packed prefixes, partial blocks, bottom-right causal / sliding window / full attention."""
+    pr = Prims(128)
+    p = pr.cuda()
+    d, bs = 128, 16
+    seq_lens, q_lens = [400, 130, 33, 700], [300, 130, 1, 77]
+    case = build_paged_case(seq_lens, hkv, d, bs, pr, seed=21, padded=True)
+    q = torch.randn(sum(q_lens), hq, d, generator=torch.Generator().manual_seed(8)).bfloat16()
+    qsl = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    for causal, window in ((True, None), (True, 100), (False, None)):
+        ref = O.paged_attention_fp32(q, case["cache"], case["block_table"], seq_lens, qsl, pr.kc, pr.vc, pr.rot,
+                                     hkv, None, causal, window)
+        out = _run(ops, 3, q=q.cuda(), kv_cache=case["cache"].cuda(), block_table=case["block_table"].cuda(),
+                   seq_lens=case["seq_lens"].cuda(), k_centroids=p["kc"], v_centroids=p["vc"], rotation=p["rot"],
+                   num_kv_heads=hkv, block_size=bs, query_start_loc=qsl.cuda(), causal=causal,
+                   sliding_window=window, out_dtype=torch.float32)
+        _check(out, ref)
 
 
 @pytest.mark.parametrize("mode", MODES)

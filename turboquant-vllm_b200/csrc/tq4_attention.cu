@@ -895,8 +895,8 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
           }
           s_l[d] = L;
         }
-#pragma unroll 4
-        for (int i = 0; i < nc; ++i) {  // accumulate: independent loads, four partials in flight
+#pragma unroll 8
+        for (int i = 0; i < nc; ++i) {  // accumulate: independent loads, eight partials (64 loads) in flight
 #pragma unroll
           for (int hh = 0; hh < kCombHeads; ++hh) {
             const float w = s_w[i * kCombHeads + hh];
@@ -1104,7 +1104,8 @@ static int attention_impl(
   const bool mma_ok = attention_mma_supported(a.sh, block_size, cache, cache_block_stride,
                                               cache_token_stride);
   if (mode == 2 && !mma_ok) return TQ4_ERR_UNSUPPORTED;
-  const bool use_mma = mode == 2 || (mode == 0 && mma_ok);
+  if (mode < 0 || mode > 3) return TQ4_ERR_INVALID_ARG;
+  const bool use_mma = mode == 2 || mode == 3 || (mode == 0 && mma_ok);
   if (use_mma)
     make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC, num_kv_heads));
   const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
@@ -1144,6 +1145,12 @@ static int attention_impl(
   a.out_rotated = out_rotated;
   a.err_flag = err_flag;
 
+  // chunked prefill (several query rows per sequence) at head_dim 128: tensor-core kernel, one
+  // dequantisation of a key tile serves a whole block of query rows
+  const bool prefill_ok = prefill_tc_supported(a);
+  if (mode == 3 && !prefill_ok) return TQ4_ERR_UNSUPPORTED;
+  const bool use_prefill = mode == 3 || (mode == 0 && prefill_ok && num_rows >= 8 * (int64_t)num_seqs);
+
   const int sms = sm_count();
   int ctas = (use_mma ? 1 : 4) * sms / a.sh.n_slices;
   if (ctas < 1) ctas = 1;
@@ -1159,11 +1166,13 @@ static int attention_impl(
     prof_end(TQ4_PROF_PROLOGUE, st);
     if (rc != TQ4_OK) return rc;
     prof_begin(TQ4_PROF_ATTENTION, st);
-    rc = use_mma ? launch_attention_mma(a, st) : launch_attention_fp32(a, st);
+    rc = use_prefill ? launch_prefill_tc(a, st)
+                     : (use_mma ? launch_attention_mma(a, st) : launch_attention_fp32(a, st));
     prof_end(TQ4_PROF_ATTENTION, st);
     if (rc != TQ4_OK) return rc;
     CombineArgs c{};
-    c.slot_base = a.plan.slot_base;
+    c.slot_base = use_prefill ? nullptr : a.plan.slot_base;  // prefill: one dense partial per row
+    c.world = 1;
     c.TPC = a.sh.TPC;
     c.part_o = a.plan.part_o;
     c.part_m = a.plan.part_m;

@@ -1,0 +1,541 @@
+// Chunked-prefill attention over the packed TQ4 cache on the 5th-generation tensor cores
+// (head_dim 128).  A CTA owns a block of 128 / G query rows of one sequence and one KV head: the
+// M = 128 rows of the MMAs are the (query row, query head of the GQA group) pairs, so a key/value
+// tile is dequantised ONCE per CTA and serves all of them (the streaming kernel dequantises it per
+// query row).  Everything happens in rotated space on the queries the prologue kernel rotated.
+//
+// Per 64-token tile:
+//   TMA boxes (K+V index rows and norm columns of 4 pages)                      -> shared memory
+//   dequantise through a 256-entry byte -> half2 table: K~ [64 tok][128 d] and V~ as fp16,
+//     stored in the swizzled layouts the MMA descriptors expect                  CUDA cores
+//   S = Qhi K~^T + Qlo K~^T   (tcgen05.mma kind::f16, 128 x 64 x 16, fp32 in TMEM)   tensor cores
+//   tcgen05.ld S, x knorm, mask, lazy online softmax, P = p * vnorm as fp16 hi + lo   CUDA cores
+//   O += Plo V~ + Phi V~      (tcgen05.mma 128 x 128 x 16, V~ as an MN-major B operand)
+// At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
+// layout of one dense partial per row; the merge kernel un-rotates and stores them.
+// The phases of a tile run one after the other (block-wide barriers); every wait is bounded.
+#include <cuda.h>
+#include <math_constants.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "tq4_attention.cuh"
+
+namespace tq4 {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kBN = 64;                 // tokens per tile
+constexpr int kThreads = 256;
+constexpr uint32_t kTmemCols = 256;     // S: columns [0, 64), O: columns [64, 192)
+constexpr uint32_t kColS = 0, kColO = 64;
+
+// shared-memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t kOffQhi = 0;                       // 2 K-blocks x [128 rows][128 B]
+constexpr uint32_t kOffQlo = 32768;
+constexpr uint32_t kOffK = 65536;                     // 2 K-blocks x [64 tok][128 B]
+constexpr uint32_t kOffV = kOffK + 16384;             // 2 MN-blocks x [64 tok][128 B]
+constexpr uint32_t kOffP = kOffV + 16384;             // [128 rows][128 B] fp16 hi part of p * vnorm
+constexpr uint32_t kOffPlo = kOffP + 16384;           // ... and its fp16 remainder
+constexpr uint32_t kOffStage = kOffPlo + 16384;       // 2 x (4 pages x 2048 B indices + 4 x 512 B norms)
+constexpr uint32_t kStageBytes = 4 * 2048 + 4 * 512;
+constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // K table, V table: 256 x 4 B each
+constexpr uint32_t kOffNorm = kOffLut + 2048;               // kn[64], vn[64], lg[64]
+constexpr uint32_t kSmemBytes = kOffNorm + 3 * 64 * 4;
+
+// instruction descriptors (kind::f16, fp16 operands, fp32 accumulator, M = 128)
+constexpr uint32_t kDescS = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);                // N = 64, B K-major
+constexpr uint32_t kDescO = (1u << 4) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);  // N = 128, B MN-major
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t swz(int row, int c) { return (uint32_t)(row * 128 + ((c ^ (row & 7)) << 4)); }
+
+// K-major operand, 128-byte swizzle: 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand, 128-byte swizzle: 64-element MN blocks `lbo` bytes apart, 8-row K groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool bar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (int it = 0; it < (1 << 22); ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, int w,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+      "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// G = query heads per KV head (1, 2, 4 or 8); a block holds RB = 128 / G query rows
+template <int G>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
+                  const __grid_constant__ CUtensorMap tm_norm) {
+  constexpr int RB = 128 / G;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t s_bar[4];  // [0], [1]: tile stages (TMA), [2]: S ready, [3]: PV done
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_info[4];                   // sequence, first local row, rows in block, dead flag
+  const AttnShape& sh = a.sh;
+  const AttnPlan& p = a.plan;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = blockIdx.y;
+
+  pdl_trigger();
+  pdl_wait();  // plan and rotated queries come from the prologue kernel, the cache from the write
+
+  // ---- which (sequence, row block) is this CTA's? ----------------------------------------------
+  if (tid == 0) {
+    const int lo_all = sh.row_offset, hi_all = sh.row_offset + sh.rows;
+    int acc = 0, found = -1, first = 0, nrows = 0;
+    for (int s = 0; s < sh.num_seqs && found < 0; ++s) {
+      const int q0 = max(a.query_start_loc[s], lo_all), q1 = min(a.query_start_loc[s + 1], hi_all);
+      if (q1 <= q0) continue;
+      const int nb = (q1 - q0 + RB - 1) / RB;
+      if ((int)blockIdx.x < acc + nb) {
+        found = s;
+        first = q0 + ((int)blockIdx.x - acc) * RB;
+        nrows = min(RB, q1 - first);
+      }
+      acc += nb;
+    }
+    s_info[0] = found;
+    s_info[1] = first - sh.row_offset;
+    s_info[2] = nrows;
+    s_info[3] = 0;
+  }
+  __syncthreads();
+  const int seq = s_info[0], lr0 = s_info[1], nrows = s_info[2];
+  if (seq < 0) return;  // grid is an upper bound on the number of blocks
+
+  const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+  unsigned char* sm = smem_raw + (base - smem_addr(smem_raw));
+  const uint32_t bar_t0 = smem_addr(&s_bar[0]), bar_s = smem_addr(&s_bar[2]), bar_o = smem_addr(&s_bar[3]);
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_t0 + 8 * i) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)),
+                 "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // byte -> half2 tables: (centroid[hi nibble], centroid[lo nibble]) scaled onto the fp16 grid
+  {
+    uint32_t* lut = reinterpret_cast<uint32_t*>(sm + kOffLut);
+    for (int i = tid; i < 512; i += kThreads) {
+      const int w = i >> 8, b = i & 255;
+      const float* cent = w ? a.v_centroids : a.k_centroids;
+      const int nc = w ? a.n_v_centroids : a.n_k_centroids;
+      const float sc = w ? a.lut_scale_v : a.lut_scale_k;
+      const float c_hi = (b >> 4) < nc ? __fmul_rn(sc, cent[b >> 4]) : 0.f;
+      const float c_lo = (b & 15) < nc ? __fmul_rn(sc, cent[b & 15]) : 0.f;
+      lut[i] = pack_h2(c_hi, c_lo);
+    }
+  }
+  // ---- the block's queries: row m = r * G + g, scaled by 1 / max|q|, split into fp16 hi + lo -----
+  float qscale = 0.f;  // (threads 0..127, their own row) max|q| * sm_scale * log2(e) / alpha_k
+  {
+    const int m = tid >> 1, kb = tid & 1;  // two threads per row, one 64-column K-block each
+    const int r = m / G, g = m - r * G;
+    float v[64];
+    float qmax = 0.f;
+    if (r < nrows) {
+      const float4* src = reinterpret_cast<const float4*>(
+          p.q_rot + ((int64_t)(lr0 + r) * sh.Hq + kvh * G + g) * kD + 64 * kb);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float4 x = src[i];
+        v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 64; ++i) qmax = fmaxf(qmax, fabsf(v[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) v[i] = 0.f;
+    }
+    qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, 1));
+    const float inv = qmax > 0.f ? 1.f / qmax : 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = v[8 * c + 2 * e] * inv, x1 = v[8 * c + 2 * e + 1] * inv;
+        const float h0 = __half2float(__float2half_rn(x0)), h1 = __half2float(__float2half_rn(x1));
+        hi[e] = pack_h2(h0, h1);
+        lo[e] = pack_h2(x0 - h0, x1 - h1);
+      }
+      const uint32_t off = (uint32_t)kb * 16384u + swz(m, c);
+      *reinterpret_cast<uint4*>(sm + kOffQhi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<uint4*>(sm + kOffQlo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    // hand qmax of row m to the thread that owns TMEM lane m (thread m): through the norm scratch
+    if (kb == 0) reinterpret_cast<float*>(sm + kOffP)[m] = qmax * (a.scale_log2e / a.lut_scale_k);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s_tmem;
+  if (tid < 128) qscale = reinterpret_cast<const float*>(sm + kOffP)[tid];
+  __syncthreads();  // the P area is reused below
+
+  // ---- this thread's row (softmax threads: 0..127, row = TMEM lane) ----------------------------
+  const int my_r = tid < 128 ? tid / G : 0, my_g = tid < 128 ? tid % G : 0;
+  const bool row_live = tid < 128 && my_r < nrows;
+  const int kv_lo = row_live ? p.kv_start[lr0 + my_r] : 0;
+  const int kv_hi = row_live ? p.kv_end[lr0 + my_r] : 0;
+  // keys the block needs: rows are in query order, ranges move forward with the row
+  const int blk_lo = p.kv_start[lr0], blk_hi = p.kv_end[lr0 + nrows - 1];
+  const int t_first = blk_hi > blk_lo ? (blk_lo / kBN) * kBN : 0;
+  const int n_tiles = blk_hi > blk_lo ? (blk_hi - t_first + kBN - 1) / kBN : 0;
+  const int32_t* bt = a.block_table + (int64_t)p.row_seq[lr0] * a.bt_stride;
+  const RowLayout lay = row_layout(sh.Hkv, kD);
+  const int x_idx = lay.k_idx + kvh * 64, x_nrm = (lay.k_norm + kvh * 4) & ~15;
+  const int n_sub = (lay.k_norm + kvh * 4) & 15;
+  const int bs_mask = a.block_size - 1, bs_shift = __ffs(a.block_size) - 1;
+
+  // one lane issues the boxes of tile j into stage j & 1: 4 pages x (indices K+V, norms K+V)
+  auto issue_tile = [&](int j) {
+    const uint32_t st = base + kOffStage + (uint32_t)(j & 1) * kStageBytes, bar = bar_t0 + 8 * (j & 1);
+    const int t0 = t_first + j * kBN;
+    int npages = 0;
+#pragma unroll
+    for (int pg = 0; pg < 4; ++pg) npages += (t0 + 16 * pg < blk_hi) ? 1 : 0;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(npages * 2560) : "memory");
+#pragma unroll
+    for (int pg = 0; pg < 4; ++pg) {
+      const int pos = t0 + 16 * pg;
+      if (pos < blk_hi) {
+        const int blk = __ldg(bt + (pos >> bs_shift));  // out-of-range ids read zeros (TMA bounds)
+        tma_load_4d(st + pg * 2048, &tm_idx, x_idx, pos & bs_mask, 0, blk, bar);
+        tma_load_4d(st + 8192 + pg * 512, &tm_norm, x_nrm, pos & bs_mask, 0, blk, bar);
+      }
+    }
+  };
+
+  float m_run = -CUDART_INF_F, l_run = 0.f;
+  bool o_zero = true;  // the O accumulator holds nothing yet (first PV overwrites)
+  if (n_tiles > 0 && warp == 0 && elect_one_sync()) issue_tile(0);
+
+  for (int j = 0; j < n_tiles; ++j) {
+    const int t0 = t_first + j * kBN;
+    if (j + 1 < n_tiles && warp == 0 && elect_one_sync()) issue_tile(j + 1);
+    bool ok = bar_wait_bounded(bar_t0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1));
+    // ---- dequantise: 512 items (K or V, token, 16-byte segment), two per thread -----------------
+    const unsigned char* stg = sm + kOffStage + (j & 1) * kStageBytes;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int tok = (tid >> 2) & 63, seg = tid & 3;
+      const uint4 pk = *reinterpret_cast<const uint4*>(stg + (tok >> 4) * 2048 + u * 1024 + (tok & 15) * 64 + seg * 16);
+      const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256;
+      const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+      unsigned char* dst = sm + (u ? kOffV : kOffK) + (seg >> 1) * 8192;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t x = w[c];
+        const uint4 o = make_uint4(lut[x & 255], lut[(x >> 8) & 255], lut[(x >> 16) & 255], lut[x >> 24]);
+        *reinterpret_cast<uint4*>(dst + swz(tok, (seg & 1) * 4 + c)) = o;
+      }
+    }
+    if (tid < 64) {  // norms of the tile's tokens
+      const unsigned char* nb = stg + 8192 + (tid >> 4) * 512 + (tid & 15) * 16 + n_sub;
+      const float kn = *reinterpret_cast<const float*>(nb), vn = *reinterpret_cast<const float*>(nb + 256);
+      float* ns = reinterpret_cast<float*>(sm + kOffNorm);
+      ns[tid] = kn;
+      ns[64 + tid] = vn;
+      ns[128 + tid] = fmaxf(lg2_approx(vn), -30.f);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (!ok) s_info[3] = 1;
+    __syncthreads();
+    if (s_info[3]) break;
+    // ---- S = Q K~^T ------------------------------------------------------------------------------
+    if (warp == 0 && elect_one_sync()) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const uint64_t db = desc_kmajor(base + kOffK + kb * 8192 + 32 * s);
+          mma_f16(tmem + kColS, desc_kmajor(base + kOffQlo + kb * 16384 + 32 * s), db, kDescS, (kb | s) ? 1u : 0u);
+          mma_f16(tmem + kColS, desc_kmajor(base + kOffQhi + kb * 16384 + 32 * s), db, kDescS, 1u);
+        }
+      mma_commit(bar_s);
+    }
+    // ---- softmax of the tile (threads 0..127) ----------------------------------------------------
+    if (tid < 128) {
+      ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s, (uint32_t)(j & 1)));
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm);
+      const uint32_t lane_base = tmem + ((uint32_t)(32 * warp) << 16);
+      float sc[64];
+      float mt = -CUDART_INF_F;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint32_t v[32];
+        if (ok) tmem_ld32(lane_base + kColS + 32 * q, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int t = 32 * q + i, pos = t0 + t;
+          const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
+          const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[t]) : -CUDART_INF_F;
+          sc[t] = s;
+          mt = fmaxf(mt, vis ? s + ns[128 + t] : -CUDART_INF_F);
+        }
+      }
+      // lazily updated reference: moves only when a score (shifted by log2 of its value norm)
+      // exceeds it by more than 2^8; then this row of O is rescaled in tensor memory
+      const bool bump = mt > m_run + 8.f;
+      if (__any_sync(0xffffffffu, bump)) {
+        const float alpha = bump ? (m_run == -CUDART_INF_F ? 0.f : ex2_approx(m_run - mt)) : 1.f;
+        if (bump) { m_run = mt; l_run *= alpha; }
+        if (!o_zero && ok) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t v[32];
+            tmem_ld32(lane_base + kColO + 32 * q, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st32(lane_base + kColO + 32 * q, v);
+          }
+        }
+      }
+      const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t h[4], lw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int t = 8 * c + 2 * e;
+          const float e0 = ex2_approx(sc[t] - m_use), e1 = ex2_approx(sc[t + 1] - m_use);
+          lsum += e0 + e1;
+          const float v0 = sc[t] == -CUDART_INF_F ? 0.f : e0 * ns[64 + t];
+          const float v1 = sc[t + 1] == -CUDART_INF_F ? 0.f : e1 * ns[64 + t + 1];
+          const float h0 = __half2float(__float2half_rn(v0)), h1 = __half2float(__float2half_rn(v1));
+          h[e] = pack_h2(h0, h1);
+          lw[e] = pack_h2(v0 - h0, v1 - h1);  // the fp16 rounding of the weights is recovered by a second term
+        }
+        *reinterpret_cast<uint4*>(sm + kOffP + swz(tid, c)) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(sm + kOffPlo + swz(tid, c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+      }
+      l_run += lsum;
+      if (!ok) s_info[3] = 1;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_info[3]) break;
+    // ---- O += P V~ -------------------------------------------------------------------------------
+    if (warp == 0 && elect_one_sync()) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint64_t dv = desc_mnmajor(base + kOffV + 2048 * s, 8192);
+        mma_f16(tmem + kColO, desc_kmajor(base + kOffPlo + 32 * s), dv, kDescO, (!o_zero || s) ? 1u : 0u);
+        mma_f16(tmem + kColO, desc_kmajor(base + kOffP + 32 * s), dv, kDescO, 1u);
+      }
+      mma_commit(bar_o);
+    }
+    o_zero = false;
+    ok = bar_wait_bounded(bar_o, (uint32_t)(j & 1));  // K~, V~, P and the tile stage are free again
+    if (!ok) s_info[3] = 1;
+    __syncthreads();
+    if (s_info[3]) break;
+  }
+
+  // ---- normalised rotated output + log-sum-exp, as one dense partial per (row, head) ------------
+  const bool dead = s_info[3] != 0;
+  if (tid < 128) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t lane_base = tmem + ((uint32_t)(32 * warp) << 16);
+    const bool have = !dead && !o_zero && l_run > 0.f;
+    const float inv = have ? 1.f / (a.lut_scale_v * l_run) : 0.f;
+    const int64_t vec = row_live ? (int64_t)(lr0 + my_r) * sh.Hq + kvh * G + my_g : 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t v[32];
+      if (!o_zero && !dead) {
+        tmem_ld32(lane_base + kColO + 32 * q, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (row_live) {
+        float4* dst = reinterpret_cast<float4*>(p.part_o + vec * kD + 32 * q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          dst[i] = make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
+                               __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+      }
+    }
+    if (row_live)
+      p.part_m[vec] = have ? (m_run + lg2_approx(l_run)) * 0.6931471805599453f : -CUDART_INF_F;
+  }
+  if (dead && tid == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+// dims (bytes of one half of a token row, tokens in a block, K/V half, blocks); box = 16 tokens x both halves
+bool make_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t half_bytes = (cuuint64_t)a.sh.Hkv * (a.sh.D / 2 + 4);
+  const cuuint64_t dims[4] = {half_bytes, (cuuint64_t)a.block_size, 2, (cuuint64_t)a.num_blocks};
+  const cuuint64_t strides[3] = {(cuuint64_t)a.cache_token_stride, half_bytes, (cuuint64_t)a.cache_block_stride};
+  const cuuint32_t box[4] = {box_bytes, 16, 2, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t*>(a.cache), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int G>
+int launch_t(const AttnArgs& a, cudaStream_t st) {
+  static bool attr_set = false;
+  const int smem = (int)kSmemBytes + 1024;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(prefill_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
+      return TQ4_ERR_CUDA;
+    attr_set = true;
+  }
+  CUtensorMap tm_idx, tm_norm;
+  memset(&tm_idx, 0, sizeof(tm_idx));
+  memset(&tm_norm, 0, sizeof(tm_norm));
+  if (!make_map(&tm_idx, a, 64) || !make_map(&tm_norm, a, 16)) return TQ4_ERR_UNSUPPORTED;
+  constexpr int RB = 128 / G;
+  const unsigned blocks = (unsigned)((a.sh.rows + RB - 1) / RB + a.sh.num_seqs);  // upper bound
+  if (launch_kernel(prefill_tc_kernel<G>, dim3(blocks, (unsigned)a.sh.Hkv), dim3(kThreads), (size_t)smem, st,
+                    true, a, tm_idx, tm_norm) != cudaSuccess)
+    return TQ4_ERR_CUDA;
+  TQ4_CHECK_LAUNCH();
+  return TQ4_OK;
+}
+
+}  // namespace
+
+// Shapes and layouts the tensor-core prefill kernel covers (everything else streams).
+bool prefill_tc_supported(const AttnArgs& a) {
+  static const bool disabled = getenv("TQ4_NO_TC") != nullptr;
+  const int G = a.sh.G;
+  const RowLayout lay = row_layout(a.sh.Hkv, a.sh.D);
+  return !disabled && a.sh.D == kD && (G == 1 || G == 2 || G == 4 || G == 8) && a.query_start_loc != nullptr &&
+         (uintptr_t)a.cache % 16 == 0 && a.cache_block_stride % 16 == 0 && a.cache_token_stride % 16 == 0 &&
+         a.block_size % 16 == 0 && a.block_size <= 256 && (a.block_size & (a.block_size - 1)) == 0 &&
+         lay.v_idx % 16 == 0 && a.num_blocks < (1ll << 31) && encode_fn() != nullptr;
+}
+
+int launch_prefill_tc(const AttnArgs& a, cudaStream_t st) {
+  switch (a.sh.G) {
+    case 1: return launch_t<1>(a, st);
+    case 2: return launch_t<2>(a, st);
+    case 4: return launch_t<4>(a, st);
+    case 8: return launch_t<8>(a, st);
+  }
+  return TQ4_ERR_UNSUPPORTED;
+}
+
+}  // namespace tq4
