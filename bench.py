@@ -309,6 +309,15 @@ def run_ours(args, rank, world, device):
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": round(e2e_ms / args.steps, 5), "cuda_graph": e2e_graph}
 
+    # ---- chunked prefill (BASELINE config 4 shape: 8 sequences x 2048 new tokens on an 8192-token
+    #      packed prefix, causal): tcgen05 kernel and, beside it, the streaming kernel -------------
+    prefill = None
+    if rank == 0 and world == 1 and not args.no_prefill:
+        try:
+            prefill = prefill_measurement(device, wl, ops)
+        except Exception as e:  # noqa: BLE001
+            prefill = {"error": f"{type(e).__name__}: {e}"[:200]}
+
     line = {
         "metric": "paged_tq4_decode_tok_per_s", "value": round(value, 1), "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -328,6 +337,7 @@ def run_ours(args, rank, world, device):
         "hbm_gbs": round(alg_bytes / (ms_step * 1e-3) / 1e9, 1),
         "compress_mtok_s": round(compress_mtok_s, 3),
         "compress_config": f"{nt} tokens x {hkv} KV heads, K and V, bf16 -> paged cache, one launch",
+        "prefill": prefill,
         "roofline": roofline, "e2e": e2e, "gpu_launches": (4 if args.separate_write else 3) * args.steps,
         "clocks": clocks,
     }
@@ -340,6 +350,46 @@ def run_ours(args, rank, world, device):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_budget)
     return line
+
+
+def prefill_measurement(device, wl, ops):
+    """8 sequences x 2048 new tokens attending causally over an 8192-token packed prefix + themselves
+    (32 q / 8 kv heads, head_dim 128, block 16, shuffled pages).  Reports ms and TFLOP/s
+    (4 * keys seen * head_dim * q_heads) of the tcgen05 kernel (mode 0 picks it) and of the streaming
+    kernel (mode 2)."""
+    hq, hkv, nseq, prefix, new = 32, 8, 8, 8192, 2048
+    total = prefix + new
+    nblk = nseq * total // BS
+    gen = torch.Generator(device=device).manual_seed(11)
+    cache = torch.zeros(nblk, BS, hkv * 256, dtype=torch.uint8, device=device)
+    bt = torch.randperm(nblk, device=device, generator=gen).view(nseq, total // BS).to(torch.int32)
+    slots = (bt.long()[:, :, None] * BS + torch.arange(BS, device=device)[None, None, :]).reshape(-1)
+    k = torch.randn(nseq * total, hkv, D, device=device, generator=gen).bfloat16()
+    v = torch.randn(nseq * total, hkv, D, device=device, generator=gen).bfloat16()
+    ops.tq4_write_paged(k, v, cache, slots, wl["even"], wl["odd"], wl["kb"], wl["vb"])
+    del k, v
+    q = torch.randn(nseq * new, hq, D, device=device, generator=gen).bfloat16()
+    qsl = (torch.arange(nseq + 1, device=device) * new).to(torch.int32)
+    sl = torch.full((nseq,), total, dtype=torch.int32, device=device)
+    keys = nseq * sum(prefix + i + 1 for i in range(new))
+    flops = 4.0 * keys * D * hq
+    res = {"config": f"{nseq} seqs x {new} new tokens on {prefix}-token packed prefix, causal, 32q/8kv, D=128"}
+    for name, mode, iters in (("tcgen05", 0, 5), ("streaming", 2, 2)):
+        def run():
+            return ops.paged_tq4_attention(q, cache, bt, sl, wl["kc"], wl["vc"], wl["rot"], hkv, BS,
+                                           query_start_loc=qsl, mode=mode)
+        run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        res[name] = {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
+                     "tokens_per_s": round(nseq * new / (ms * 1e-3), 1)}
+    return res
 
 
 # ----------------------------------------------------------------------------------------
@@ -504,6 +554,7 @@ def main():
     ap.add_argument("--no-bf16-baseline", action="store_true")
     ap.add_argument("--separate-write", action="store_true",
                     help="tq4_write_paged + attention as two calls (4 launches) instead of the fused step")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (no CUDA graph)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: run ONE rank's share of a W-GPU head-sharded job on this GPU")

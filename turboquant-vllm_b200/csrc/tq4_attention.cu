@@ -1107,7 +1107,7 @@ static int attention_impl(
   if (mode < 0 || mode > 3) return TQ4_ERR_INVALID_ARG;
   const bool use_mma = mode == 2 || mode == 3 || (mode == 0 && mma_ok);
   if (use_mma)
-    make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC, num_kv_heads));
+    make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC, num_kv_heads, cache_token_stride));
   const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
   if (workspace_bytes < carve_plan(a.plan, nullptr, rows_cap, num_q_heads, head_dim, a.sh.TPC))
     return TQ4_ERR_WORKSPACE;
@@ -1149,7 +1149,11 @@ static int attention_impl(
   // dequantisation of a key tile serves a whole block of query rows
   const bool prefill_ok = prefill_tc_supported(a);
   if (mode == 3 && !prefill_ok) return TQ4_ERR_UNSUPPORTED;
-  const bool use_prefill = mode == 3 || (mode == 0 && prefill_ok && num_rows >= 8 * (int64_t)num_seqs);
+  // (automatic only when the query blocks fill the GPU: a CTA owns a (row block, KV head) pair, a
+  // small chunk is spread wider by the streaming kernel)
+  const int64_t prefill_ctas = (num_rows * a.sh.G / 128) * num_kv_heads;
+  const bool use_prefill = mode == 3 || (mode == 0 && prefill_ok && num_rows >= 8 * (int64_t)num_seqs &&
+                                         2 * prefill_ctas >= sm_count());
 
   const int sms = sm_count();
   int ctas = (use_mma ? 1 : 4) * sms / a.sh.n_slices;

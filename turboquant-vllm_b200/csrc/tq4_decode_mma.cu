@@ -232,9 +232,12 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
                      const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_norm) {
   using C = MmaCfg<D, ALIGNED>;
-  constexpr bool VWIDE = BOX == 1, MERGED = BOX == 2;
+  constexpr bool VWIDE = BOX == 1, MERGED = BOX == 2, ROWBOX = BOX == 3;
+  constexpr bool V4B = VWIDE || ROWBOX;  // V chunks start on 4-byte (not 8/16-byte) boundaries
+  constexpr int kRowPitch = (D + 8 + 15) & ~15;  // ROWBOX: one box holds the whole row of the only KV head
   constexpr int kTmaKN = C::template tma_kn<VWIDE>(), kTmaVN = kTmaKN + 256;
-  constexpr int kTmaStage = C::template tma_stage<VWIDE>(), kVPitch = C::template v_pitch<VWIDE>();
+  constexpr int kTmaStage = ROWBOX ? 16 * kRowPitch : C::template tma_stage<VWIDE>();
+  constexpr int kVPitch = ROWBOX ? kRowPitch : C::template v_pitch<VWIDE>();
   constexpr int kStage = TMA ? kTmaStage : C::kStageBytes;
   const AttnShape& sh = a.sh;
   const AttnPlan& p = a.plan;
@@ -295,9 +298,13 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   //  * the 8-byte V reads of a half warp (rows sigma(2c) or sigma(2c+1) for c = 0..3, chunks 0-1
   //    or 2-3) need four rows that differ in (bit 0, bit 2),
   // which this permutation provides: every shared-memory read of a tile is conflict-free.
-  auto sigma = [](int k) { return (int)((0x65742130u >> (4 * (k & 7))) & 7u) + (k & 8); };  // 0,3,1,2,4,7,5,6
+  // (ROWBOX rows are 144 bytes apart and unswizzled: 0,2,4,6,1,3,5,7 keeps the 4-byte V reads at
+  // the unavoidable two wavefronts and the 16-byte K reads at three per two)
+  auto sigma = [](int k) {
+    return (int)(((ROWBOX ? 0x75316420u : 0x65742130u) >> (4 * (k & 7))) & 7u) + (k & 8);  // 0,3,1,2,4,7,5,6
+  };
   const int rg = sigma(g), rc0 = sigma(2 * c), rc1 = sigma(2 * c + 1);
-  constexpr bool SWZ = TMA && D == 128 && !VWIDE;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
+  constexpr bool SWZ = TMA && D == 128 && !VWIDE && !ROWBOX;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
   // byte offsets of this head's K norm / V indices / V norm relative to the 16-byte boundary below
   const int kn_sub = (row_layout(sh.Hkv, D).k_norm + 4 * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15;
   const int vn_sub = (row_layout(sh.Hkv, D).v_norm + 4 * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15;
@@ -308,11 +315,17 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   };
   // lane-constant byte offsets inside a TMA stage: K chunk of token sigma(g), V chunks of tokens
   // sigma(2c) / sigma(2c+1), norm columns of token sigma(g); tokens +8 are a fixed distance further
-  const uint32_t o_k = tile_off(rg, c * C::KBY);
-  const uint32_t o_v0 = C::kTmaV + (VWIDE ? rc0 * kVPitch + v_sub + g * C::VBY : tile_off(rc0, g * C::VBY));
-  const uint32_t o_v1 = C::kTmaV + (VWIDE ? rc1 * kVPitch + v_sub + g * C::VBY : tile_off(rc1, g * C::VBY));
-  const uint32_t o_kn = kTmaKN + rg * 16 + kn_sub, o_vn = kTmaKN + 256 + rg * 16 + vn_sub;
-  constexpr uint32_t kRow8 = 8 * (SWZ ? 64 : C::HALF), kVRow8 = 8 * (VWIDE ? kVPitch : (SWZ ? 64 : C::HALF));
+  // (ROWBOX: a stage row is the token row itself: [K idx D/2][K norm 4][V idx D/2][V norm 4])
+  const uint32_t o_k = ROWBOX ? rg * kRowPitch + c * C::KBY : tile_off(rg, c * C::KBY);
+  const uint32_t o_v0 = ROWBOX ? rc0 * kRowPitch + C::HALF + 4 + g * C::VBY
+                               : C::kTmaV + (VWIDE ? rc0 * kVPitch + v_sub + g * C::VBY : tile_off(rc0, g * C::VBY));
+  const uint32_t o_v1 = ROWBOX ? rc1 * kRowPitch + C::HALF + 4 + g * C::VBY
+                               : C::kTmaV + (VWIDE ? rc1 * kVPitch + v_sub + g * C::VBY : tile_off(rc1, g * C::VBY));
+  const uint32_t o_kn = ROWBOX ? rg * kRowPitch + C::HALF : kTmaKN + rg * 16 + kn_sub;
+  const uint32_t o_vn = ROWBOX ? rg * kRowPitch + D + 4 : kTmaKN + 256 + rg * 16 + vn_sub;
+  constexpr uint32_t kRow8 = 8 * (ROWBOX ? kRowPitch : (SWZ ? 64 : C::HALF));
+  constexpr uint32_t kVRow8 = 8 * (V4B ? kVPitch : (SWZ ? 64 : C::HALF));
+  constexpr uint32_t kNormRow8 = ROWBOX ? 8 * kRowPitch : 128;
   uint32_t gk = 0;      // tiles this warp has pushed through the ring (stage = gk % kStages)
   bool dead = false;    // a bounded wait gave up: stop issuing work, fall through to the end
 
@@ -525,10 +538,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     auto load_norms = [&](uint32_t sb, float (&nrm)[4]) {  // kn(g), kn(g+8), vn(g), vn(g+8)
       if (TMA) {
         lds_imm<4, 0>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm));
-        lds_imm<4, 128>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 1));
-        if (VWIDE) {  // the two norm regions may sit at different offsets inside their 16-byte columns
+        lds_imm<4, kNormRow8>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 1));
+        if (V4B) {  // the two norm regions may sit at different offsets inside their 16-byte columns
           lds_imm<4, 0>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 2));
-          lds_imm<4, 128>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 3));
+          lds_imm<4, kNormRow8>(sb + o_vn, reinterpret_cast<uint32_t*>(nrm + 3));
         } else {
           lds_imm<4, 256>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 2));
           lds_imm<4, 384>(sb + o_kn, reinterpret_cast<uint32_t*>(nrm + 3));
@@ -544,7 +557,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       for (int j = 0; j < 4; ++j) {
         if (TMA) {
           const uint32_t vo = sb + ((j & 1) ? o_v1 : o_v0);
-          if (VWIDE) {  // 4-byte reads: the chunk may start on any 4-byte boundary
+          if (V4B) {  // 4-byte reads: the chunk may start on any 4-byte boundary
 #pragma unroll
             for (int u = 0; u < C::VW; ++u) {
               if (j < 2) lds_imm<4, 0>(vo + 4 * u, vw[j] + u);
@@ -718,6 +731,9 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
                 tma_load_4d(sb + kStage, &tm_data, x_k, in_b, 0, bb, bar);
                 tma_load_4d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, 0, bb, bar);
               }
+            } else if (ROWBOX) {  // one box per tile: the 16 whole token rows of the only KV head
+              tma_load_3d(sb, &tm_data, 0, in_a, ba, bar);
+              if (two) tma_load_3d(sb + kStage, &tm_data, 0, in_b, bb, bar);
             } else {
               tma_load_3d(sb, &tm_data, x_k, in_a, ba, bar);
               tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_a, ba, bar);
@@ -936,6 +952,7 @@ constexpr int kErrNoHalvesMap = -1000;  // internal: the 4-D map could not be en
 template <int D, int NB, bool ALIGNED, bool PAGE16, bool TMA, int BOX>
 int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   constexpr bool VWIDE = BOX == 1;
+  constexpr int kRowPitch = (D + 8 + 15) & ~15;
   constexpr int WARPS = (D * NB <= 128) ? 16 : 8;  // upper bound; the launch uses HPC * TPC warps
   using C = MmaCfg<D, ALIGNED>;
   // All opt-in shared memory of the SM (one CTA per SM by design): the 64 KB table sits on a
@@ -949,7 +966,7 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return TQ4_ERR_CUDA;
     const int want = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
-    const int stage = TMA ? C::template tma_stage<VWIDE>() : C::kStageBytes;
+    const int stage = TMA ? (BOX == 3 ? 16 * kRowPitch : C::template tma_stage<VWIDE>()) : C::kStageBytes;
     if (want < (int)kTableBytes + a.sh.HPC * a.sh.TPC * kStages * 2 * stage) return TQ4_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
       return TQ4_ERR_CUDA;
@@ -959,7 +976,9 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   memset(&tm_data, 0, sizeof(tm_data));
   memset(&tm_v, 0, sizeof(tm_v));
   memset(&tm_norm, 0, sizeof(tm_norm));
-  if (TMA && BOX == 2) {
+  if (TMA && BOX == 3) {
+    if (!make_cache_map(&tm_data, a, kRowPitch, false)) return TQ4_ERR_CUDA;
+  } else if (TMA && BOX == 2) {
     if (!make_cache_map_halves(&tm_data, a, D / 2, D == 128) || !make_cache_map_halves(&tm_norm, a, 16, false))
       return kErrNoHalvesMap;
   } else if (TMA && (!make_cache_map(&tm_data, a, D / 2, D == 128 && !VWIDE) ||
@@ -993,6 +1012,10 @@ bool cache_tma_ok(const AttnArgs& a) {
          a.cache_token_stride >= (int64_t)((row_data_bytes(a.sh.Hkv, a.sh.D) + 15) & ~15) &&
          a.num_blocks < (1ll << 31) && getenv("TQ4_NO_TMA") == nullptr && encode_tiled_fn() != nullptr;
 }
+// a single KV head (e.g. one rank of an 8-way head-sharded Llama): the whole token row fits one box
+bool rowbox_ok(int Hkv, int D, int64_t token_stride) {
+  return Hkv == 1 && (D == 64 || D == 128) && token_stride >= ((D + 8 + 15) & ~15);
+}
 bool cache_v_aligned16(const AttnArgs& a) {
   const RowLayout lay = row_layout(a.sh.Hkv, a.sh.D);
   return lay.v_idx % 16 == 0;
@@ -1012,6 +1035,8 @@ int launch_mma_dn(const AttnArgs& a, cudaStream_t st) {
       }
       return launch_mma_t<D, NB, true, true, (D != 96), 0>(a, st);
     }
+    if (rowbox_ok(a.sh.Hkv, D, a.cache_token_stride))
+      return launch_mma_t<D, NB, true, true, (D != 96), (D == 64 || D == 128) ? 3 : 0>(a, st);
     return launch_mma_t<D, NB, true, true, (D != 96), (D != 96) ? 1 : 0>(a, st);
   }
   if (aligned && page16) return launch_mma_t<D, NB, true, true, false, false>(a, st);
@@ -1027,8 +1052,9 @@ int launch_mma_d(const AttnArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-int mma_warps_per_cta(int D, int GC, int Hkv) {
+int mma_warps_per_cta(int D, int GC, int Hkv, int64_t token_stride) {
   if (D * (GC <= 4 ? 1 : 2) > 128) return 8;
+  if (rowbox_ok(Hkv, D, token_stride)) return 16;
   return Hkv % 4 == 0 ? 16 : 12;  // wider V tiles need more ring space per warp
 }
 

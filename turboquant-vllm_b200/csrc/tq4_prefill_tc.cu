@@ -13,7 +13,8 @@
 //   O += Plo V~ + Phi V~      (tcgen05.mma 128 x 128 x 16, V~ as an MN-major B operand)
 // At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
 // layout of one dense partial per row; the merge kernel un-rotates and stores them.
-// The phases of a tile run one after the other (block-wide barriers); every wait is bounded.
+// Warps 0-3 own the S / O rows (softmax, rescale, epilogue); warps 4-7 dequantise the next tile
+// into the other K~ / V~ buffer meanwhile; one thread issues the MMAs.  Every wait is bounded.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -34,15 +35,15 @@ constexpr uint32_t kColS = 0, kColO = 64;
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffQhi = 0;                       // 2 K-blocks x [128 rows][128 B]
 constexpr uint32_t kOffQlo = 32768;
-constexpr uint32_t kOffK = 65536;                     // 2 K-blocks x [64 tok][128 B]
-constexpr uint32_t kOffV = kOffK + 16384;             // 2 MN-blocks x [64 tok][128 B]
-constexpr uint32_t kOffP = kOffV + 16384;             // [128 rows][128 B] fp16 hi part of p * vnorm
+constexpr uint32_t kOffK = 65536;                     // 2 buffers x 2 K-blocks x [64 tok][128 B]
+constexpr uint32_t kOffV = kOffK + 32768;             // 2 buffers x 2 MN-blocks x [64 tok][128 B]
+constexpr uint32_t kOffP = kOffV + 32768;             // [128 rows][128 B] fp16 hi part of p * vnorm
 constexpr uint32_t kOffPlo = kOffP + 16384;           // ... and its fp16 remainder
 constexpr uint32_t kOffStage = kOffPlo + 16384;       // 2 x (4 pages x 2048 B indices + 4 x 512 B norms)
 constexpr uint32_t kStageBytes = 4 * 2048 + 4 * 512;
 constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // K table, V table: 256 x 4 B each
-constexpr uint32_t kOffNorm = kOffLut + 2048;               // kn[64], vn[64], lg[64]
-constexpr uint32_t kSmemBytes = kOffNorm + 3 * 64 * 4;
+constexpr uint32_t kOffNorm = kOffLut + 2048;               // 2 buffers x (kn[64], vn[64], lg[64])
+constexpr uint32_t kSmemBytes = kOffNorm + 2 * 3 * 64 * 4;
 
 // instruction descriptors (kind::f16, fp16 operands, fp32 accumulator, M = 128)
 constexpr uint32_t kDescS = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);                // N = 64, B K-major
@@ -292,23 +293,17 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     }
   };
 
-  float m_run = -CUDART_INF_F, l_run = 0.f;
-  bool o_zero = true;  // the O accumulator holds nothing yet (first PV overwrites)
-  if (n_tiles > 0 && warp == 0 && elect_one_sync()) issue_tile(0);
-
-  for (int j = 0; j < n_tiles; ++j) {
-    const int t0 = t_first + j * kBN;
-    if (j + 1 < n_tiles && warp == 0 && elect_one_sync()) issue_tile(j + 1);
-    bool ok = bar_wait_bounded(bar_t0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1));
-    // ---- dequantise: 512 items (K or V, token, 16-byte segment), two per thread -----------------
+  // ---- dequantise tile j (its packed stage has landed) into buffer j & 1: 512 items
+  //      (K or V, token, 16-byte segment) spread over threads t of nt; norms by the first 64 --------
+  auto dequant_tile = [&](int j, int t, int nt) {
     const unsigned char* stg = sm + kOffStage + (j & 1) * kStageBytes;
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int tok = (tid >> 2) & 63, seg = tid & 3;
+    const uint32_t kv_off = (uint32_t)(j & 1) * 16384u;
+    for (int item = t; item < 512; item += nt) {
+      const int u = item >> 8, tok = (item >> 2) & 63, seg = item & 3;
       const uint4 pk = *reinterpret_cast<const uint4*>(stg + (tok >> 4) * 2048 + u * 1024 + (tok & 15) * 64 + seg * 16);
       const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256;
       const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
-      unsigned char* dst = sm + (u ? kOffV : kOffK) + (seg >> 1) * 8192;
+      unsigned char* dst = sm + (u ? kOffV : kOffK) + kv_off + (seg >> 1) * 8192;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const uint32_t x = w[c];
@@ -316,37 +311,65 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         *reinterpret_cast<uint4*>(dst + swz(tok, (seg & 1) * 4 + c)) = o;
       }
     }
-    if (tid < 64) {  // norms of the tile's tokens
-      const unsigned char* nb = stg + 8192 + (tid >> 4) * 512 + (tid & 15) * 16 + n_sub;
+    if (t < 64) {
+      const unsigned char* nb = stg + 8192 + (t >> 4) * 512 + (t & 15) * 16 + n_sub;
       const float kn = *reinterpret_cast<const float*>(nb), vn = *reinterpret_cast<const float*>(nb + 256);
-      float* ns = reinterpret_cast<float*>(sm + kOffNorm);
-      ns[tid] = kn;
-      ns[64 + tid] = vn;
-      ns[128 + tid] = fmaxf(lg2_approx(vn), -30.f);
+      float* ns = reinterpret_cast<float*>(sm + kOffNorm) + (j & 1) * 192;
+      ns[t] = kn;
+      ns[64 + t] = vn;
+      ns[128 + t] = fmaxf(lg2_approx(vn), -30.f);
     }
+  };
+  auto issue_s = [&](int j) {  // S = Q K~^T of tile j (one thread)
+    const uint32_t kb_base = base + kOffK + (uint32_t)(j & 1) * 16384u;
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint64_t db = desc_kmajor(kb_base + kb * 8192 + 32 * s);
+        mma_f16(tmem + kColS, desc_kmajor(base + kOffQlo + kb * 16384 + 32 * s), db, kDescS, (kb | s) ? 1u : 0u);
+        mma_f16(tmem + kColS, desc_kmajor(base + kOffQhi + kb * 16384 + 32 * s), db, kDescS, 1u);
+      }
+    mma_commit(bar_s);
+  };
+
+  float m_run = -CUDART_INF_F, l_run = 0.f;
+  bool o_zero = true;  // the O accumulator holds nothing yet (first PV overwrites)
+  // ---- pipeline fill: tiles 0 and 1 in flight, tile 0 dequantised by everybody, S_0 issued ---------
+  if (n_tiles > 0) {
+    if (warp == 0 && elect_one_sync()) {
+      issue_tile(0);
+      if (n_tiles > 1) issue_tile(1);
+    }
+    const bool ok0 = bar_wait_bounded(bar_t0, 0u);
+    dequant_tile(0, tid, kThreads);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    if (!ok) s_info[3] = 1;
+    if (!ok0) s_info[3] = 1;
     __syncthreads();
-    if (s_info[3]) break;
-    // ---- S = Q K~^T ------------------------------------------------------------------------------
-    if (warp == 0 && elect_one_sync()) {
+    if (!s_info[3] && warp == 0 && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          const uint64_t db = desc_kmajor(base + kOffK + kb * 8192 + 32 * s);
-          mma_f16(tmem + kColS, desc_kmajor(base + kOffQlo + kb * 16384 + 32 * s), db, kDescS, (kb | s) ? 1u : 0u);
-          mma_f16(tmem + kColS, desc_kmajor(base + kOffQhi + kb * 16384 + 32 * s), db, kDescS, 1u);
-        }
-      mma_commit(bar_s);
+      issue_s(0);
     }
-    // ---- softmax of the tile (threads 0..127) ----------------------------------------------------
-    if (tid < 128) {
+  }
+
+  // ---- per tile: warps 0-3 turn S_j into P_j while warps 4-7 dequantise tile j+1; then one thread
+  //      issues S_{j+1} and O += P_j V~_j ----------------------------------------------------------------
+  for (int j = 0; j < n_tiles && !s_info[3]; ++j) {
+    const int t0 = t_first + j * kBN;
+    bool ok = true;
+    if (tid >= 128) {
+      // buffer (j+1) & 1 was read by the MMAs of tile j-1: wait for them, then refill it
+      if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1));
+      if (j + 1 < n_tiles) {
+        ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
+        dequant_tile(j + 1, tid - 128, 128);
+      }
+      if (!ok) s_info[3] = 1;
+    } else {
       ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s, (uint32_t)(j & 1)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm);
+      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192;
       const uint32_t lane_base = tmem + ((uint32_t)(32 * warp) << 16);
       float sc[64];
       float mt = -CUDART_INF_F;
@@ -363,6 +386,9 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
           mt = fmaxf(mt, vis ? s + ns[128 + t] : -CUDART_INF_F);
         }
       }
+      // P and O are still in use by the MMAs of tile j-1
+      if (j >= 1) ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1))) && ok;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // lazily updated reference: moves only when a score (shifted by log2 of its value norm)
       // exceeds it by more than 2^8; then this row of O is rescaled in tensor memory
       const bool bump = mt > m_run + 8.f;
@@ -406,23 +432,26 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (s_info[3]) break;
-    // ---- O += P V~ -------------------------------------------------------------------------------
     if (warp == 0 && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (j + 1 < n_tiles) issue_s(j + 1);  // first: the softmax warps wait for it
+      const uint32_t vb = base + kOffV + (uint32_t)(j & 1) * 16384u;
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
-        const uint64_t dv = desc_mnmajor(base + kOffV + 2048 * s, 8192);
+        const uint64_t dv = desc_mnmajor(vb + 2048 * s, 8192);
         mma_f16(tmem + kColO, desc_kmajor(base + kOffPlo + 32 * s), dv, kDescO, (!o_zero || s) ? 1u : 0u);
         mma_f16(tmem + kColO, desc_kmajor(base + kOffP + 32 * s), dv, kDescO, 1u);
       }
       mma_commit(bar_o);
+      // the packed stage of tile j was dequantised one iteration ago: refill it with tile j + 2
+      if (j + 2 < n_tiles) issue_tile(j + 2);
     }
     o_zero = false;
-    ok = bar_wait_bounded(bar_o, (uint32_t)(j & 1));  // K~, V~, P and the tile stage are free again
-    if (!ok) s_info[3] = 1;
-    __syncthreads();
-    if (s_info[3]) break;
   }
+  if (n_tiles > 0 && !s_info[3]) {  // the last tile's MMAs
+    if (!bar_wait_bounded(bar_o, (uint32_t)((n_tiles - 1) & 1))) s_info[3] = 1;
+  }
+  __syncthreads();
 
   // ---- normalised rotated output + log-sum-exp, as one dense partial per (row, head) ------------
   const bool dead = s_info[3] != 0;
