@@ -150,7 +150,9 @@ size_t tq4_attention_workspace_bytes(int64_t max_query_rows, int num_q_heads, in
  *              (-inf for a row that sees no key); with out_rotated != 0 the output stays in
  *              rotated space (normalised) for a later cross-GPU combine.
  * workspace    >= tq4_attention_workspace_bytes(num_rows, Hq, Hkv, D), 16-byte aligned
- * mode         0 = auto, 1 = fp32 CUDA-core kernel, 2 = tensor-core LUT kernel
+ * mode         0 = auto, 1 = fp32 CUDA-core kernel, 2 = streaming tensor-core LUT kernel (mma.sync),
+ *              3 = chunked-prefill tcgen05 kernel (needs query_start_loc, head_dim 128, 16-byte
+ *              aligned K/V regions; TQ4_ERR_UNSUPPORTED otherwise)
  * A row that sees no key (seq_len 0) gets zeros.
  */
 int tq4_paged_attention(const void* q, int q_dtype, int64_t num_rows, int num_seqs,

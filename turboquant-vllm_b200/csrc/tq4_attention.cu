@@ -102,7 +102,7 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
     run += nt;
   }
   const int total = s_total;
-  const int tps = max(1, (total + sh.ctas - 1) / sh.ctas);
+  const int tps = max(1, (total + sh.span_ctas - 1) / sh.span_ctas);
   __syncthreads();
   local = 0;
   for (int r = r_lo; r < r_hi; ++r) {
@@ -1066,7 +1066,7 @@ extern "C" size_t tq4_attention_workspace_bytes(int64_t max_query_rows, int num_
   tq4::AttnPlan p;
   const size_t a = tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, sh.TPC);
   tq4::make_shape(sh, num_q_heads, num_kv_heads, head_dim, tq4::kMmaWarpsPerCta);
-  const size_t b = tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, sh.TPC);
+  const size_t b = tq4::carve_plan(p, nullptr, rows, num_q_heads, head_dim, 1, (int64_t)tq4::kMaxSms * sh.TPC);
   return a > b ? a : b;
 }
 
@@ -1109,9 +1109,12 @@ static int attention_impl(
   if (use_mma)
     make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC, num_kv_heads, cache_token_stride));
   const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
-  if (workspace_bytes < carve_plan(a.plan, nullptr, rows_cap, num_q_heads, head_dim, a.sh.TPC))
+  // tensor-core kernel: one partial per (row, span), one span per warp phase of every CTA
+  const int part_tpc = use_mma ? 1 : a.sh.TPC;
+  const int64_t max_spans = use_mma ? (int64_t)kMaxSms * a.sh.TPC : kMaxCtasPerSlice;
+  if (workspace_bytes < carve_plan(a.plan, nullptr, rows_cap, num_q_heads, head_dim, part_tpc, max_spans))
     return TQ4_ERR_WORKSPACE;
-  carve_plan(a.plan, workspace, rows_cap, num_q_heads, head_dim, a.sh.TPC);
+  carve_plan(a.plan, workspace, rows_cap, num_q_heads, head_dim, part_tpc, max_spans);
 
   a.sh.num_seqs = num_seqs;
   a.q = q;
@@ -1159,7 +1162,10 @@ static int attention_impl(
   int ctas = (use_mma ? 1 : 4) * sms / a.sh.n_slices;
   if (ctas < 1) ctas = 1;
   if (ctas > kMaxCtasPerSlice) ctas = kMaxCtasPerSlice;
+  if (use_mma && ctas > kMaxSms) ctas = kMaxSms;
   a.sh.ctas = ctas;
+  a.sh.span_ctas = use_mma ? ctas * a.sh.TPC : ctas;
+  a.sh.part_tpc = part_tpc;
   cudaStream_t st = (cudaStream_t)stream;
 
   for (int64_t r0 = 0; r0 < num_rows; r0 += kMaxRowsPerLaunch) {
@@ -1177,7 +1183,7 @@ static int attention_impl(
     CombineArgs c{};
     c.slot_base = use_prefill ? nullptr : a.plan.slot_base;  // prefill: one dense partial per row
     c.world = 1;
-    c.TPC = a.sh.TPC;
+    c.TPC = a.sh.part_tpc;
     c.part_o = a.plan.part_o;
     c.part_m = a.plan.part_m;
     c.part_l = a.plan.part_l;

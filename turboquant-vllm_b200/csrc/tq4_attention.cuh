@@ -19,7 +19,8 @@ namespace tq4 {
 constexpr int kTileTokens = 16;
 constexpr int kMaxWarpsPerCta = 8;     // fp32 kernel
 constexpr int kMmaWarpsPerCta = 16;    // tensor-core LUT kernel (one CTA per SM)
-constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace sizing
+constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace sizing (fp32 kernel)
+constexpr int kMaxSms = 160;               // tensor-core kernel: one CTA per SM, one span per warp phase
 constexpr int kMaxRowsPerLaunch = 4096;    // larger query batches are processed in pieces
 
 struct AttnPlan {
@@ -45,6 +46,9 @@ struct AttnShape {
   int TPC;        // tile phases per CTA (warps per virtual head)
   int n_slices;   // VH / HPC
   int ctas;       // CTAs per slice
+  int span_ctas;  // equal spans the tile stream of a slice is cut into (fp32 kernel: ctas; tensor-core
+                  // kernel: ctas * TPC, every warp phase streams its own contiguous span)
+  int part_tpc;   // partials per slot (fp32 kernel: TPC, tensor-core kernel: 1)
 };
 
 struct AttnArgs {
@@ -94,8 +98,9 @@ inline bool make_shape(AttnShape& s, int Hq, int Hkv, int D, int max_warps = kMa
 }
 
 // Carve the workspace.  Returns the number of bytes used.
-inline size_t carve_plan(AttnPlan& p, void* ws, int64_t rows, int Hq, int D, int TPC) {
-  const int64_t slots = rows + kMaxCtasPerSlice;
+inline size_t carve_plan(AttnPlan& p, void* ws, int64_t rows, int Hq, int D, int TPC,
+                         int64_t max_spans = kMaxCtasPerSlice) {
+  const int64_t slots = rows + max_spans;
   unsigned char* b = reinterpret_cast<unsigned char*>(ws);
   size_t off = 0;
   auto take = [&](size_t bytes) {

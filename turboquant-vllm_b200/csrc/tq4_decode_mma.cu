@@ -334,8 +334,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   const int kvh = vh / sh.NCH, chunk = vh % sh.NCH;
   const int qh0 = kvh * sh.G + chunk * sh.GC;
   const int gcount = min(sh.GC, sh.G - chunk * sh.GC);
+  // every warp phase streams its own contiguous span of the tile stream: span index = cta * TPC + ts
+  const int span = cta * sh.TPC + ts;
   const int total = p.scalars[0], tps = p.scalars[1];
-  const int t_begin = cta * tps, t_end = min(total, t_begin + tps);
+  const int t_begin = span * tps, t_end = min(total, t_begin + tps);
   if (t_begin >= t_end) return;
   const RowLayout lay = row_layout(sh.Hkv, D);
   const int k_off = lay.k_idx + kvh * C::HALF + c * C::KBY;  // this thread's K chunk
@@ -704,8 +706,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     // additions; block-table reads past the segment are clamped to its last tile (never issued).
     if constexpr (TMA) {
       static_assert(kStages == 2, "the TMA loop alternates between two stages");
-      const int step = 2 * sh.TPC;
-      const int first = t + 2 * ts;
+      const int step = 2;
+      const int first = t;
       const int n_pairs = (first < seg_end && !dead) ? (seg_end - first + step - 1) / step : 0;
       if (n_pairs > 0) {
         const int step_tok = step * kTileTokens;
@@ -782,8 +784,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     } else
     // ---- stream the segment: kStages ring stages of one tile pair each; block ids one pair ahead ----
     {
-      const int step = 2 * sh.TPC;
-      const int first = t + 2 * ts;
+      const int step = 2;
+      const int first = t;
       const int n_pairs = (first < seg_end && !dead) ? (seg_end - first + step - 1) / step : 0;
       auto blk_of = [&](int tt) -> int { return (PAGE16 && tt < seg_end) ? __ldg(bt + page_of(pos0_of(tt))) : 0; };
       // issue both tiles of pair index pi into its ring stage; returns the pair's 2 validity bits
@@ -867,8 +869,8 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     }
 
     // ---- write this warp's partial for the segment ---------------------------------------------
-    const int slot = p.slot_base[r] + (cta - row_t0 / tps);
-    const int64_t pidx = (int64_t)slot * sh.TPC + ts;
+    const int slot = p.slot_base[r] + (span - row_t0 / tps);
+    const int64_t pidx = slot;
     const float inv_av = 1.f / a.lut_scale_v;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
