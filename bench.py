@@ -281,33 +281,49 @@ def run_ours(args, rank, world, device):
     # restore the rows the compress timing overwrote is unnecessary: bytes stay valid TQ4 rows
 
     # ---- end to end through the public API with host buffers ------------------------------------
-    q_d, k_d, v_d = torch.empty_like(q), torch.empty_like(k_new), torch.empty_like(v_new)
+    # Every step copies its six inputs from pinned host memory and its output back.  The copies of
+    # step i+1 run on a second stream while step i computes (two sets of device input buffers), as a
+    # serving engine stages the next step's inputs; the join at the end of a step orders them before
+    # the next step.  --e2e-serial puts everything on one stream.
     slots_h = wl["new_slots"].cpu().pin_memory()
     bt_h = wl["block_table"].cpu().pin_memory()
     sl_h = wl["seq_lens"].cpu().pin_memory()
-    slots_d, bt_d, sl_d = torch.empty_like(wl["new_slots"]), torch.empty_like(wl["block_table"]), torch.empty_like(wl["seq_lens"])
+    host_in = (wl["q_host"], wl["k_host"], wl["v_host"], slots_h, bt_h, sl_h)
+    dev_in = [tuple(torch.empty_like(x, device=device) for x in host_in) for _ in range(2)]
     out_h = torch.empty(batch, hq, D, dtype=torch.bfloat16).pin_memory()
+    copy_stream = torch.cuda.Stream()
+
+    def h2d(bufs):
+        for d_, h_ in zip(bufs, host_in):
+            d_.copy_(h_, non_blocking=True)
 
     def e2e_step(i):
-        q_d.copy_(wl["q_host"], non_blocking=True)
-        k_d.copy_(wl["k_host"], non_blocking=True)
-        v_d.copy_(wl["v_host"], non_blocking=True)
-        slots_d.copy_(slots_h, non_blocking=True)
-        bt_d.copy_(bt_h, non_blocking=True)
-        sl_d.copy_(sl_h, non_blocking=True)
-        step(i, q_d, k_d, v_d, slots_d, bt_d, sl_d)
+        cur_bufs, next_bufs = dev_in[i % 2], dev_in[(i + 1) % 2]
+        if args.e2e_serial:
+            h2d(cur_bufs)
+            step(i, *cur_bufs)
+            out_h.copy_(out, non_blocking=True)
+            return
+        cur = torch.cuda.current_stream()
+        copy_stream.wait_stream(cur)  # fork: the previous step (which read next_bufs) is ordered before
+        with torch.cuda.stream(copy_stream):
+            h2d(next_bufs)            # inputs of step i + 1
+        step(i, *cur_bufs)            # inputs of step i were staged during step i - 1
         out_h.copy_(out, non_blocking=True)
+        cur.wait_stream(copy_stream)  # join
 
+    h2d(dev_in[0])
     for i in range(3):
         e2e_step(i)
     run_e2e, e2e_graph = graphed(e2e_step)
     run_e2e(3)
     e2e_ms = timed(lambda i: run_e2e(args.steps) if i == 0 else None, 1)
-    h2d = sum(x.numel() * x.element_size() for x in (wl["q_host"], wl["k_host"], wl["v_host"], slots_h, bt_h, sl_h))
+    h2d_bytes = sum(x.numel() * x.element_size() for x in host_in)
     d2h = out_h.numel() * out_h.element_size()
     e2e = {"value": round(batch * args.steps / (e2e_ms * 1e-3), 1), "unit": "tok/s",
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "ms_per_step": round(e2e_ms / args.steps, 5), "cuda_graph": e2e_graph}
+           "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h,
+           "ms_per_step": round(e2e_ms / args.steps, 5), "cuda_graph": e2e_graph,
+           "copies": "serial" if args.e2e_serial else "inputs of step i+1 staged on a second stream during step i"}
 
     # ---- chunked prefill (BASELINE config 4 shape: 8 sequences x 2048 new tokens on an 8192-token
     #      packed prefix, causal): tcgen05 kernel and, beside it, the streaming kernel -------------
@@ -554,6 +570,8 @@ def main():
     ap.add_argument("--no-bf16-baseline", action="store_true")
     ap.add_argument("--separate-write", action="store_true",
                     help="tq4_write_paged + attention as two calls (4 launches) instead of the fused step")
+    ap.add_argument("--e2e-serial", action="store_true",
+                    help="end-to-end: copies and kernels of a step on one stream (no staging of the next step)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (no CUDA graph)")
     ap.add_argument("--emulate-world", type=int, default=0,

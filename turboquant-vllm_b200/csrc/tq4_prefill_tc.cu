@@ -13,8 +13,9 @@
 //   O += Plo V~ + Phi V~      (tcgen05.mma 128 x 128 x 16, V~ as an MN-major B operand)
 // At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
 // layout of one dense partial per row; the merge kernel un-rotates and stores them.
-// Warps 0-3 own the S / O rows (softmax, rescale, epilogue); warps 4-7 dequantise the next tile
-// into the other K~ / V~ buffer meanwhile; one thread issues the MMAs.  Every wait is bounded.
+// Warps 0-7 own the S / O rows, two threads per row (softmax, rescale, epilogue); warps 8-11
+// dequantise the next tile into the other K~ / V~ buffer meanwhile and one of their threads issues
+// the TMA copies and the MMAs.  Every wait is bounded.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -28,7 +29,7 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBN = 64;                 // tokens per tile
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;             // warps 0-7: softmax (two threads per row), warps 8-11: dequantise, issue
 constexpr uint32_t kTmemCols = 256;     // S: columns [0, 64), O: columns [64, 192)
 constexpr uint32_t kColS = 0, kColO = 64;
 
@@ -43,7 +44,8 @@ constexpr uint32_t kOffStage = kOffPlo + 16384;       // 2 x (4 pages x 2048 B i
 constexpr uint32_t kStageBytes = 4 * 2048 + 4 * 512;
 constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // K table, V table: 256 x 4 B each
 constexpr uint32_t kOffNorm = kOffLut + 2048;               // 2 buffers x (kn[64], vn[64], lg[64])
-constexpr uint32_t kSmemBytes = kOffNorm + 2 * 3 * 64 * 4;
+constexpr uint32_t kOffXchg = kOffNorm + 2 * 3 * 64 * 4;     // [2 halves][128 rows] floats exchanged by a row's two threads
+constexpr uint32_t kSmemBytes = kOffXchg + 2 * 128 * 4;
 
 // instruction descriptors (kind::f16, fp16 operands, fp32 accumulator, M = 128)
 constexpr uint32_t kDescS = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);                // N = 64, B K-major
@@ -212,8 +214,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     }
   }
   // ---- the block's queries: row m = r * G + g, scaled by 1 / max|q|, split into fp16 hi + lo -----
-  float qscale = 0.f;  // (threads 0..127, their own row) max|q| * sm_scale * log2(e) / alpha_k
-  {
+  float qscale = 0.f;  // (softmax threads, their row) max|q| * sm_scale * log2(e) / alpha_k
+  if (tid < 256) {
     const int m = tid >> 1, kb = tid & 1;  // two threads per row, one 64-column K-block each
     const int r = m / G, g = m - r * G;
     float v[64];
@@ -256,12 +258,16 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = s_tmem;
-  if (tid < 128) qscale = reinterpret_cast<const float*>(sm + kOffP)[tid];
+  // ---- softmax threads: warps 0-7; row = TMEM lane = 32 * (warp & 3) + lane, column half = warp >> 2
+  const bool smx = tid < 256;
+  const int row = 32 * (warp & 3) + lane, hf = (warp >> 2) & 1;
+  if (smx) qscale = reinterpret_cast<const float*>(sm + kOffP)[row];
   __syncthreads();  // the P area is reused below
-
-  // ---- this thread's row (softmax threads: 0..127, row = TMEM lane) ----------------------------
-  const int my_r = tid < 128 ? tid / G : 0, my_g = tid < 128 ? tid % G : 0;
-  const bool row_live = tid < 128 && my_r < nrows;
+  const int my_r = row / G, my_g = row % G;
+  const bool row_live = smx && my_r < nrows;
+  float* xchg = reinterpret_cast<float*>(sm + kOffXchg);
+  // the two threads of a row sit in warps w and w + 4: a 64-thread named barrier per warp pair
+  auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory"); };
   const int kv_lo = row_live ? p.kv_start[lr0 + my_r] : 0;
   const int kv_hi = row_live ? p.kv_end[lr0 + my_r] : 0;
   // keys the block needs: rows are in query order, ranges move forward with the row
@@ -337,7 +343,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   bool o_zero = true;  // the O accumulator holds nothing yet (first PV overwrites)
   // ---- pipeline fill: tiles 0 and 1 in flight, tile 0 dequantised by everybody, S_0 issued ---------
   if (n_tiles > 0) {
-    if (warp == 0 && elect_one_sync()) {
+    if (warp == 8 && elect_one_sync()) {
       issue_tile(0);
       if (n_tiles > 1) issue_tile(1);
     }
@@ -347,7 +353,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (!ok0) s_info[3] = 1;
     __syncthreads();
-    if (!s_info[3] && warp == 0 && elect_one_sync()) {
+    if (!s_info[3] && warp == 8 && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       issue_s(0);
     }
@@ -358,34 +364,37 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   for (int j = 0; j < n_tiles && !s_info[3]; ++j) {
     const int t0 = t_first + j * kBN;
     bool ok = true;
-    if (tid >= 128) {
+    if (!smx) {
       // buffer (j+1) & 1 was read by the MMAs of tile j-1: wait for them, then refill it
       if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1));
       if (j + 1 < n_tiles) {
         ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
-        dequant_tile(j + 1, tid - 128, 128);
+        dequant_tile(j + 1, tid - 256, 128);
       }
       if (!ok) s_info[3] = 1;
     } else {
       ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s, (uint32_t)(j & 1)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192;
-      const uint32_t lane_base = tmem + ((uint32_t)(32 * warp) << 16);
-      float sc[64];
+      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
+      const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+      float sc[32];
       float mt = -CUDART_INF_F;
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
+      {
         uint32_t v[32];
-        if (ok) tmem_ld32(lane_base + kColS + 32 * q, v);
+        if (ok) tmem_ld32(lane_base + kColS + 32 * hf, v);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int t = 32 * q + i, pos = t0 + t;
+          const int pos = t0 + 32 * hf + i;
           const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
-          const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[t]) : -CUDART_INF_F;
-          sc[t] = s;
-          mt = fmaxf(mt, vis ? s + ns[128 + t] : -CUDART_INF_F);
+          const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[i]) : -CUDART_INF_F;
+          sc[i] = s;
+          mt = fmaxf(mt, vis ? s + ns[128 + i] : -CUDART_INF_F);
         }
       }
+      // the row's maximum over both halves (the decisions below must agree in its two threads)
+      xchg[hf * 128 + row] = mt;
+      pair_sync();
+      mt = fmaxf(mt, xchg[(hf ^ 1) * 128 + row]);
       // P and O are still in use by the MMAs of tile j-1
       if (j >= 1) ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1))) && ok;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -397,19 +406,19 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         if (bump) { m_run = mt; l_run *= alpha; }
         if (!o_zero && ok) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 2; ++q) {  // this thread's 64 of the row's 128 columns
             uint32_t v[32];
-            tmem_ld32(lane_base + kColO + 32 * q, v);
+            tmem_ld32(lane_base + kColO + 64 * hf + 32 * q, v);
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st32(lane_base + kColO + 32 * q, v);
+            tmem_st32(lane_base + kColO + 64 * hf + 32 * q, v);
           }
         }
       }
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
       float lsum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t h[4], lw[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -422,17 +431,17 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
           h[e] = pack_h2(h0, h1);
           lw[e] = pack_h2(v0 - h0, v1 - h1);  // the fp16 rounding of the weights is recovered by a second term
         }
-        *reinterpret_cast<uint4*>(sm + kOffP + swz(tid, c)) = make_uint4(h[0], h[1], h[2], h[3]);
-        *reinterpret_cast<uint4*>(sm + kOffPlo + swz(tid, c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        *reinterpret_cast<uint4*>(sm + kOffP + swz(row, 4 * hf + c)) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
       }
-      l_run += lsum;
+      l_run += lsum;  // (this thread's half of the row sum)
       if (!ok) s_info[3] = 1;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (s_info[3]) break;
-    if (warp == 0 && elect_one_sync()) {
+    if (warp == 8 && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (j + 1 < n_tiles) issue_s(j + 1);  // first: the softmax warps wait for it
       const uint32_t vb = base + kOffV + (uint32_t)(j & 1) * 16384u;
@@ -455,30 +464,33 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 
   // ---- normalised rotated output + log-sum-exp, as one dense partial per (row, head) ------------
   const bool dead = s_info[3] != 0;
-  if (tid < 128) {
+  if (smx) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t lane_base = tmem + ((uint32_t)(32 * warp) << 16);
+    const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+    xchg[hf * 128 + row] = l_run;  // the row sum = the two halves
+    pair_sync();
+    l_run += xchg[(hf ^ 1) * 128 + row];
     const bool have = !dead && !o_zero && l_run > 0.f;
     const float inv = have ? 1.f / (a.lut_scale_v * l_run) : 0.f;
     const int64_t vec = row_live ? (int64_t)(lr0 + my_r) * sh.Hq + kvh * G + my_g : 0;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < 2; ++q) {  // this thread's 64 columns
       uint32_t v[32];
       if (!o_zero && !dead) {
-        tmem_ld32(lane_base + kColO + 32 * q, v);
+        tmem_ld32(lane_base + kColO + 64 * hf + 32 * q, v);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0u;
       }
       if (row_live) {
-        float4* dst = reinterpret_cast<float4*>(p.part_o + vec * kD + 32 * q);
+        float4* dst = reinterpret_cast<float4*>(p.part_o + vec * kD + 64 * hf + 32 * q);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           dst[i] = make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
                                __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
       }
     }
-    if (row_live)
+    if (row_live && hf == 0)
       p.part_m[vec] = have ? (m_run + lg2_approx(l_run)) * 0.6931471805599453f : -CUDART_INF_F;
   }
   if (dead && tid == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
