@@ -16,9 +16,12 @@
 //   48 x tcgen05.mma 128x128x8 over two K-steps of 64, D in 128 TMEM columns   tensor cores
 //   tcgen05.ld of the thread's 64 columns, bucketize, pack, store              CUDA cores
 // Pi (hi and lo) stays resident in shared memory: 2 x 64 KB.  Every wait is bounded.
+#include <cuda.h>
 #include <math_constants.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <type_traits>
 
 #include "tq4_common.cuh"
 
@@ -31,6 +34,8 @@ constexpr int kThreads = 256;
 constexpr int kBlockBytes = kRows * 128;         // one K-block (32 tf32 columns) of an operand: 16 KB
 constexpr uint32_t kOffBhi = 0, kOffBlo = 4 * kBlockBytes, kOffA = 8 * kBlockBytes;
 constexpr uint32_t kSmemBytes = 8 * kBlockBytes + 2 * 2 * kBlockBytes;  // Pi hi/lo + two A buffers (hi, lo)
+constexpr uint32_t kOffX = kSmemBytes;            // XT: the tile's 128 input rows (16-bit), two column halves
+constexpr uint32_t kXBytes = 2 * kBlockBytes;     // 2 x [128 rows][64 elements = 128 B], 128-byte swizzle
 constexpr uint32_t kTmemCols = 128;
 // instruction descriptor: D = F32, A = B = TF32, both K-major, N = 128, M = 128
 constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
@@ -132,10 +137,44 @@ struct RowLoader<__nv_bfloat16> {
   }
 };
 
+// 32 consecutive elements [32 * i, 32 * i + 32) of row `r` of the staged tile (16-bit types): the tile is
+// two column halves of [128 rows][128 B], each with the 128-byte swizzle the TMA applied
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const CompressArgs a) {
+__device__ __forceinline__ void load32_tile(const unsigned char* xt, int r, int i, float (&x)[32]) {
+#pragma unroll
+  for (int cc = 0; cc < 4; ++cc) {
+    const int chunk = 4 * i + cc;  // 16-byte chunk of the row (8 elements)
+    const uint4 v = *reinterpret_cast<const uint4*>(xt + (chunk >> 3) * kBlockBytes + swz(r, chunk & 7));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        x[8 * cc + 2 * j] = __uint_as_float(w[j] << 16);
+        x[8 * cc + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        x[8 * cc + 2 * j] = f.x;
+        x[8 * cc + 2 * j + 1] = f.y;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// XT: the rows of a source are contiguous 16-bit vectors; the next tile's rows are fetched into
+// shared memory by TMA while the current tile is in the tensor core and the epilogue.  Tiles then
+// never mix the two sources (the last tile of K may be partly empty).
+template <typename T, bool XT>
+__global__ void __launch_bounds__(kThreads, 1)
+compress_tc_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap tm_x0,
+                   const __grid_constant__ CUtensorMap tm_x1) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t s_bar[2];  // [0]: first K-step's MMAs done, [1]: tile's MMAs done
+  __shared__ __align__(8) uint64_t s_bar[3];  // [0]: first K-step's MMAs done, [1]: tile's MMAs done, [2]: input tile landed
   __shared__ uint32_t s_tmem;
   __shared__ int s_dead;
   __shared__ float s_bounds[2][16];
@@ -153,6 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar1) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s_bar[2])) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_dead = 0;
   }
@@ -181,18 +221,40 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
 
   const int64_t rows_per_src = a.n_tokens * a.num_heads;
   const int64_t total_rows = rows_per_src * a.n_sources;
-  const int64_t n_tiles = (total_rows + kRows - 1) / kRows;
+  const int64_t tiles_per_src = (rows_per_src + kRows - 1) / kRows;
+  const int64_t n_tiles = XT ? tiles_per_src * a.n_sources : (total_rows + kRows - 1) / kRows;
   const RowLayout lay = row_layout(a.num_heads, kD);
+  const uint32_t bar_x = smem_addr(&s_bar[2]);
+  const unsigned char* xt = sm + kOffX;
   uint32_t phase = 0;
+  // XT: one thread fetches the 128 rows of tile `t` (two boxes of 64 columns); rows past the end of
+  // the source are zero-filled by the copy
+  auto fetch_tile = [&](int64_t t) {
+    const int s_ = (int)(t / tiles_per_src);
+    const int y = (int)((t - (int64_t)s_ * tiles_per_src) * kRows);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_x), "r"(kXBytes) : "memory");
+    tma_load_2d(base + kOffX, s_ ? &tm_x1 : &tm_x0, 0, y, bar_x);
+    tma_load_2d(base + kOffX + kBlockBytes, s_ ? &tm_x1 : &tm_x0, 64, y, bar_x);
+  };
+  if (XT && (int64_t)blockIdx.x < n_tiles && warp == 0 && elect_one_sync()) fetch_tile(blockIdx.x);
 
   for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-    const int64_t row = tile * kRows + row_in_tile;
-    const bool live = row < total_rows;
+    int64_t row;
+    bool live;
     int src = 0, h = 0;
     int64_t tok = 0;
     const T* xp = nullptr;
+    if (XT) {
+      src = (int)(tile / tiles_per_src);
+      const int64_t in_src = (tile - (int64_t)src * tiles_per_src) * kRows + row_in_tile;
+      live = in_src < rows_per_src;
+      row = (int64_t)src * rows_per_src + in_src;
+    } else {
+      row = tile * kRows + row_in_tile;
+      live = row < total_rows;
+      if (live) src = row >= rows_per_src ? 1 : 0;
+    }
     if (live) {
-      src = row >= rows_per_src ? 1 : 0;
       const unsigned rem = (unsigned)(row - (src ? rows_per_src : 0));
       const unsigned t = rem / (unsigned)a.num_heads;
       tok = t;
@@ -201,6 +263,8 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
     }
     // ---- norm, in the summation order of the FMA kernels: p[l] over k = l, l+32, l+64, l+96,
     //      then the butterfly tree 16, 8, 4, 2, 1 -------------------------------------------------
+    bool ok = true;
+    if (XT) ok = bar_wait_bounded(bar_x, phase);  // the tile's rows have landed
     float nrm = 0.f;
     if (live) {
       float p[32];
@@ -209,7 +273,8 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float x[32];
-        RowLoader<T>::load32(xp + 32 * i, x);
+        if constexpr (XT) load32_tile<T>(xt, row_in_tile, i, x);
+        else RowLoader<T>::load32(xp + 32 * i, x);
 #pragma unroll
         for (int l = 0; l < 32; ++l) p[l] = fmaf(x[l], x[l], p[l]);
       }
@@ -223,18 +288,18 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
     const float inv_den = 1.f / (nrm + 1e-10f);
 
     // ---- two K-steps of 64: this thread fills K-block (2 * step + half) of A into buffer `half` ----
-    bool ok = true;
 #pragma unroll 1
     for (int step = 0; step < 2; ++step) {
       const int kb = 2 * step + half;
       float x[32];
       if (live) {
-        RowLoader<T>::load32(xp + 32 * kb, x);
+        if constexpr (XT) load32_tile<T>(xt, row_in_tile, kb, x);
+        else RowLoader<T>::load32(xp + 32 * kb, x);
       } else {
 #pragma unroll
         for (int l = 0; l < 32; ++l) x[l] = 0.f;
       }
-      if (step == 1) ok = bar_wait_bounded(bar0, phase);  // the first K-step's MMAs have read the buffers
+      if (step == 1) ok = bar_wait_bounded(bar0, phase) && ok;  // the first K-step's MMAs have read the buffers
       unsigned char* a_hi = sm + kOffA + half * (2 * kBlockBytes);
       unsigned char* a_lo = a_hi + kBlockBytes;
 #pragma unroll
@@ -267,6 +332,8 @@ __global__ void __launch_bounds__(kThreads, 1) compress_tc_kernel(const Compress
           }
         }
         mma_commit(step == 0 ? bar0 : bar1);
+        // every thread has read its row for the last time: fetch the rows of this CTA's next tile
+        if (XT && step == 1 && tile + gridDim.x < n_tiles) fetch_tile(tile + gridDim.x);
       }
     }
     if (s_dead) break;
@@ -351,21 +418,70 @@ bool compress_tc_eligible(const CompressArgs& a, int head_dim, int dtype) {
   return true;
 }
 
-template <typename T>
-static int launch_tc(const CompressArgs& a, cudaStream_t st) {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+// rows of one source as a 2-D tensor [rows][128] of 16-bit elements; box = 128 rows x 64 columns
+static bool make_x_map(CUtensorMap* m, const void* x, int64_t rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn || rows <= 0) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)kD, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)kD * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)kRows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, bool XT>
+static int launch_tc_t(const CompressArgs& a, const CUtensorMap& m0, const CUtensorMap& m1, cudaStream_t st) {
   static bool attr_set = false;
-  const int smem = (int)kSmemBytes + 1024;
+  const int smem = (int)kSmemBytes + (XT ? (int)kXBytes : 0) + 1024;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(compress_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(compress_tc_kernel<T, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
       return TQ4_ERR_CUDA;
     attr_set = true;
   }
-  const int64_t total_rows = a.n_tokens * a.num_heads * a.n_sources;
-  int64_t blocks = (total_rows + kRows - 1) / kRows;
+  const int64_t rows_per_src = a.n_tokens * a.num_heads;
+  int64_t blocks = XT ? ((rows_per_src + kRows - 1) / kRows) * a.n_sources
+                      : (rows_per_src * a.n_sources + kRows - 1) / kRows;
   if (blocks > sm_count()) blocks = sm_count();
-  compress_tc_kernel<T><<<(unsigned)blocks, kThreads, smem, st>>>(a);
+  compress_tc_kernel<T, XT><<<(unsigned)blocks, kThreads, smem, st>>>(a, m0, m1);
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
+}
+
+template <typename T>
+static int launch_tc(const CompressArgs& a, cudaStream_t st) {
+  CUtensorMap m0, m1;
+  memset(&m0, 0, sizeof(m0));
+  memset(&m1, 0, sizeof(m1));
+  if (sizeof(T) == 2) {
+    // staged input tiles need every source to be a dense [rows][128] array
+    bool dense = true;
+    for (int s = 0; s < a.n_sources; ++s)
+      dense = dense && a.head_stride[s] == kD && a.token_stride[s] == (int64_t)a.num_heads * kD;
+    const int64_t rows = a.n_tokens * a.num_heads;
+    if (dense && make_x_map(&m0, a.x[0], rows) && make_x_map(&m1, a.x[a.n_sources > 1 ? 1 : 0], rows))
+      return launch_tc_t<T, true>(a, m0, m1, st);
+  }
+  return launch_tc_t<T, false>(a, m0, m1, st);
 }
 
 int launch_compress_tc(const CompressArgs& a, int dtype, cudaStream_t st) {
