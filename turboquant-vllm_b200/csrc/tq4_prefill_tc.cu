@@ -326,15 +326,21 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       ns[128 + t] = fmaxf(lg2_approx(vn), -30.f);
     }
   };
+  // descriptors of the operand regions; a byte offset inside a region adds offset / 16 to the
+  // address field (all regions lie below 256 KB, the sum never carries into the other fields)
+  const uint64_t d_qhi = desc_kmajor(base + kOffQhi), d_qlo = desc_kmajor(base + kOffQlo);
+  const uint64_t d_k = desc_kmajor(base + kOffK), d_p = desc_kmajor(base + kOffP);
+  const uint64_t d_plo = desc_kmajor(base + kOffPlo), d_v = desc_mnmajor(base + kOffV, 8192);
   auto issue_s = [&](int j) {  // S = Q K~^T of tile j (one thread)
-    const uint32_t kb_base = base + kOffK + (uint32_t)(j & 1) * 16384u;
+    const uint64_t dk = d_k + (uint64_t)((j & 1) * (16384 >> 4));
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
-        const uint64_t db = desc_kmajor(kb_base + kb * 8192 + 32 * s);
-        mma_f16(tmem + kColS, desc_kmajor(base + kOffQlo + kb * 16384 + 32 * s), db, kDescS, (kb | s) ? 1u : 0u);
-        mma_f16(tmem + kColS, desc_kmajor(base + kOffQhi + kb * 16384 + 32 * s), db, kDescS, 1u);
+        const uint64_t db = dk + (uint64_t)((kb * 8192 + 32 * s) >> 4);
+        const uint64_t qo = (uint64_t)((kb * 16384 + 32 * s) >> 4);
+        mma_f16(tmem + kColS, d_qlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
+        mma_f16(tmem + kColS, d_qhi + qo, db, kDescS, 1u);
       }
     mma_commit(bar_s);
   };
@@ -377,18 +383,37 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
       const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+      // sc[i] = score of column i in the log2 domain (-inf = not visible).  Tiles strictly inside
+      // the visible range of every row of the warp take the short path without per-element masks.
       float sc[32];
       float mt = -CUDART_INF_F;
+      const bool inner = __all_sync(0xffffffffu, ok && row_live && t0 >= kv_lo && t0 + kBN <= kv_hi);
       {
         uint32_t v[32];
         if (ok) tmem_ld32(lane_base + kColS + 32 * hf, v);
+        const float4* kn4 = reinterpret_cast<const float4*>(ns);
+        const float4* lg4 = reinterpret_cast<const float4*>(ns + 128);
+        if (inner) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int pos = t0 + 32 * hf + i;
-          const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
-          const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[i]) : -CUDART_INF_F;
-          sc[i] = s;
-          mt = fmaxf(mt, vis ? s + ns[128 + i] : -CUDART_INF_F);
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 kn = kn4[i4], lg = lg4[i4];
+            const float kk[4] = {kn.x, kn.y, kn.z, kn.w}, ll[4] = {lg.x, lg.y, lg.z, lg.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float s = (__uint_as_float(v[4 * i4 + e]) * kk[e]) * qscale;
+              sc[4 * i4 + e] = s;
+              mt = fmaxf(mt, s + ll[e]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int pos = t0 + 32 * hf + i;
+            const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
+            const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[i]) : -CUDART_INF_F;
+            sc[i] = s;
+            mt = fmaxf(mt, vis ? s + ns[128 + i] : -CUDART_INF_F);
+          }
         }
       }
       // the row's maximum over both halves (the decisions below must agree in its two threads)
@@ -417,19 +442,24 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       }
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
       float lsum = 0.f;
+      const float4* vn4 = reinterpret_cast<const float4*>(ns + 64);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t h[4], lw[4];
+        const float4 va = vn4[2 * c], vb4 = vn4[2 * c + 1];
+        const float vv[8] = {va.x, va.y, va.z, va.w, vb4.x, vb4.y, vb4.z, vb4.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int t = 8 * c + 2 * e;
           const float e0 = ex2_approx(sc[t] - m_use), e1 = ex2_approx(sc[t + 1] - m_use);
           lsum += e0 + e1;
-          const float v0 = sc[t] == -CUDART_INF_F ? 0.f : e0 * ns[64 + t];
-          const float v1 = sc[t + 1] == -CUDART_INF_F ? 0.f : e1 * ns[64 + t + 1];
-          const float h0 = __half2float(__float2half_rn(v0)), h1 = __half2float(__float2half_rn(v1));
-          h[e] = pack_h2(h0, h1);
-          lw[e] = pack_h2(v0 - h0, v1 - h1);  // the fp16 rounding of the weights is recovered by a second term
+          // (a hidden column has e = 0; its value norm may be anything, so select instead of multiply)
+          const float v0 = (inner || sc[t] != -CUDART_INF_F) ? e0 * vv[2 * e] : 0.f;
+          const float v1 = (inner || sc[t + 1] != -CUDART_INF_F) ? e1 * vv[2 * e + 1] : 0.f;
+          const __half2 hp = __floats2half2_rn(v0, v1);
+          const float2 hf2 = __half22float2(hp);
+          h[e] = *reinterpret_cast<const uint32_t*>(&hp);
+          lw[e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
         }
         *reinterpret_cast<uint4*>(sm + kOffP + swz(row, 4 * hf + c)) = make_uint4(h[0], h[1], h[2], h[3]);
         *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
@@ -444,12 +474,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     if (warp == 8 && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (j + 1 < n_tiles) issue_s(j + 1);  // first: the softmax warps wait for it
-      const uint32_t vb = base + kOffV + (uint32_t)(j & 1) * 16384u;
+      const uint64_t dvb = d_v + (uint64_t)((j & 1) * (16384 >> 4));
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
-        const uint64_t dv = desc_mnmajor(vb + 2048 * s, 8192);
-        mma_f16(tmem + kColO, desc_kmajor(base + kOffPlo + 32 * s), dv, kDescO, (!o_zero || s) ? 1u : 0u);
-        mma_f16(tmem + kColO, desc_kmajor(base + kOffP + 32 * s), dv, kDescO, 1u);
+        const uint64_t dv = dvb + (uint64_t)((2048 * s) >> 4);
+        mma_f16(tmem + kColO, d_plo + (uint64_t)((32 * s) >> 4), dv, kDescO, (!o_zero || s) ? 1u : 0u);
+        mma_f16(tmem + kColO, d_p + (uint64_t)((32 * s) >> 4), dv, kDescO, 1u);
       }
       mma_commit(bar_o);
       // the packed stage of tile j was dequantised one iteration ago: refill it with tile j + 2
