@@ -154,13 +154,15 @@ def test_decode_reference_signature_and_out(ops, mode):
     assert cosine(a.float().cpu(), ref) > 0.999
 
 
-@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 4), (4, 4), (32, 4)])
-def test_prefill_tensor_core_kernel(ops, hq, hkv):
+@pytest.mark.parametrize("hq,hkv,bs,vbits", [(32, 8, 16, 4), (8, 4, 16, 4), (4, 4, 16, 4), (32, 4, 16, 4),
+                                             (16, 4, 32, 3), (8, 8, 64, 4)])
+def test_prefill_tensor_core_kernel(ops, hq, hkv, bs, vbits):
     """tcgen05 chunked-prefill kernel (mode 3): blocks of 128 / G query rows per CTA, several tiles,
-    packed prefixes, partial blocks, bottom-right causal / sliding window / full attention."""
-    pr = Prims(128)
+    packed prefixes, partial blocks, bottom-right causal / sliding window / full attention, pages of
+    16 / 32 / 64 tokens, asymmetric K4/V3 codebooks."""
+    pr = Prims(128, 4, vbits)
     p = pr.cuda()
-    d, bs = 128, 16
+    d = 128
     seq_lens, q_lens = [400, 130, 33, 700], [300, 130, 1, 77]
     case = build_paged_case(seq_lens, hkv, d, bs, pr, seed=21, padded=True)
     q = torch.randn(sum(q_lens), hq, d, generator=torch.Generator().manual_seed(8)).bfloat16()

@@ -218,3 +218,46 @@ def test_small_and_streaming_kernels_agree_bitwise(ops, d):
             assert index_mismatch(sm_p, big_p[s0:s0 + 512]) <= MAX_INDEX_MISMATCH
         else:
             assert torch.equal(sm_p, big_p[s0:s0 + 512])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("n_tok,strided", [(1031, False), (1100, True)])
+def test_write_paged_tensor_core_kernel_edges(ops, dtype, n_tok, strided):
+    """Prefill-sized cache write at head_dim 128 (tensor-core kernel): a row count that is not a
+    multiple of the 128-row tile (the K and V sources never share a tile), padding slots, and a
+    strided source (which takes the kernel's direct-load path instead of the staged tiles)."""
+    pr = Prims(128)
+    p = pr.cuda()
+    h, d, bs = 8, 128, 16
+    k, v = O.synthetic_kv(n_tok, h, d, seed=n_tok, dtype=dtype)
+    nblk = (n_tok + bs - 1) // bs + 1
+    width = h * O.padded_slot_bytes(d)
+    perm = torch.randperm(nblk * bs, generator=torch.Generator().manual_seed(4))[:n_tok]
+    slots = perm.clone()
+    slots[5] = -1
+    slots[n_tok - 1] = -1
+    ref = torch.zeros(nblk, bs, width, dtype=torch.uint8)
+    keep = slots >= 0
+    O.write_paged(k[keep], v[keep], ref, slots[keep], pr.rot, pr.kb, pr.vb)
+    kd, vd = k.cuda(), v.cuda()
+    if strided:  # [N, H, 2D] buffer, the vectors are its first halves
+        kd = torch.cat([kd, torch.zeros_like(kd)], dim=-1)[..., :d]
+        vd = torch.cat([vd, torch.zeros_like(vd)], dim=-1)[..., :d]
+        assert not kd.is_contiguous()
+    cache = torch.zeros(nblk, bs, width, dtype=torch.uint8, device="cuda")
+    ops.tq4_write_paged(kd, vd, cache, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"])
+    got, want = cache.cpu().view(-1, width), ref.view(-1, width)
+    kn_off, v_off, vn_off, _ = O.row_layout(h, d)
+    k_idx, v_idx = slice(0, kn_off), slice(v_off, vn_off)
+    for sl in (k_idx, v_idx):
+        a = got[:, sl].reshape(-1, h, d // 2)
+        b = want[:, sl].reshape(-1, h, d // 2)
+        assert index_mismatch(a, b) <= MAX_INDEX_MISMATCH
+    for off in (kn_off, vn_off):  # norms: same bits up to the summation-order tolerance
+        a = got[:, off:off + 4 * h].contiguous().view(torch.float32)
+        b = want[:, off:off + 4 * h].contiguous().view(torch.float32)
+        assert ulp_diff(a.abs() + 1e-30, b.abs() + 1e-30).max() <= MAX_NORM_ULP
+    # untouched slots (padding entries, unused rows) stay zero
+    untouched = torch.ones(nblk * bs, dtype=torch.bool)
+    untouched[slots[keep]] = False
+    assert not got[untouched].any()
