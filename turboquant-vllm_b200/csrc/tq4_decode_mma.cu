@@ -351,14 +351,24 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   const uint32_t ts32 = (uint32_t)a.cache_token_stride;
   const int bs_shift = (a.block_size & (a.block_size - 1)) == 0 ? __ffs(a.block_size) - 1 : -1;
 
+  // first row of the span: the largest r with tile_prefix[r] <= t_begin (the array is
+  // non-decreasing).  Two levels of 32-way search: two dependent memory round trips instead of
+  // log2(rows) of a binary search.
   int r;
   {
-    int lo = 0, hi = sh.rows - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (p.tile_prefix[mid] <= t_begin) lo = mid; else hi = mid - 1;
+    const int rows = sh.rows;
+    const int stride = (rows + 31) / 32;
+    const int v1 = __ldg(p.tile_prefix + min(lane * stride, rows));
+    const unsigned m1 = __ballot_sync(0xffffffffu, v1 <= t_begin);  // a prefix of the lanes (entry 0 is 0)
+    const int base_i = (31 - __clz(m1 | 1u)) * stride;
+    int best = base_i;
+    for (int jj = lane; jj < stride; jj += 32) {
+      const int i = base_i + jj;
+      if (i < rows && __ldg(p.tile_prefix + i) <= t_begin) best = i;
     }
-    r = lo;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    r = min(best, rows - 1);
     while (p.tile_prefix[r + 1] <= t_begin) ++r;
   }
 
