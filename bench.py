@@ -171,7 +171,8 @@ def run_ours(args, rank, world, device):
 
     sm_scale = 1.0 / (D ** 0.5)
 
-    def step(i, q_=q, k_=k_new, v_=v_new, slots_=wl["new_slots"], bt_=wl["block_table"], sl_=wl["seq_lens"]):
+    def step(i, q_=q, k_=k_new, v_=v_new, slots_=wl["new_slots"], bt_=wl["block_table"], sl_=wl["seq_lens"],
+             out=out):
         cache = wl["caches"][i % args.layers]
         if args.separate_write:
             ops.tq4_write_paged(k_, v_, cache, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"])
@@ -311,13 +312,14 @@ def run_ours(args, rank, world, device):
             out_h.copy_(out, non_blocking=True)
             return
         cur = torch.cuda.current_stream()
-        copy_stream.wait_stream(cur)  # fork: the previous step (which read next_bufs) is ordered before
+        copy_stream.wait_stream(cur)  # fork: step i - 1 (it read next_bufs, wrote outs[(i - 1) % 2]) is done
         with torch.cuda.stream(copy_stream):
-            h2d(next_bufs)            # inputs of step i + 1
-        step(i, *cur_bufs)            # inputs of step i were staged during step i - 1
-        out_h.copy_(out, non_blocking=True)
+            out_h.copy_(outs[(i + 1) % 2], non_blocking=True)  # result of step i - 1
+            h2d(next_bufs)                                      # inputs of step i + 1
+        step(i, *cur_bufs, out=outs[i % 2])  # inputs of step i were staged during step i - 1
         cur.wait_stream(copy_stream)  # join
 
+    outs = [out, torch.empty_like(out)]
     h2d(dev_in[0])
     for i in range(3):
         e2e_step(i)
@@ -329,7 +331,8 @@ def run_ours(args, rank, world, device):
     e2e = {"value": round(batch * args.steps / (e2e_ms * 1e-3), 1), "unit": "tok/s",
            "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h,
            "ms_per_step": round(e2e_ms / args.steps, 5), "cuda_graph": e2e_graph,
-           "copies": "serial" if args.e2e_serial else "inputs of step i+1 staged on a second stream during step i"}
+           "copies": "serial" if args.e2e_serial else
+           "second stream: inputs of step i+1 in, result of step i-1 out, while step i computes"}
 
     # ---- chunked prefill (BASELINE config 4 shape: 8 sequences x 2048 new tokens on an 8192-token
     #      packed prefix, causal): tcgen05 kernel and, beside it, the streaming kernel -------------
