@@ -6,9 +6,11 @@
 //   * the keys of a row are cut into 16-token TILES on absolute 16-token boundaries;
 //   * all tiles of all rows form one stream, cut into `ctas` equal contiguous SPANS; CTA c
 //     works on span c, so load balance is independent of the length distribution;
-//   * inside a CTA, warp (ts, vh) handles virtual head vh and every TPC-th tile (phase ts);
-//   * a (row, CTA) intersection is a SEGMENT; every warp writes one partial (m, l, O) per
-//     segment into slot slot_base[r] + (c - first_cta(r)), sub-slot ts;
+//   * fp32 kernel: inside a CTA, warp (ts, vh) handles virtual head vh and every TPC-th tile
+//     (phase ts); a (row, CTA) intersection is a SEGMENT; every warp writes one partial (m, l, O)
+//     per segment into slot slot_base[r] + (c - first_cta(r)), sub-slot ts;
+//   * tensor-core kernel: the stream is cut into ctas * TPC spans instead, warp (ts, vh) of CTA c
+//     streams span c * TPC + ts for virtual head vh and writes one partial per (row, span) segment;
 //   * the combine kernel merges the slots of a row, normalises and un-rotates.
 #pragma once
 #include "tq4_common.cuh"

@@ -18,10 +18,16 @@
 // 1/alpha is folded into the fp32 score scale and the output.  Norms are factored out: scores are scaled by
 // knorm in fp32, probabilities by vnorm before the split.
 //
-// Data movement: every thread cp.async-copies exactly the cache bytes it will consume itself
-// into a private slot of a per-warp shared-memory ring, kStages tiles ahead (no registers are
-// held by loads in flight, no cross-thread synchronisation is needed), and reads them back
-// with conflict-free 16/8-byte shared loads right before use.
+// Work: the tile stream of a call is cut into one contiguous span per warp; a warp walks the
+// (query row, span) segments of its span and writes one partial (m, l, O) per segment.
+//
+// Data movement: a per-warp shared-memory ring of two stages, one pair of tiles each.  With TMA
+// (the usual case) one elected lane issues the pair's box copies (two 4-D boxes per tile when the
+// K and V halves of a token row are 16-byte aligned, a wider-V 3-D scheme or one whole-row box
+// otherwise) onto the stage's mbarrier; every wait is bounded.  Layouts TMA cannot address fall
+// back to per-thread cp.async of exactly the bytes each thread consumes.  Tiles are read back
+// with 16/8-byte shared loads at compile-time offsets; a token permutation plus the 64-byte TMA
+// swizzle keep them free of bank conflicts.
 #include <cuda.h>
 #include <math_constants.h>
 
