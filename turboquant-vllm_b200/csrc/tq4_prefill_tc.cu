@@ -8,7 +8,7 @@
 //   TMA boxes (K+V index rows and norm columns of 4 pages)                      -> shared memory
 //   dequantise through a 256-entry byte -> half2 table: K~ [64 tok][128 d] and V~ as fp16,
 //     stored in the swizzled layouts the MMA descriptors expect                  CUDA cores
-//   S = Qhi K~^T + Qlo K~^T   (tcgen05.mma kind::f16, 128 x 64 x 16, fp32 in TMEM)   tensor cores
+//   S = Qhi K~^T + Qlo K~^T   (tcgen05.mma kind::f16, 128 x 64 x 16, fp32 in TMEM, two S buffers)
 //   tcgen05.ld S, x knorm, mask, lazy online softmax, P = p * vnorm as fp16 hi + lo   CUDA cores
 //   O += Plo V~ + Phi V~      (tcgen05.mma 128 x 128 x 16, V~ as an MN-major B operand)
 // At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
@@ -30,8 +30,8 @@ namespace {
 constexpr int kD = 128;
 constexpr int kBN = 64;                 // tokens per tile
 constexpr int kThreads = 384;             // warps 0-7: softmax (two threads per row), warps 8-11: dequantise, issue
-constexpr uint32_t kTmemCols = 256;     // S: columns [0, 64), O: columns [64, 192)
-constexpr uint32_t kColS = 0, kColO = 64;
+constexpr uint32_t kTmemCols = 256;     // S (two buffers): columns [0, 64) and [64, 128), O: columns [128, 256)
+constexpr uint32_t kColS = 0, kColO = 128;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffQhi = 0;                       // 2 K-blocks x [128 rows][128 B]
@@ -149,7 +149,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
                   const __grid_constant__ CUtensorMap tm_norm) {
   constexpr int RB = 128 / G;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t s_bar[4];  // [0], [1]: tile stages (TMA), [2]: S ready, [3]: PV done
+  __shared__ __align__(8) uint64_t s_bar[5];  // [0], [1]: tile stages (TMA), [2], [3]: S buffer ready, [4]: PV done
   __shared__ uint32_t s_tmem;
   __shared__ int s_info[4];                   // sequence, first local row, rows in block, dead flag
   const AttnShape& sh = a.sh;
@@ -186,10 +186,10 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
   unsigned char* sm = smem_raw + (base - smem_addr(smem_raw));
-  const uint32_t bar_t0 = smem_addr(&s_bar[0]), bar_s = smem_addr(&s_bar[2]), bar_o = smem_addr(&s_bar[3]);
+  const uint32_t bar_t0 = smem_addr(&s_bar[0]), bar_s0 = smem_addr(&s_bar[2]), bar_o = smem_addr(&s_bar[4]);
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 5; ++i)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_t0 + 8 * i) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -339,10 +339,10 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       for (int s = 0; s < 4; ++s) {
         const uint64_t db = dk + (uint64_t)((kb * 8192 + 32 * s) >> 4);
         const uint64_t qo = (uint64_t)((kb * 16384 + 32 * s) >> 4);
-        mma_f16(tmem + kColS, d_qlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
-        mma_f16(tmem + kColS, d_qhi + qo, db, kDescS, 1u);
+        mma_f16(tmem + kColS + 64 * (j & 1), d_qlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
+        mma_f16(tmem + kColS + 64 * (j & 1), d_qhi + qo, db, kDescS, 1u);
       }
-    mma_commit(bar_s);
+    mma_commit(bar_s0 + 8 * (j & 1));  // one barrier per S buffer: a waiter can never be two phases behind
   };
 
   float m_run = -CUDART_INF_F, l_run = 0.f;
@@ -376,10 +376,20 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       if (j + 1 < n_tiles) {
         ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
         dequant_tile(j + 1, tid - 256, 128);
+        // S_{j+1} goes into the other S buffer as soon as its K~ is in place: the softmax warps
+        // find it ready when they finish tile j
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("bar.sync 5, 128;" ::: "memory");
+        const bool okw = __all_sync(0xffffffffu, ok);
+        if (okw && warp == 8 && elect_one_sync()) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(j + 1);
+        }
       }
       if (!ok) s_info[3] = 1;
     } else {
-      ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s, (uint32_t)(j & 1)));
+      ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
       const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
@@ -390,7 +400,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       const bool inner = __all_sync(0xffffffffu, ok && row_live && t0 >= kv_lo && t0 + kBN <= kv_hi);
       {
         uint32_t v[32];
-        if (ok) tmem_ld32(lane_base + kColS + 32 * hf, v);
+        if (ok) tmem_ld32(lane_base + kColS + 64 * (j & 1) + 32 * hf, v);
         const float4* kn4 = reinterpret_cast<const float4*>(ns);
         const float4* lg4 = reinterpret_cast<const float4*>(ns + 128);
         if (inner) {
@@ -473,7 +483,6 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     if (s_info[3]) break;
     if (warp == 8 && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (j + 1 < n_tiles) issue_s(j + 1);  // first: the softmax warps wait for it
       const uint64_t dvb = d_v + (uint64_t)((j & 1) * (16384 >> 4));
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
