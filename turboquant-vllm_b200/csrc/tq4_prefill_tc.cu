@@ -301,10 +301,11 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 
   // ---- dequantise tile j (its packed stage has landed) into buffer j & 1: 512 items
   //      (K or V, token, 16-byte segment) spread over threads t of nt; norms by the first 64 --------
-  auto dequant_tile = [&](int j, int t, int nt) {
+  // (item_lo, item_hi): items [0, 256) are the K half of the tile, [256, 512) the V half
+  auto dequant_tile = [&](int j, int t, int nt, int item_lo, int item_hi) {
     const unsigned char* stg = sm + kOffStage + (j & 1) * kStageBytes;
     const uint32_t kv_off = (uint32_t)(j & 1) * 16384u;
-    for (int item = t; item < 512; item += nt) {
+    for (int item = item_lo + t; item < item_hi; item += nt) {
       const int u = item >> 8, tok = (item >> 2) & 63, seg = item & 3;
       const uint4 pk = *reinterpret_cast<const uint4*>(stg + (tok >> 4) * 2048 + u * 1024 + (tok & 15) * 64 + seg * 16);
       const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256;
@@ -317,7 +318,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         *reinterpret_cast<uint4*>(dst + swz(tok, (seg & 1) * 4 + c)) = o;
       }
     }
-    if (t < 64) {
+    if (item_lo == 0 && t < 64) {
       const unsigned char* nb = stg + 8192 + (t >> 4) * 512 + (t & 15) * 16 + n_sub;
       const float kn = *reinterpret_cast<const float*>(nb), vn = *reinterpret_cast<const float*>(nb + 256);
       float* ns = reinterpret_cast<float*>(sm + kOffNorm) + (j & 1) * 192;
@@ -354,7 +355,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       if (n_tiles > 1) issue_tile(1);
     }
     const bool ok0 = bar_wait_bounded(bar_t0, 0u);
-    dequant_tile(0, tid, kThreads);
+    dequant_tile(0, tid, kThreads, 0, 512);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (!ok0) s_info[3] = 1;
@@ -375,7 +376,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1));
       if (j + 1 < n_tiles) {
         ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
-        dequant_tile(j + 1, tid - 256, 128);
+        dequant_tile(j + 1, tid - 256, 128, 0, 256);  // keys and norms; the softmax warps take the values
         // S_{j+1} goes into the other S buffer as soon as its K~ is in place: the softmax warps
         // find it ready when they finish tile j
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -475,6 +476,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
       }
       l_run += lsum;  // (this thread's half of the row sum)
+      // the values of tile j + 1 (only O += P V~ of the next iteration reads them): its buffer was freed
+      // by the MMAs of tile j - 1, which this thread has already waited for
+      if (j + 1 < n_tiles) {
+        ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
+        dequant_tile(j + 1, tid, 256, 256, 512);
+      }
       if (!ok) s_info[3] = 1;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
