@@ -281,7 +281,16 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   const int bs_mask = a.block_size - 1, bs_shift = __ffs(a.block_size) - 1;
 
   // one lane issues the boxes of tile j into stage j & 1: 4 pages x (indices K+V, norms K+V)
-  auto issue_tile = [&](int j) {
+  // block ids of the four pages of tile j (read ahead of the copy issue: a global round trip)
+  auto load_blks = [&](int j, int (&blk)[4]) {
+    const int t0 = t_first + j * kBN;
+#pragma unroll
+    for (int pg = 0; pg < 4; ++pg) {
+      const int pos = t0 + 16 * pg;
+      blk[pg] = pos < blk_hi ? __ldg(bt + (pos >> bs_shift)) : 0;  // out-of-range ids read zeros (TMA bounds)
+    }
+  };
+  auto issue_tile = [&](int j, const int (&blks)[4]) {
     const uint32_t st = base + kOffStage + (uint32_t)(j & 1) * kStageBytes, bar = bar_t0 + 8 * (j & 1);
     const int t0 = t_first + j * kBN;
     int npages = 0;
@@ -292,9 +301,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     for (int pg = 0; pg < 4; ++pg) {
       const int pos = t0 + 16 * pg;
       if (pos < blk_hi) {
-        const int blk = __ldg(bt + (pos >> bs_shift));  // out-of-range ids read zeros (TMA bounds)
-        tma_load_4d(st + pg * 2048, &tm_idx, x_idx, pos & bs_mask, 0, blk, bar);
-        tma_load_4d(st + 8192 + pg * 512, &tm_norm, x_nrm, pos & bs_mask, 0, blk, bar);
+        tma_load_4d(st + pg * 2048, &tm_idx, x_idx, pos & bs_mask, 0, blks[pg], bar);
+        tma_load_4d(st + 8192 + pg * 512, &tm_norm, x_nrm, pos & bs_mask, 0, blks[pg], bar);
       }
     }
   };
@@ -351,8 +359,11 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   // ---- pipeline fill: tiles 0 and 1 in flight, tile 0 dequantised by everybody, S_0 issued ---------
   if (n_tiles > 0) {
     if (warp == 8 && elect_one_sync()) {
-      issue_tile(0);
-      if (n_tiles > 1) issue_tile(1);
+      int b0[4], b1[4];
+      load_blks(0, b0);
+      if (n_tiles > 1) load_blks(1, b1);
+      issue_tile(0, b0);
+      if (n_tiles > 1) issue_tile(1, b1);
     }
     const bool ok0 = bar_wait_bounded(bar_t0, 0u);
     dequant_tile(0, tid, kThreads, 0, 512);
@@ -371,6 +382,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   for (int j = 0; j < n_tiles && !s_info[3]; ++j) {
     const int t0 = t_first + j * kBN;
     bool ok = true;
+    int blk_next[4] = {0, 0, 0, 0};  // (warp 8) pages of tile j + 2, fetched while this tile is processed
+    if (warp == 8 && j + 2 < n_tiles) load_blks(j + 2, blk_next);
     if (!smx) {
       // buffer (j+1) & 1 was read by the MMAs of tile j-1: wait for them, then refill it
       if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1));
@@ -499,7 +512,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       }
       mma_commit(bar_o);
       // the packed stage of tile j was dequantised one iteration ago: refill it with tile j + 2
-      if (j + 2 < n_tiles) issue_tile(j + 2);
+      if (j + 2 < n_tiles) issue_tile(j + 2, blk_next);
     }
     o_zero = false;
   }
