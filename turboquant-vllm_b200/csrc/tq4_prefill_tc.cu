@@ -42,8 +42,11 @@ constexpr uint32_t kOffP = kOffV + 32768;             // [128 rows][128 B] fp16 
 constexpr uint32_t kOffPlo = kOffP + 16384;           // ... and its fp16 remainder
 constexpr uint32_t kOffStage = kOffPlo + 16384;       // 2 x (4 pages x 2048 B indices + 4 x 512 B norms)
 constexpr uint32_t kStageBytes = 4 * 2048 + 4 * 512;
-constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // K table, V table: 256 x 4 B each
-constexpr uint32_t kOffNorm = kOffLut + 2048;               // 2 buffers x (kn[64], vn[64], lg[64])
+// byte -> half2 tables of K and V, 16 copies of every entry side by side (lane pair p reads copy p:
+// lookups of different lane pairs never share a bank, at most two lanes collide)
+constexpr int kLutCopies = 16;
+constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // 2 tables x 256 entries x 16 copies x 4 B
+constexpr uint32_t kOffNorm = kOffLut + 2 * 256 * kLutCopies * 4;  // 2 buffers x (kn[64], vn[64], lg[64])
 constexpr uint32_t kOffXchg = kOffNorm + 2 * 3 * 64 * 4;     // [2 halves][128 rows] floats exchanged by a row's two threads
 constexpr uint32_t kSmemBytes = kOffXchg + 2 * 128 * 4;
 
@@ -203,8 +206,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   // byte -> half2 tables: (centroid[hi nibble], centroid[lo nibble]) scaled onto the fp16 grid
   {
     uint32_t* lut = reinterpret_cast<uint32_t*>(sm + kOffLut);
-    for (int i = tid; i < 512; i += kThreads) {
-      const int w = i >> 8, b = i & 255;
+    for (int i = tid; i < 512 * kLutCopies; i += kThreads) {
+      const int e = i / kLutCopies, w = e >> 8, b = e & 255;
       const float* cent = w ? a.v_centroids : a.k_centroids;
       const int nc = w ? a.n_v_centroids : a.n_k_centroids;
       const float sc = w ? a.lut_scale_v : a.lut_scale_k;
@@ -316,13 +319,14 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     for (int item = item_lo + t; item < item_hi; item += nt) {
       const int u = item >> 8, tok = (item >> 2) & 63, seg = item & 3;
       const uint4 pk = *reinterpret_cast<const uint4*>(stg + (tok >> 4) * 2048 + u * 1024 + (tok & 15) * 64 + seg * 16);
-      const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256;
+      const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256 * kLutCopies + (lane >> 1);
       const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
       unsigned char* dst = sm + (u ? kOffV : kOffK) + kv_off + (seg >> 1) * 8192;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const uint32_t x = w[c];
-        const uint4 o = make_uint4(lut[x & 255], lut[(x >> 8) & 255], lut[(x >> 16) & 255], lut[x >> 24]);
+        const uint4 o = make_uint4(lut[(x & 255) * kLutCopies], lut[((x >> 8) & 255) * kLutCopies],
+                                   lut[((x >> 16) & 255) * kLutCopies], lut[(x >> 24) * kLutCopies]);
         *reinterpret_cast<uint4*>(dst + swz(tok, (seg & 1) * 4 + c)) = o;
       }
     }
