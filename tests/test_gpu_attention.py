@@ -338,3 +338,32 @@ def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, v
     O.write_paged(k_new.cpu()[keep], v_new.cpu()[keep], ref_cache, slots[keep], pr.rot, pr.kb, pr.vb)
     ref = O.paged_decode_fp32(q.cpu(), ref_cache, bt, seq_lens, pr.kc, pr.vc, pr.rot, hkv)
     _check(out_b, ref)
+
+
+def test_prefill_more_rows_than_one_launch(ops):
+    """A chunk of more than 4096 query rows is processed in several launches: the tensor-core prefill
+    kernel (row blocks cut at the launch boundaries) must agree with the streaming kernel, and a sample
+    of rows with the fp32 oracle."""
+    pr = Prims(128)
+    p = pr.cuda()
+    hq, hkv, d, bs = 8, 4, 128, 16
+    seq_lens, q_lens = [5000, 900], [4500, 700]
+    case = build_paged_case(seq_lens, hkv, d, bs, pr, seed=33, padded=True)
+    q = torch.randn(sum(q_lens), hq, d, generator=torch.Generator().manual_seed(13)).bfloat16()
+    qsl = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    kw = dict(q=q.cuda(), kv_cache=case["cache"].cuda(), block_table=case["block_table"].cuda(),
+              seq_lens=case["seq_lens"].cuda(), k_centroids=p["kc"], v_centroids=p["vc"], rotation=p["rot"],
+              num_kv_heads=hkv, block_size=bs, query_start_loc=qsl.cuda(), out_dtype=torch.float32)
+    out3 = _run(ops, 3, **kw)
+    out2 = _run(ops, 2, **kw)
+    assert torch.isfinite(out3).all()
+    assert (out3 - out2).abs().max().item() <= MAX_ABS
+    # oracle on the rows around the launch boundary and the chunk ends (each sees its own prefix)
+    rows = [0, 4095, 4096, 4499, 4500, 5199]
+    for r in rows:
+        s = 0 if r < 4500 else 1
+        local = r - int(qsl[s])
+        pos = seq_lens[s] - q_lens[s] + local  # absolute position of the query token
+        ref = O.paged_attention_fp32(q[r:r + 1], case["cache"], case["block_table"][s:s + 1], [pos + 1],
+                                     [0, 1], pr.kc, pr.vc, pr.rot, hkv)
+        _check(out3[r:r + 1], ref)
