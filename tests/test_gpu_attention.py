@@ -367,3 +367,22 @@ def test_prefill_more_rows_than_one_launch(ops):
         ref = O.paged_attention_fp32(q[r:r + 1], case["cache"], case["block_table"][s:s + 1], [pos + 1],
                                      [0, 1], pr.kc, pr.vc, pr.rot, hkv)
         _check(out3[r:r + 1], ref)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_prefill_head_dim_256_sliding_window(ops, mode):
+    """Gemma-2-shaped chunked prefill (8 q / 4 kv heads, head_dim 256) with a sliding window."""
+    pr = Prims(256)
+    p = pr.cuda()
+    hq, hkv, d, bs = 8, 4, 256, 16
+    seq_lens, q_lens = [300, 90], [120, 90]
+    case = build_paged_case(seq_lens, hkv, d, bs, pr, seed=44, padded=True)
+    q = torch.randn(sum(q_lens), hq, d, generator=torch.Generator().manual_seed(14)).bfloat16()
+    qsl = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    ref = O.paged_attention_fp32(q, case["cache"], case["block_table"], seq_lens, qsl, pr.kc, pr.vc, pr.rot,
+                                 hkv, None, True, 64)
+    out = _run(ops, mode, q=q.cuda(), kv_cache=case["cache"].cuda(), block_table=case["block_table"].cuda(),
+               seq_lens=case["seq_lens"].cuda(), k_centroids=p["kc"], v_centroids=p["vc"], rotation=p["rot"],
+               num_kv_heads=hkv, block_size=bs, query_start_loc=qsl.cuda(), causal=True, sliding_window=64,
+               out_dtype=torch.float32)
+    _check(out, ref)
