@@ -10,6 +10,10 @@ returns incrementally dequantised K/V.  Differences under the surface:
   + pack; unpack + LUT + scale), not chains of PyTorch ops;
 * storage grows by capacity doubling, so appending a token does not re-copy the whole layer
   (the reference ``torch.cat``s every step);
+* in fused mode a 4-bit layer is kept as token rows in the paged kernels' own format
+  (:class:`turboquant_vllm.token_rows.TokenRowStore`): an update is one launch of the paged write
+  kernel and the fused attention reads the rows in place; ``get_compressed`` then returns strided
+  views of that buffer;
 * tensors must live on a CUDA device — there is no CPU compute path.
 """
 
@@ -23,6 +27,7 @@ import torch
 
 from turboquant_vllm.compressors import CompressedValues, TurboQuantCompressorMSE
 from turboquant_vllm.quantizer import nibble_pack, nibble_unpack
+from turboquant_vllm.token_rows import TokenRowStore
 
 
 def _packed_size(bits: int, head_dim: int) -> int:
@@ -64,6 +69,21 @@ class _GrowBuffer:
     def view(self) -> torch.Tensor:
         assert self.buf is not None
         return self.buf[:, :, : self.len]
+
+
+class _RowsField:
+    """One of the four reference tensors of a row-format layer, with the ``len`` / ``view()`` face of
+    :class:`_GrowBuffer` (0 = K indices, 1 = K norms, 2 = V indices, 3 = V norms)."""
+
+    def __init__(self, store: TokenRowStore, which: int) -> None:
+        self.store, self.which = store, which
+
+    @property
+    def len(self) -> int:
+        return self.store.len
+
+    def view(self) -> torch.Tensor:
+        return self.store.views()[self.which]
 
 
 class CompressedDynamicCache:
@@ -123,6 +143,9 @@ class CompressedDynamicCache:
         self._v_store: list[tuple[_GrowBuffer, _GrowBuffer] | None] = []
         self._dec_k: list[_GrowBuffer | None] = []
         self._dec_v: list[_GrowBuffer | None] = []
+        # per layer: token-row storage while the layer is in fused mode (then _k_store/_v_store
+        # hold _RowsField views of it)
+        self._rows: list[TokenRowStore | None] = []
 
         if hasattr(cache.update, "__self__") and isinstance(cache.update.__self__, CompressedDynamicCache):
             warnings.warn(
@@ -216,6 +239,7 @@ class CompressedDynamicCache:
             self._v_store.append(None)
             self._dec_k.append(None)
             self._dec_v.append(None)
+            self._rows.append(None)
 
     # ----- the patched cache methods ----------------------------------------------------------------
     def _compressed_update(self, key_states, value_states, layer_idx: int, cache_kwargs=None):
@@ -236,6 +260,15 @@ class CompressedDynamicCache:
                 f"{layer_idx} has head_dim={dim}. Disable fused mode for heterogeneous architectures."
             )
         k_comp, v_comp = self._get_compressors(dim)
+        self._pad_to(layer_idx)
+        if self.fused_mode and self._k_nibble_packed and self._v_nibble_packed:
+            self._append_rows(layer_idx, key_states, value_states, k_comp, v_comp)
+            layer = self.cache.layers[layer_idx]
+            self._ensure_layer_initialized(layer, key_states, value_states)
+            layer.keys, layer.values = key_states, value_states  # placeholders; attention reads the rows
+            return key_states, value_states
+        if self._rows[layer_idx] is not None:
+            self._rows_to_buffers(layer_idx, k_comp, v_comp)
         new_k = self._compress_tensor(k_comp, key_states, nibble_packed=self._k_nibble_packed)
         new_v = self._compress_tensor(v_comp, value_states, nibble_packed=self._v_nibble_packed)
         self._pad_to(layer_idx)
@@ -259,6 +292,46 @@ class CompressedDynamicCache:
         dv = self._dec_v[layer_idx].append(self._dequantize_layer(v_comp, new_v))
         layer.keys, layer.values = dk, dv
         return dk, dv
+
+    # ----- token-row storage (fused mode) -------------------------------------------------------------
+    def _append_rows(self, layer_idx: int, key_states, value_states, k_comp, v_comp) -> None:
+        """Fused-mode update: compress and store the new tokens as token rows, one kernel launch."""
+        b, h, _, d = key_states.shape
+        store = self._rows[layer_idx]
+        if store is None or not store.matches(b, h, d, key_states.device):
+            held = self._k_store[layer_idx]
+            if store is None and held is not None and held[0].len and held[0].view().shape[:2] == (b, h):
+                # tokens stored before fused mode was switched on: carry them over
+                ks, vs = held, self._v_store[layer_idx]
+                store = TokenRowStore.from_tensors(ks[0].view(), ks[1].view(), vs[0].view(), vs[1].view())
+            else:
+                store = TokenRowStore(b, h, d, key_states.device)
+            self._rows[layer_idx] = store
+            self._k_store[layer_idx] = (_RowsField(store, 0), _RowsField(store, 1))
+            self._v_store[layer_idx] = (_RowsField(store, 2), _RowsField(store, 3))
+            self._dec_k[layer_idx] = self._dec_v[layer_idx] = None
+        store.append(key_states, value_states, k_comp.quantizer, v_comp.quantizer)
+
+    def _rows_to_buffers(self, layer_idx: int, k_comp, v_comp) -> None:
+        """Leave fused mode for one layer: four growable tensors again, plus the dequantised K/V of
+        the tokens held so far (what the non-fused ``update`` returns)."""
+        store = self._rows[layer_idx]
+        assert store is not None
+        k_idx, k_n, v_idx, v_n = (x.contiguous() for x in store.views())
+        self._rows[layer_idx] = None
+        for slot, idx, norm, comp, dec in ((self._k_store, k_idx, k_n, k_comp, self._dec_k),
+                                           (self._v_store, v_idx, v_n, v_comp, self._dec_v)):
+            pair = (_GrowBuffer(), _GrowBuffer())
+            pair[0].append(idx)
+            pair[1].append(norm)
+            slot[layer_idx] = pair
+            dec[layer_idx] = _GrowBuffer()
+            dec[layer_idx].append(self._dequantize_layer(comp, _CompressedLayer(idx, norm, True)))
+
+    def get_token_rows(self, layer_idx: int) -> TokenRowStore | None:
+        """The layer's token-row storage, or ``None`` when the layer is not held in that format
+        (not in fused mode, a bit width other than 4, bypassed, or never updated)."""
+        return self._rows[layer_idx] if layer_idx < len(self._rows) else None
 
     def _compressed_get_seq_length(self, layer_idx: int = 0) -> int:
         if not self.enabled or layer_idx in self._full_attn_bypass:
