@@ -373,6 +373,13 @@ def run_ours(args, rank, world, device):
         if "ms" in line["bf16_paged_decode"]:
             line["bf16_paged_decode"]["tq4_attention_path_ms"] = round(
                 sum(avg[k] for k in ("prologue", "attention", "combine")), 5)
+    if rank == 0 and world == 1 and args.extra:
+        del wl["caches"][:]  # free HBM: these caches are several GB each
+        torch.cuda.empty_cache()
+        try:
+            line["extra_decode_configs"] = extra_decode_configs(device, args.extra.split(","))
+        except Exception as e:  # noqa: BLE001
+            line["extra_decode_configs"] = {"error": f"{type(e).__name__}: {e}"[:200]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_budget)
     return line
@@ -415,6 +422,90 @@ def prefill_measurement(device, wl, ops):
         ms = e0.elapsed_time(e1) / iters
         res[name] = {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
                      "tokens_per_s": round(nseq * new / (ms * 1e-3), 1)}
+    return res
+
+
+def ragged_decode_measurement(device, name, *, lens, hq, hkv, d, k_bits, v_bits, iters=20):
+    """Side measurement of one decode step (cache write of a token per sequence + fused paged decode)
+    on a ragged batch: `lens` tokens already held per sequence, shuffled 16-token pages, vLLM's padded
+    page format.  The cache is filled through the write kernel from one 65 536-token block of
+    N(0,1)+outlier K/V that is reused for every chunk (contents do not change the timing).  Reports
+    ms per step, algorithmic GB/s (sum(lens) * hkv * (d + 8)) and tok/s."""
+    from turboquant_vllm.kernels import ops
+    from turboquant_vllm.quantizer import TurboQuantMSE
+
+    kq = TurboQuantMSE(d, k_bits, seed=42)
+    vq = kq if v_bits == k_bits else TurboQuantMSE(d, v_bits, seed=42)
+    rot, even, odd, kc, kb = kq.device_primitives(device)
+    _, _, _, vc, vb = vq.device_primitives(device)
+    gen = torch.Generator(device=device).manual_seed(23)
+    lens_t = torch.as_tensor(lens, dtype=torch.int64, device=device)
+    batch, total = lens_t.numel(), int(lens_t.sum())
+    blocks = (lens_t + BS - 1) // BS
+    nblk, max_blocks = int(blocks.sum()), int(blocks.max())
+    width = hkv * (1 << ((d + 8) - 1).bit_length())
+    cache = torch.empty(nblk, BS, width, dtype=torch.uint8, device=device)
+    perm = torch.randperm(nblk, device=device, generator=gen).to(torch.int32)
+    first = torch.cumsum(blocks, 0) - blocks
+    col = torch.arange(max_blocks, device=device)[None, :]
+    block_table = perm[(first[:, None] + col).clamp_(max=nblk - 1)].masked_fill_(col >= blocks[:, None], 0)
+    block_table = block_table.contiguous()
+    seq_of = torch.repeat_interleave(torch.arange(batch, device=device), lens_t)
+    pos = torch.arange(total, device=device) - (torch.cumsum(lens_t, 0) - lens_t)[seq_of]
+    slots = block_table[seq_of, pos // BS].long() * BS + pos % BS
+    chunk = 65536
+    k = torch.randn(chunk, hkv, d, device=device, generator=gen)
+    v = torch.randn(chunk, hkv, d, device=device, generator=gen)
+    for ch in (3, 17, 64, 101):
+        if ch < d:
+            k[..., ch] *= 8.0
+            v[..., ch] *= 8.0
+    k, v = k.bfloat16(), v.bfloat16()
+    for t0 in range(0, total, chunk):
+        n = min(chunk, total - t0)
+        ops.tq4_write_paged(k[:n], v[:n], cache, slots[t0 : t0 + n], even, odd, kb, vb)
+    new_slots = slots[torch.cumsum(lens_t, 0) - 1].contiguous()  # the step rewrites each last token
+    seq_lens = lens_t.to(torch.int32)
+    q = torch.randn(batch, hq, d, device=device, generator=gen).bfloat16()
+    out = torch.empty_like(q)
+    ws = torch.empty(ops.attention_workspace_bytes(batch, hq, hkv, d), dtype=torch.uint8, device=device)
+
+    def step():
+        ops.tq4_write_and_attention(k[:batch], v[:batch], new_slots, even, odd, kb, vb, q, cache, block_table,
+                                    seq_lens, kc, vc, rot, hkv, BS, None, out=out, workspace=ws)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    alg = total * hkv * (d + 8)
+    return {"config": name, "batch": batch, "tokens_held": total, "cache_mb": round(cache.numel() / 1e6),
+            "ms_per_step": round(ms, 4), "hbm_gbs": round(alg / (ms * 1e-3) / 1e9, 1),
+            "tok_per_s": round(batch / (ms * 1e-3), 1)}
+
+
+def extra_decode_configs(device, which):
+    """`serving_mix`: batch 256, contexts ~U[512, 32768] (seeded), 32q/8kv, head_dim 128, K4/V3.
+    `long_context`: batch 8 x 131 072 tokens, 32q/32kv, head_dim 96, K4/V4 (one rank's view of the
+    sequence-split case with W = 1)."""
+    import random
+
+    res = {}
+    if "serving_mix" in which:
+        rng = random.Random(7)
+        lens = [rng.randint(512, 32768) for _ in range(256)]
+        res["serving_mix"] = ragged_decode_measurement(
+            device, "batch 256, ctx~U[512,32768], 32q/8kv, D=128, K4/V3", lens=lens, hq=32, hkv=8, d=128,
+            k_bits=4, v_bits=3)
+    if "long_context" in which:
+        res["long_context"] = ragged_decode_measurement(
+            device, "batch 8 x 131072, 32q/32kv, D=96, K4/V4", lens=[131072] * 8, hq=32, hkv=32, d=96,
+            k_bits=4, v_bits=4, iters=10)
     return res
 
 
@@ -583,6 +674,8 @@ def main():
     ap.add_argument("--e2e-serial", action="store_true",
                     help="end-to-end: copies and kernels of a step on one stream (no staging of the next step)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
+    ap.add_argument("--extra", default="", help="comma list of side measurements run after the timed region: "
+                                                "serving_mix, long_context")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (no CUDA graph)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: run ONE rank's share of a W-GPU head-sharded job on this GPU")

@@ -323,10 +323,14 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   // sigma(2c) / sigma(2c+1), norm columns of token sigma(g); tokens +8 are a fixed distance further
   // (ROWBOX: a stage row is the token row itself: [K idx D/2][K norm 4][V idx D/2][V norm 4])
   const uint32_t o_k = ROWBOX ? rg * kRowPitch + c * C::KBY : tile_off(rg, c * C::KBY);
-  const uint32_t o_v0 = ROWBOX ? rc0 * kRowPitch + C::HALF + 4 + g * C::VBY
-                               : C::kTmaV + (VWIDE ? rc0 * kVPitch + v_sub + g * C::VBY : tile_off(rc0, g * C::VBY));
-  const uint32_t o_v1 = ROWBOX ? rc1 * kRowPitch + C::HALF + 4 + g * C::VBY
-                               : C::kTmaV + (VWIDE ? rc1 * kVPitch + v_sub + g * C::VBY : tile_off(rc1, g * C::VBY));
+  // (V bytes of a thread: 4 * VW bytes at g * 4 * VW, and at D = 96 a half-word at 32 * VW + 2 * g)
+  constexpr int kVWordBytes = 4 * C::VW;
+  const uint32_t o_v0 = ROWBOX ? rc0 * kRowPitch + C::HALF + 4 + g * kVWordBytes
+                               : C::kTmaV + (VWIDE ? rc0 * kVPitch + v_sub + g * kVWordBytes : tile_off(rc0, g * kVWordBytes));
+  const uint32_t o_v1 = ROWBOX ? rc1 * kRowPitch + C::HALF + 4 + g * kVWordBytes
+                               : C::kTmaV + (VWIDE ? rc1 * kVPitch + v_sub + g * kVWordBytes : tile_off(rc1, g * kVWordBytes));
+  const uint32_t o_vh0 = C::kTmaV + tile_off(rc0, 32 * C::VW + 2 * g);
+  const uint32_t o_vh1 = C::kTmaV + tile_off(rc1, 32 * C::VW + 2 * g);
   const uint32_t o_kn = ROWBOX ? rg * kRowPitch + C::HALF : kTmaKN + rg * 16 + kn_sub;
   const uint32_t o_vn = ROWBOX ? rg * kRowPitch + D + 4 : kTmaKN + 256 + rg * 16 + vn_sub;
   constexpr uint32_t kRow8 = 8 * (ROWBOX ? kRowPitch : (SWZ ? 64 : C::HALF));
@@ -586,6 +590,10 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
             for (int u = 0; u < C::NV; ++u) {
               if (j < 2) lds_imm<C::UV, 0>(vo + u * C::UV, vw[j] + u * (C::UV / 4));
               else lds_imm<C::UV, kVRow8>(vo + u * C::UV, vw[j] + u * (C::UV / 4));
+            }
+            if (C::VH) {  // D = 96: the thread's last two V bytes, in the low half of the word
+              const uint32_t ho = sb + ((j & 1) ? o_vh1 : o_vh0) + (j < 2 ? 0u : kVRow8);
+              asm volatile("ld.shared.u16 %0, [%1];" : "=r"(vw[j][C::VW]) : "r"(ho));
             }
           }
         } else {
@@ -1043,6 +1051,18 @@ template <int D, int NB>
 int launch_mma_dn(const AttnArgs& a, cudaStream_t st) {
   const bool aligned = cache_aligned(a.sh, a.cache, a.cache_block_stride, a.cache_token_stride);
   const bool page16 = a.block_size % kTileTokens == 0;
+  if constexpr (D == 96) {
+    // 48-byte index rows: the halves boxes work as for the other head dims; shared-memory reads
+    // are 4-byte words plus a half-word (the unaligned unit sizes)
+    if (cache_tma_ok(a) && cache_v_aligned16(a)) {
+      static bool halves_ok96 = true;
+      if (halves_ok96) {
+        const int rc = launch_mma_t<D, NB, false, true, true, 2>(a, st);
+        if (rc != kErrNoHalvesMap) return rc;
+        halves_ok96 = false;
+      }
+    }
+  }
   if (D != 96 && cache_tma_ok(a)) {
     if (cache_v_aligned16(a)) {
       static bool halves_ok = true;  // cleared if the driver refuses the 4-D map
