@@ -134,3 +134,70 @@ def test_growth_fused_mode_and_quality(cuda_lib):
     assert rk is k and cache.get_seq_length(0) == 274
     with pytest.raises(RuntimeError, match="primary head_dim"):
         cache.update(torch.zeros(2, 4, 1, 64, device="cuda").bfloat16(), torch.zeros(2, 4, 1, 64, device="cuda").bfloat16(), 1)
+
+
+def test_token_rows_layout_cpu():
+    """Token-row storage: the four reference tensors are views of one row buffer; growth keeps them."""
+    from turboquant_vllm.token_rows import PAGE_TOKENS, TokenRowStore
+
+    g = torch.Generator().manual_seed(3)
+    b, h, s, d = 2, 4, 300, 128
+    kp = torch.randint(0, 256, (b, h, s, d // 2), dtype=torch.uint8, generator=g)
+    vp = torch.randint(0, 256, (b, h, s, d // 2), dtype=torch.uint8, generator=g)
+    kn, vn = torch.rand(b, h, s, generator=g), torch.rand(b, h, s, 1, generator=g)
+    store = TokenRowStore.from_tensors(kp, kn, vp, vn)
+    assert store.len == s and store.capacity == 2 * PAGE_TOKENS and store.row_bytes == h * (d + 8)
+    k_idx, k_norm, v_idx, v_norm = store.views()
+    assert k_idx.shape == (b, h, s, d // 2) and k_norm.shape == (b, h, s, 1) and k_norm.dtype == torch.float32
+    assert torch.equal(k_idx, kp) and torch.equal(v_idx, vp)
+    assert torch.equal(k_norm.squeeze(-1), kn) and torch.equal(v_norm, vn)
+    assert all(x.untyped_storage().data_ptr() == store.rows.untyped_storage().data_ptr() for x in store.views())
+    # one token row = [K idx of all heads | K norms | V idx | V norms]
+    row = store.rows[1, 7]
+    assert torch.equal(row[: h * d // 2], kp[1, :, 7].reshape(-1))
+    assert torch.equal(row[h * d // 2 : h * (d // 2 + 4)].view(torch.float32), kn[1, :, 7])
+    assert torch.equal(row[h * (d // 2 + 4) : h * (d + 4)], vp[1, :, 7].reshape(-1))
+    # pages of batch b are b*P .. b*P+P-1
+    assert store.paged_cache().shape == (b * 2, PAGE_TOKENS, store.row_bytes)
+    assert store.block_table().tolist() == [[0, 1], [2, 3]]
+    store._reserve(513)  # growth doubles the capacity and keeps the tokens
+    assert store.capacity == 4 * PAGE_TOKENS and torch.equal(store.views()[0], kp)
+    assert store.block_table().tolist() == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    with pytest.raises(ValueError, match="even head_dim"):
+        TokenRowStore(1, 4, 63, "cpu")
+    with pytest.raises(ValueError, match="multiple of 4"):
+        TokenRowStore(1, 1, 6, "cpu")
+
+
+def test_fused_backend_install_and_fallthrough_cpu():
+    """`install_fused_tq4_kv` wiring on a tiny random Llama; a module without a stashed cache is served
+    by HuggingFace SDPA."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from transformers.integrations.sdpa_attention import sdpa_attention_forward
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+    from turboquant_vllm.triton.attention_interface import (
+        BACKEND_NAME, install_fused_tq4_kv, triton_fa_tq4_kv_forward, uninstall_fused_tq4_kv)
+
+    C = _cls()
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
+                      num_key_value_heads=2, head_dim=32, vocab_size=32)
+    model = LlamaForCausalLM(cfg).eval()
+    cc = C(DynamicCache(config=cfg), head_dim=32, bits=4)
+    install_fused_tq4_kv(model, cc)
+    assert ALL_ATTENTION_FUNCTIONS[BACKEND_NAME] is triton_fa_tq4_kv_forward
+    assert model.config._attn_implementation == BACKEND_NAME and cc.fused_mode
+    stashed = [m for m in model.modules() if getattr(m, "_tq4_cache", None) is cc]
+    assert len(stashed) >= cfg.num_hidden_layers and all(hasattr(m, "layer_idx") for m in stashed)
+    assert cc.get_token_rows(0) is None  # nothing stored yet
+    uninstall_fused_tq4_kv(model)
+    assert model.config._attn_implementation == "sdpa" and not cc.fused_mode
+    assert not any(hasattr(m, "_tq4_cache") for m in model.modules())
+    with pytest.raises(AttributeError, match="no config"):
+        install_fused_tq4_kv(torch.nn.Linear(2, 2), cc)
+    # no stashed cache: the call is HuggingFace SDPA's
+    attn = model.model.layers[0].self_attn
+    q, k = torch.randn(1, 2, 5, 32), torch.randn(1, 2, 5, 32)
+    got, _ = triton_fa_tq4_kv_forward(attn, q, k, k, None, scaling=0.2)
+    want, _ = sdpa_attention_forward(attn, q, k, k, None, scaling=0.2)
+    assert torch.equal(got, want)
