@@ -120,7 +120,7 @@ def synth_kv_gpu(n, h, gen, device):
     return k.bfloat16(), v.bfloat16()
 
 
-def build_workload(device, world, layers):
+def build_workload(device, world, layers, row_bytes=0):
     """Per-rank state: `layers` packed caches filled through the fused write kernel."""
     from turboquant_vllm.kernels import ops
 
@@ -131,7 +131,7 @@ def build_workload(device, world, layers):
     _, _, _, vc, vb = vq.device_primitives(device)
     nblk = batch * CTX // BS
     slot = 1 << ((D + 8) - 1).bit_length()  # vLLM padded per-head slot (256 B at D=128)
-    width = hkv * slot
+    width = row_bytes or hkv * slot  # row_bytes: a denser token row than vLLM's padded page format
     gen = torch.Generator(device=device).manual_seed(SEED)
     perm = torch.randperm(nblk, device=device, generator=gen)
     block_table = perm.view(batch, CTX // BS).to(torch.int32).contiguous()
@@ -162,7 +162,7 @@ def run_ours(args, rank, world, device):
     from turboquant_vllm import _native as nv
     from turboquant_vllm.kernels import ops
 
-    wl = build_workload(device, args.emulate_world or world, args.layers)
+    wl = build_workload(device, args.emulate_world or world, args.layers, args.row_bytes)
     batch, hkv, hq = wl["batch"], wl["hkv"], wl["hq"]
     q = wl["q_host"].to(device)
     k_new, v_new = wl["k_host"].to(device), wl["v_host"].to(device)
@@ -356,6 +356,7 @@ def run_ours(args, rank, world, device):
             "parallelism": f"tp{world} head-sharded, no collective",
             "l2": f"inputs>L2: {args.layers} rotating layer caches of {wl['nblk'] * BS * wl['width'] / 1e6:.0f} MB",
             "kernel_mode": args.mode,
+            "row_bytes": wl["width"],
             "launch": launch_style,
             "ms_per_step_eager": round(ms_eager, 5),
             "ms_per_step_graph": round(ms_graph, 5) if used_graph else None,
@@ -676,6 +677,9 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
     ap.add_argument("--extra", default="", help="comma list of side measurements run after the timed region: "
                                                 "serving_mix, long_context")
+    ap.add_argument("--row-bytes", type=int, default=0,
+                    help="token-row stride of the cache in bytes (>= kv_heads*(head_dim+8), multiple of 16); "
+                         "0 = vLLM's padded page format, which the reference uses")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (no CUDA graph)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: run ONE rank's share of a W-GPU head-sharded job on this GPU")

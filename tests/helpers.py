@@ -39,7 +39,10 @@ def build_paged_case(seq_lens, h_kv, d, bs, prims: Prims, seed=0, padded=False, 
     """Seeded K/V (outlier channels), shuffled physical blocks, cache written by the ORACLE."""
     nblk = [(s + bs - 1) // bs for s in seq_lens]
     total_blocks = sum(nblk) + extra_blocks
-    width = h_kv * O.padded_slot_bytes(d) if padded else O.row_layout(h_kv, d)[3]
+    if padded == "dense":  # the tight row rounded up to 16 bytes (the backend's TQ4_DENSE_ROWS format)
+        width = (O.row_layout(h_kv, d)[3] + 15) & ~15
+    else:
+        width = h_kv * O.padded_slot_bytes(d) if padded else O.row_layout(h_kv, d)[3]
     cache = torch.zeros(total_blocks, bs, width, dtype=torch.uint8)
     order = list(range(total_blocks))
     random.Random(seed).shuffle(order)

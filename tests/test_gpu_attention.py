@@ -102,6 +102,7 @@ def test_decode_seq_len_edges(ops, seq_lens, mode):
     (28, 4, 128, 16, False), (32, 8, 128, 16, True), (4, 4, 128, 16, False), (32, 32, 96, 16, True),
     (8, 4, 256, 16, False), (16, 2, 64, 32, False), (32, 8, 128, 64, True), (16, 1, 128, 8, False),
     (24, 2, 128, 16, False), (4, 1, 128, 16, True), (8, 1, 64, 16, True), (4, 1, 128, 32, False),
+    (4, 1, 128, 16, "dense"), (8, 2, 128, 16, "dense"), (8, 1, 64, 16, "dense"), (3, 3, 96, 16, "dense"),
 ])
 def test_decode_shapes(ops, hq, hkv, d, bs, padded, mode):
     pr = Prims(d)

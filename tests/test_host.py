@@ -132,6 +132,21 @@ def test_backend_class_contract(backend):
     assert spec.real_page_size_bytes == 16 * 8 * 256 == 32768
 
 
+def test_dense_rows_flag(backend, monkeypatch):
+    """TQ4_DENSE_ROWS drops the power-of-two slot padding: same row layout, 16-byte aligned stride."""
+    monkeypatch.delenv("TQ4_DENSE_ROWS", raising=False)
+    assert backend._row_bytes(8, 128) == 8 * 256 and backend._row_bytes(1, 128) == 256
+    monkeypatch.setenv("TQ4_DENSE_ROWS", "1")
+    assert backend._row_bytes(8, 128) == 1088 and backend._row_bytes(2, 128) == 272
+    assert backend._row_bytes(1, 128) == 144 and backend._row_bytes(1, 64) == 80
+    assert backend._row_bytes(32, 96) == 32 * 104
+    assert backend.TQ4AttentionBackend.get_kv_cache_shape(100, 16, 1, 128) == (100, 16, 144)
+    spec = backend.TQ4FullAttentionSpec(block_size=16, num_kv_heads=1, head_size=128, dtype=torch.uint8)
+    assert spec.real_page_size_bytes == 16 * 144
+    monkeypatch.setenv("TQ4_DENSE_ROWS", "0")
+    assert backend._row_bytes(1, 128) == 256
+
+
 def test_env_parsing(backend, monkeypatch):
     for k in ("TQ4_K_BITS", "TQ4_V_BITS", "TQ4_USE_FUSED_PAGED", "TQ4_USE_INT8_PREFILL"):
         monkeypatch.delenv(k, raising=False)

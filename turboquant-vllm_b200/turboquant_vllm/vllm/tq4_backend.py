@@ -73,6 +73,27 @@ def _padded_slot_bytes(head_dim: int) -> int:
     return 1 << (raw - 1).bit_length()
 
 
+def _parse_dense_rows_env() -> bool:
+    """``TQ4_DENSE_ROWS`` as a boolean (``1/true/yes``; default off).  No counterpart in the
+    reference: drops the power-of-two slot padding, see :func:`_row_bytes`."""
+    return os.environ.get("TQ4_DENSE_ROWS", "").lower() in ("1", "true", "yes")
+
+
+def _row_bytes(num_kv_heads: int, head_dim: int) -> int:
+    """Bytes of one token row of the packed cache (all KV heads of this rank).
+
+    Default: ``num_kv_heads`` power-of-two slots, the reference's page format
+    (tq4_backend.py:92-106), needed when TQ4 pages must divide evenly against other layer types
+    of a hybrid model.  With ``TQ4_DENSE_ROWS=1``: the ``H*(D+8)`` data bytes rounded up to 16.
+    The data layout inside a row is the same; only the stride changes.  It matters on
+    head-sharded ranks: with one or two KV heads per rank the padded row makes every 128-byte
+    line of the cache travel for 136 useful bytes per 256, the dense row streams contiguously.
+    """
+    if _parse_dense_rows_env():
+        return (num_kv_heads * _tq4_bytes_per_token_kv(head_dim) + 15) & ~15
+    return num_kv_heads * _padded_slot_bytes(head_dim)
+
+
 # --------------------------------------------------------------------------------------
 # environment knobs (reference: tq4_backend.py:146-215)
 # --------------------------------------------------------------------------------------
@@ -133,7 +154,7 @@ class TQ4FullAttentionSpec(FullAttentionSpec):
 
     @property
     def real_page_size_bytes(self) -> int:  # noqa: D102
-        return self.block_size * self.num_kv_heads * _padded_slot_bytes(self.head_size)
+        return self.block_size * _row_bytes(self.num_kv_heads, self.head_size)
 
 
 class TQ4MetadataBuilder(FlashAttentionMetadataBuilder):
@@ -180,7 +201,7 @@ class TQ4AttentionBackend(FlashAttentionBackend):
         head_size: int,
         cache_dtype_str: str = "auto",
     ) -> tuple[int, ...]:
-        return (num_blocks, block_size, num_kv_heads * _padded_slot_bytes(head_size))
+        return (num_blocks, block_size, _row_bytes(num_kv_heads, head_size))
 
     @staticmethod
     def get_kv_cache_stride_order(include_num_layers_dimension: bool = False) -> tuple[int, ...]:
