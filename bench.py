@@ -490,6 +490,50 @@ def ragged_decode_measurement(device, name, *, lens, hq, hkv, d, k_bits, v_bits,
             "tok_per_s": round(batch / (ms * 1e-3), 1)}
 
 
+def hf_fused_measurement(device, batch=8, ctx=32768, hq=32, hkv=8, d=128, iters=50):
+    """One decode step of a layer on the HuggingFace side: `CompressedDynamicCache.update` of one
+    token per sequence in fused mode (token rows) + the `triton_fa_tq4_kv` backend's forward, on a
+    cache that already holds `ctx` tokens per sequence (same packed bytes as the headline workload)."""
+    import types
+
+    from transformers import DynamicCache
+
+    from turboquant_vllm.kv_cache import CompressedDynamicCache
+    from turboquant_vllm.triton.attention_interface import triton_fa_tq4_kv_forward
+
+    gen = torch.Generator(device=device).manual_seed(31)
+    cache = DynamicCache()
+    cc = CompressedDynamicCache(cache, head_dim=d, bits=4)
+    cc.fused_mode = True
+    module = types.SimpleNamespace(layer_idx=0, _tq4_cache=cc, is_causal=True)
+    for s0 in range(0, ctx, 4096):  # prefill in chunks
+        k = torch.randn(batch, hkv, 4096, d, device=device, generator=gen).bfloat16()
+        cache.update(k, -k, 0)
+    k1 = torch.randn(batch, hkv, 1, d, device=device, generator=gen).bfloat16()
+    q = torch.randn(batch, hq, 1, d, device=device, generator=gen).bfloat16()
+    store = cc.get_token_rows(0)
+    store._reserve(ctx + iters + 8)  # keep capacity growth out of the timed steps
+
+    def step():
+        cache.update(k1, k1, 0)
+        return triton_fa_tq4_kv_forward(module, q, k1, k1, None)[0]
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    alg = batch * ctx * hkv * (d + 8)
+    return {"config": f"HF fused mode: batch {batch} x {ctx} tokens held, {hq}q/{hkv}kv, D={d}, K4/V4, "
+                      "update of 1 token/seq + attention forward",
+            "ms_per_step": round(ms, 4), "hbm_gbs": round(alg / (ms * 1e-3) / 1e9, 1),
+            "tok_per_s": round(batch / (ms * 1e-3), 1)}
+
+
 def extra_decode_configs(device, which):
     """`serving_mix`: batch 256, contexts ~U[512, 32768] (seeded), 32q/8kv, head_dim 128, K4/V3.
     `long_context`: batch 8 x 131 072 tokens, 32q/32kv, head_dim 96, K4/V4 (one rank's view of the
@@ -503,6 +547,8 @@ def extra_decode_configs(device, which):
         res["serving_mix"] = ragged_decode_measurement(
             device, "batch 256, ctx~U[512,32768], 32q/8kv, D=128, K4/V3", lens=lens, hq=32, hkv=8, d=128,
             k_bits=4, v_bits=3)
+    if "hf_fused" in which:
+        res["hf_fused"] = hf_fused_measurement(device)
     if "long_context" in which:
         res["long_context"] = ragged_decode_measurement(
             device, "batch 8 x 131072, 32q/32kv, D=96, K4/V4", lens=[131072] * 8, hq=32, hkv=32, d=96,
@@ -676,7 +722,7 @@ def main():
                     help="end-to-end: copies and kernels of a step on one stream (no staging of the next step)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
     ap.add_argument("--extra", default="", help="comma list of side measurements run after the timed region: "
-                                                "serving_mix, long_context")
+                                                "serving_mix, long_context, hf_fused")
     ap.add_argument("--row-bytes", type=int, default=0,
                     help="token-row stride of the cache in bytes (>= kv_heads*(head_dim+8), multiple of 16); "
                          "0 = vLLM's padded page format, which the reference uses")
