@@ -22,6 +22,28 @@ import math
 import torch
 
 PAGE_TOKENS = 256  # tokens per page of the identity-mapped row buffer (the kernels' largest page)
+_TABLE_ENTRIES = 1 << 22  # largest batch * capacity for which the per-step index rows are kept (48 MB)
+
+
+_index_row_cache: dict = {}  # (device, batch, capacity) -> (len_rows, slot_rows); shared by all layers
+
+
+def _index_rows(device: torch.device, batch: int, cap: int):
+    """``len_rows [cap+1, B]`` int32 (row n = n repeated) and ``slot_rows [cap, B]`` int64
+    (row n = b*cap + n), or ``(None, None)`` when they would be too large."""
+    if batch * (cap + 1) > _TABLE_ENTRIES:
+        return None, None
+    key = (device, batch, cap)
+    hit = _index_row_cache.get(key)
+    if hit is None:
+        if len(_index_row_cache) >= 4:  # layers of a model share one entry; keep the dict small
+            _index_row_cache.pop(next(iter(_index_row_cache)))
+        steps = torch.arange(cap + 1, device=device)
+        base = torch.arange(batch, dtype=torch.int64, device=device) * cap
+        hit = (steps.to(torch.int32)[:, None].expand(cap + 1, batch).contiguous(),
+               (steps[:cap, None] + base[None, :]).contiguous())
+        _index_row_cache[key] = hit
+    return hit
 
 
 class TokenRowStore:
@@ -64,6 +86,9 @@ class TokenRowStore:
         self._block_table = torch.arange(self.batch * pages, dtype=torch.int32, device=self.device).view(
             self.batch, pages)
         self._slot_base = torch.arange(self.batch, dtype=torch.int64, device=self.device) * cap
+        # decode steps index ready-made rows instead of launching small kernels: row n of
+        # _len_rows is [n]*B (sequence lengths), row n of _slot_rows the slots of token n
+        self._len_rows, self._slot_rows = _index_rows(self.device, self.batch, cap)
 
     def matches(self, batch: int, heads: int, dim: int, device: torch.device) -> bool:
         return (batch, heads, dim) == (self.batch, self.heads, self.dim) and torch.device(device) == self.device
@@ -87,7 +112,7 @@ class TokenRowStore:
         key = key_states.transpose(1, 2).reshape(b * s, h, d)
         value = value_states.transpose(1, 2).reshape(b * s, h, d)
         if s == 1:
-            slots = self._slot_base + self.len
+            slots = self._slot_rows[self.len] if self._slot_rows is not None else self._slot_base + self.len
         else:
             slots = (self._slot_base[:, None] + torch.arange(self.len, self.len + s, device=self.device)).reshape(-1)
         tq4_write_paged(key, value, self.paged_cache(), slots, even, odd, k_bounds, v_bounds)
@@ -153,7 +178,8 @@ class TokenRowStore:
             table = table.repeat_interleave(sq, dim=0)
             qsl = None
         else:
-            lens = torch.full((b,), self.len, dtype=torch.int32, device=dev)
+            lens = (self._len_rows[self.len] if self._len_rows is not None
+                    else torch.full((b,), self.len, dtype=torch.int32, device=dev))
             qsl = None if sq == 1 else torch.arange(0, (b + 1) * sq, sq, dtype=torch.int32, device=dev)
         out = paged_tq4_attention(
             q_rows, self.paged_cache(), table, lens, k_centroids, v_centroids, rotation, self.heads,

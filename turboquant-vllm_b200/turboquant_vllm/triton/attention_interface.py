@@ -56,16 +56,15 @@ def triton_fa_tq4_kv_forward(
 
     is_causal = _causal_flag(module, query, attention_mask, kwargs)
     store = cache.get_token_rows(layer_idx)
+    # device-resident copies of the rotation and the codebooks (made once per device)
+    rotation, _, _, k_cents, _ = cache.key_compressor.quantizer.device_primitives(query.device)
     if store is not None:
-        k_cents = cache.centroids.to(device=query.device)
         v_cents = cache.value_compressor.quantizer.device_primitives(query.device)[3]
-        rotation = cache.key_compressor.quantizer.device_primitives(query.device)[0]
         out = store.attention(query, k_cents, v_cents, rotation, scaling, is_causal)
         return out, None
     k_packed, k_norms, v_packed, v_norms = cache.get_compressed(layer_idx)
-    out = triton_flash_attention_tq4_kv(
-        query, k_packed, k_norms, v_packed, v_norms, cache.centroids.to(device=query.device),
-        cache.rotation.to(device=query.device), sm_scale=scaling, is_causal=is_causal)
+    out = triton_flash_attention_tq4_kv(query, k_packed, k_norms, v_packed, v_norms, k_cents, rotation,
+                                        sm_scale=scaling, is_causal=is_causal)
     return out.transpose(1, 2).contiguous(), None
 
 
