@@ -549,7 +549,11 @@ def extra_decode_configs(device, which):
             k_bits=4, v_bits=3)
     if "hf_fused" in which:
         res["hf_fused"] = hf_fused_measurement(device)
-    if "long_context" in which:
+    if "long_context_small" in which:  # the long_context shape at a size suited to a profiler capture
+        res["long_context_small"] = ragged_decode_measurement(
+            device, "batch 2 x 65536, 32q/32kv, D=96, K4/V4", lens=[65536] * 2, hq=32, hkv=32, d=96,
+            k_bits=4, v_bits=4, iters=3)
+    if "long_context" in which and "long_context_small" not in which:
         res["long_context"] = ragged_decode_measurement(
             device, "batch 8 x 131072, 32q/32kv, D=96, K4/V4", lens=[131072] * 8, hq=32, hkv=32, d=96,
             k_bits=4, v_bits=4, iters=10)
@@ -722,7 +726,7 @@ def main():
                     help="end-to-end: copies and kernels of a step on one stream (no staging of the next step)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
     ap.add_argument("--extra", default="", help="comma list of side measurements run after the timed region: "
-                                                "serving_mix, long_context, hf_fused")
+                                                "serving_mix, long_context, long_context_small, hf_fused")
     ap.add_argument("--row-bytes", type=int, default=0,
                     help="token-row stride of the cache in bytes (>= kv_heads*(head_dim+8), multiple of 16); "
                          "0 = vLLM's padded page format, which the reference uses")
