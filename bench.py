@@ -7,7 +7,16 @@ K4/V4 packed cache (vLLM padded rows) filled by the fused write kernel from N(0,
 four outlier channels scaled x8, bf16 queries.  Several layer caches are rotated so the
 working set is far larger than L2.
 N > 1: KV heads are sharded across ranks (tensor parallel, no collective inside attention);
-the global batch grows with N so per-GPU work is fixed (weak scaling).
+the global batch grows with N so per-GPU work is fixed (weak scaling).  The headline is the
+CUDA-graph replay of the step; a block of --steps steps is repeated until the timed region is at
+least --min-region seconds and the median block is reported.
+
+After the headline the same line carries side measurements (each its own key):
+`serving_mix` (K4/V3, batch 256, contexts ~U[512, 32768], heads divided over the N GPUs: strong
+scaling), at N = 1 `long_context` (batch 8 x 131 072, head_dim 96) and `prefill` (chunked prefill,
+head_dim 128 and 256), at N > 1 `split_kv` (the same long-context batch split by sequence over the
+N GPUs, NCCL all-gather of partials + merge, with a parity check against the single-rank kernel
+that fails the run if it does not hold) and `dense_rows` (the headline step on unpadded token rows).
 
 Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the
 reference's PyTorch path (oracle/) on the host cores instead.
@@ -34,9 +43,11 @@ BATCH_PER_GPU_UNIT, CTX, HQ, HKV, D, BS = 64, 4096, 32, 8, 128, 16
 K_BITS = V_BITS = 4
 SEED = 0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant (attention) kernel
-# on this workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 308.8e6  # 303.84 MB read + 4.96 MB written (N = 1 workload)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant (attention) kernel on
+# the N = 1 workload.  A STORED figure from an ncu capture (the timed run cannot measure DRAM
+# traffic): it is reported together with the name of the capture it comes from and only while the
+# kernel build named there is the one that runs; otherwise `traffic` is null.
+NCU_TRAFFIC = {"bytes": None, "capture": None}
 
 
 def measured_peak_gbs():
@@ -46,6 +57,15 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_peak_tflops():
+    """Burst bf16 GEMM peak of this pool's B200s (MEASURED_PEAKS.json), else the fallback 1590."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
 
 
 # ----------------------------------------------------------------------------------------
@@ -171,17 +191,21 @@ def run_ours(args, rank, world, device):
 
     sm_scale = 1.0 / (D ** 0.5)
 
-    def step(i, q_=q, k_=k_new, v_=v_new, slots_=wl["new_slots"], bt_=wl["block_table"], sl_=wl["seq_lens"],
-             out=out):
-        cache = wl["caches"][i % args.layers]
-        if args.separate_write:
-            ops.tq4_write_paged(k_, v_, cache, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"])
-            ops.fused_paged_tq4_decode(q_, cache, bt_, sl_, wl["kc"], wl["rot"], hkv, D, BS, None, out,
-                                       v_centroids=wl["vc"], workspace=ws, mode=args.mode)
-        else:  # one call: the write rides in the attention's first kernel (3 launches)
-            ops.tq4_write_and_attention(k_, v_, slots_, wl["even"], wl["odd"], wl["kb"], wl["vb"],
-                                        q_, cache, bt_, sl_, wl["kc"], wl["vc"], wl["rot"], hkv, BS,
-                                        sm_scale, out=out, workspace=ws, mode=args.mode)
+    def make_step(wl_):
+        def step(i, q_=q, k_=k_new, v_=v_new, slots_=wl_["new_slots"], bt_=wl_["block_table"],
+                 sl_=wl_["seq_lens"], out=out):
+            cache = wl_["caches"][i % args.layers]
+            if args.separate_write:
+                ops.tq4_write_paged(k_, v_, cache, slots_, wl_["even"], wl_["odd"], wl_["kb"], wl_["vb"])
+                ops.fused_paged_tq4_decode(q_, cache, bt_, sl_, wl_["kc"], wl_["rot"], hkv, D, BS, None, out,
+                                           v_centroids=wl_["vc"], workspace=ws, mode=args.mode)
+            else:  # one call: the cache write and the attention of the step
+                ops.tq4_write_and_attention(k_, v_, slots_, wl_["even"], wl_["odd"], wl_["kb"], wl_["vb"],
+                                            q_, cache, bt_, sl_, wl_["kc"], wl_["vc"], wl_["rot"], hkv, BS,
+                                            sm_scale, out=out, workspace=ws, mode=args.mode)
+        return step
+
+    step = make_step(wl)
 
     def barrier():
         if world > 1:
@@ -235,20 +259,34 @@ def run_ours(args, rank, world, device):
 
     for i in range(max(args.warmup, 3)):
         step(i)
-    sampler = ClockSampler(device.index or 0)  # clocks over both timed passes (eager, graph)
+    sampler = ClockSampler(device.index or 0)  # clocks over every timed block (graph and eager)
     sampler.start()
-    ms_eager = timed(step, args.steps) / args.steps
     run_steps, used_graph = graphed(step)
     run_steps(max(args.warmup, 3))
-    ms_total = timed(lambda i: run_steps(args.steps) if i == 0 else None, 1)
-    clocks = sampler.stop()
-    ms_graph = ms_total / args.steps
+
+    def timed_blocks(run_block):
+        """One BLOCK = exactly --steps steps between barrier + synchronize on both sides, timed with
+        CUDA events, max over ranks.  Blocks repeat until the timed region is at least --min-region
+        seconds (the driver's 20 steps are under 2 ms: one block is noise); the result is the
+        median block."""
+        first = timed(lambda i: run_block(args.steps) if i == 0 else None, 1)
+        n = int(min(args.max_blocks, max(1, -(-args.min_region * 1e3 // max(first, 1e-3)))))
+        if world > 1:  # every rank must run the same number of blocks
+            t = torch.tensor([n], dtype=torch.int64, device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            n = int(t.item())
+        blocks = [first] + [timed(lambda i: run_block(args.steps) if i == 0 else None, 1) for _ in range(n - 1)]
+        return statistics.median(blocks), blocks
+
+    # Headline launch style: CUDA-graph replay (how a serving engine issues uniform decode steps);
+    # the eager time of the same steps is reported beside it, never substituted.
+    ms_total, blocks_ms = timed_blocks(run_steps)
     ms_step = ms_total / args.steps
-    # both launch styles ran the same K steps; the headline is the faster one (eager launches overlap
-    # consecutive kernels through programmatic dependent launch, graph replays remove host jitter)
+    ms_eager_total, _ = timed_blocks(lambda n: [step(i) for i in range(n)])
+    ms_eager = ms_eager_total / args.steps
+    clocks = sampler.stop()
+    ms_graph = ms_step if used_graph else None
     launch_style = f"CUDA graph of {args.layers} steps, replayed" if used_graph else "eager"
-    if used_graph and ms_eager < ms_step:
-        ms_step, ms_total, launch_style = ms_eager, ms_eager * args.steps, "eager (programmatic dependent launches)"
     value = batch * args.steps / (ms_total * 1e-3)
 
     # ---- per-kernel durations: an identical second pass with event brackets per kernel ------
@@ -265,7 +303,8 @@ def run_ours(args, rank, world, device):
     achieved = alg_bytes / (avg["attention"] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4),
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if alg_bytes == 285212672 else None,
+                "traffic": NCU_TRAFFIC["bytes"] if alg_bytes == 285212672 else None,
+                "traffic_source": NCU_TRAFFIC["capture"] if alg_bytes == 285212672 else None,
                 "kernel": "paged TQ4 attention (streaming) kernel", "peak_kind": f"of {peak_kind}",
                 "algorithmic_bytes_per_launch": alg_bytes,
                 "kernel_ms": {k: (round(v, 5) if v is not None else None) for k, v in avg.items()},
@@ -325,7 +364,7 @@ def run_ours(args, rank, world, device):
         e2e_step(i)
     run_e2e, e2e_graph = graphed(e2e_step)
     run_e2e(3)
-    e2e_ms = timed(lambda i: run_e2e(args.steps) if i == 0 else None, 1)
+    e2e_ms, _ = timed_blocks(run_e2e)
     h2d_bytes = sum(x.numel() * x.element_size() for x in host_in)
     d2h = out_h.numel() * out_h.element_size()
     e2e = {"value": round(batch * args.steps / (e2e_ms * 1e-3), 1), "unit": "tok/s",
@@ -334,8 +373,9 @@ def run_ours(args, rank, world, device):
            "copies": "serial" if args.e2e_serial else
            "second stream: inputs of step i+1 in, result of step i-1 out, while step i computes"}
 
-    # ---- chunked prefill (BASELINE config 4 shape: 8 sequences x 2048 new tokens on an 8192-token
-    #      packed prefix, causal): tcgen05 kernel and, beside it, the streaming kernel -------------
+    # ---- chunked prefill: 8 sequences x 2048 new tokens on an 8192-token packed prefix, causal
+    #      (head_dim 128: tcgen05 kernel and, beside it, the streaming kernel; head_dim 256 with a
+    #      sliding window of 4096) ---------------------------------------------------------------
     prefill = None
     if rank == 0 and world == 1 and not args.no_prefill:
         try:
@@ -360,6 +400,10 @@ def run_ours(args, rank, world, device):
             "launch": launch_style,
             "ms_per_step_eager": round(ms_eager, 5),
             "ms_per_step_graph": round(ms_graph, 5) if used_graph else None,
+            "timed_blocks": len(blocks_ms),
+            "timed_region_s": round(sum(blocks_ms) * 1e-3, 4),
+            "block_ms_min_median_max": [round(min(blocks_ms), 5), round(statistics.median(blocks_ms), 5),
+                                        round(max(blocks_ms), 5)],
         },
         "hbm_gbs": round(alg_bytes / (ms_step * 1e-3) / 1e9, 1),
         "compress_mtok_s": round(compress_mtok_s, 3),
@@ -374,8 +418,57 @@ def run_ours(args, rank, world, device):
         if "ms" in line["bf16_paged_decode"]:
             line["bf16_paged_decode"]["tq4_attention_path_ms"] = round(
                 sum(avg[k] for k in ("prologue", "attention", "combine")), 5)
+    eff_world = args.emulate_world or world
+    if eff_world > 1 and not args.no_dense_rows and not args.row_bytes:
+        # the same step on dense token rows (kv_heads * 136 bytes rounded up to 16) instead of vLLM's
+        # power-of-two slots: what the TQ4_DENSE_ROWS=1 backend option allocates
+        try:
+            del wl["caches"][:]
+            torch.cuda.empty_cache()
+            wl_d = build_workload(device, eff_world, args.layers, (hkv * (D + 8) + 15) & ~15)
+            step_d = make_step(wl_d)
+            for i in range(3):
+                step_d(i)
+            run_d, graph_d = graphed(step_d)
+            run_d(3)
+            ms_d, _ = timed_blocks(run_d)
+            nv.profile_start(200)
+            timed(step_d, 200)
+            nv.profile_stop()
+            att_d = nv.profile_read(nv.PROF_ATTENTION, 200)
+            att_d = sum(att_d) / len(att_d)
+            line["dense_rows"] = {
+                "row_bytes": wl_d["width"], "ms_per_step": round(ms_d / args.steps, 5),
+                "value": round(batch * args.steps / (ms_d * 1e-3), 1), "unit": "tok/s", "cuda_graph": graph_d,
+                "frac": round(alg_bytes / (att_d * 1e-3) / 1e9 / peak, 4),
+                "step_frac": round(alg_bytes / (ms_d / args.steps * 1e-3) / 1e9 / peak, 4)}
+            del wl_d["caches"][:]
+        except Exception as e:  # noqa: BLE001
+            line["dense_rows"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+    line["step_frac"] = round(alg_bytes / (ms_step * 1e-3) / 1e9 / peak, 4)
+    if not args.no_side_configs and not args.emulate_world:
+        del wl["caches"][:]  # free HBM: the side caches are several GB each
+        torch.cuda.empty_cache()
+        side = {}
+
+        def guarded(name, fn):
+            # every rank takes part (collectives inside); a failure is reported, and fails the run
+            try:
+                side[name] = fn()
+            except Exception as e:  # noqa: BLE001
+                side[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+
+        guarded("serving_mix", lambda: serving_mix_measurement(device, world, rank))
+        if world > 1:
+            guarded("serving_mix_dense_rows", lambda: serving_mix_measurement(device, world, rank, dense_rows=True))
+            guarded("split_kv", lambda: split_kv_measurement(device, world, rank))
+        else:
+            guarded("long_context", lambda: ragged_decode_measurement(
+                device, "batch 8 x 131072, 32q/32kv, D=96, K4/V4 (one GPU holds the whole sequences)",
+                lens=[131072] * 8, hq=32, hkv=32, d=96, k_bits=4, v_bits=4, iters=10))
+        line.update(side)
     if rank == 0 and world == 1 and args.extra:
-        del wl["caches"][:]  # free HBM: these caches are several GB each
+        del wl["caches"][:]
         torch.cuda.empty_cache()
         try:
             line["extra_decode_configs"] = extra_decode_configs(device, args.extra.split(","))
@@ -386,52 +479,99 @@ def run_ours(args, rank, world, device):
     return line
 
 
-def prefill_measurement(device, wl, ops):
-    """8 sequences x 2048 new tokens attending causally over an 8192-token packed prefix + themselves
-    (32 q / 8 kv heads, head_dim 128, block 16, shuffled pages).  Reports ms and TFLOP/s
-    (4 * keys seen * head_dim * q_heads) of the tcgen05 kernel (mode 0 picks it) and of the streaming
-    kernel (mode 2)."""
-    hq, hkv, nseq, prefix, new = 32, 8, 8, 8192, 2048
+def device_time_ms(fn, iters, world, device, warmup=3):
+    """Mean milliseconds of fn() over `iters` calls: CUDA events on the current stream, barrier +
+    synchronize on both sides, max over ranks."""
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+    for _ in range(warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / iters
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def prefill_case(device, ops, *, hq, hkv, d, window, modes, nseq=8, prefix=8192, new=2048):
+    """`nseq` sequences x `new` new tokens attending causally (optionally inside a sliding window)
+    over a `prefix`-token packed prefix + themselves, shuffled 16-token pages, vLLM's padded page
+    format.  Reports ms, TFLOP/s (4 * visible keys * head_dim * q_heads) and new tokens/s per mode."""
+    from turboquant_vllm.quantizer import TurboQuantMSE
+
+    kq = TurboQuantMSE(d, 4, seed=42)
+    rot, even, odd, kc, kb = kq.device_primitives(device)
     total = prefix + new
     nblk = nseq * total // BS
     gen = torch.Generator(device=device).manual_seed(11)
-    cache = torch.zeros(nblk, BS, hkv * 256, dtype=torch.uint8, device=device)
+    width = hkv * (1 << ((d + 8) - 1).bit_length())
+    cache = torch.zeros(nblk, BS, width, dtype=torch.uint8, device=device)
     bt = torch.randperm(nblk, device=device, generator=gen).view(nseq, total // BS).to(torch.int32)
     slots = (bt.long()[:, :, None] * BS + torch.arange(BS, device=device)[None, None, :]).reshape(-1)
-    k = torch.randn(nseq * total, hkv, D, device=device, generator=gen).bfloat16()
-    v = torch.randn(nseq * total, hkv, D, device=device, generator=gen).bfloat16()
-    ops.tq4_write_paged(k, v, cache, slots, wl["even"], wl["odd"], wl["kb"], wl["vb"])
+    chunk = 16384
+    for t0 in range(0, nseq * total, chunk):
+        k = torch.randn(chunk, hkv, d, device=device, generator=gen).bfloat16()
+        v = torch.randn(chunk, hkv, d, device=device, generator=gen).bfloat16()
+        ops.tq4_write_paged(k, v, cache, slots[t0:t0 + chunk], even, odd, kb, kb)
     del k, v
-    q = torch.randn(nseq * new, hq, D, device=device, generator=gen).bfloat16()
+    q = torch.randn(nseq * new, hq, d, device=device, generator=gen).bfloat16()
     qsl = (torch.arange(nseq + 1, device=device) * new).to(torch.int32)
     sl = torch.full((nseq,), total, dtype=torch.int32, device=device)
-    keys = nseq * sum(prefix + i + 1 for i in range(new))
-    flops = 4.0 * keys * D * hq
-    res = {"config": f"{nseq} seqs x {new} new tokens on {prefix}-token packed prefix, causal, 32q/8kv, D=128"}
-    for name, mode, iters in (("tcgen05", 0, 5), ("streaming", 2, 2)):
+    keys = nseq * sum(min(prefix + i + 1, window or (prefix + i + 1)) for i in range(new))
+    flops = 4.0 * keys * d * hq
+    res = {"config": f"{nseq} seqs x {new} new tokens on {prefix}-token packed prefix, causal, "
+                     f"{hq}q/{hkv}kv, D={d}" + (f", sliding window {window}" if window else ""),
+           "visible_pairs": keys, "flops": flops}
+    for name, mode, iters in modes:
         def run():
-            return ops.paged_tq4_attention(q, cache, bt, sl, wl["kc"], wl["vc"], wl["rot"], hkv, BS,
-                                           query_start_loc=qsl, mode=mode)
-        run()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(iters):
+            return ops.paged_tq4_attention(q, cache, bt, sl, kc, kc, rot, hkv, BS, query_start_loc=qsl,
+                                           sliding_window=window, mode=mode)
+        try:
             run()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
+        except NotImplementedError as e:
+            res[name] = {"unsupported": str(e)[:120]}
+            continue
+        ms = device_time_ms(run, iters, 1, device, warmup=1)
         res[name] = {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
+                     "frac_of_bf16_burst_peak": round(flops / ms / 1e9 / measured_peak_tflops(), 4),
                      "tokens_per_s": round(nseq * new / (ms * 1e-3), 1)}
     return res
 
 
-def ragged_decode_measurement(device, name, *, lens, hq, hkv, d, k_bits, v_bits, iters=20):
+def prefill_measurement(device, wl, ops):
+    """Chunked prefill on packed keys: (a) Llama shape 32 q / 8 KV heads, head_dim 128; (b) Gemma-2-2B
+    shape 8 q / 4 KV heads, head_dim 256, sliding window 4096.  `mode 0` is what the backend picks,
+    `mode 2` the streaming kernel."""
+    a = prefill_case(device, ops, hq=32, hkv=8, d=128, window=None,
+                     modes=(("tcgen05", 0, 5), ("streaming", 2, 2)))
+    try:
+        b = prefill_case(device, ops, hq=8, hkv=4, d=256, window=4096, modes=(("auto", 0, 3),))
+    except Exception as e:  # noqa: BLE001
+        b = {"error": f"{type(e).__name__}: {e}"[:200]}
+    a["head_dim_256_window_4096"] = b
+    return a
+
+
+def ragged_decode_measurement(device, name, *, lens, hq, hkv, d, k_bits, v_bits, iters=20, world=1,
+                              dense_rows=False):
     """Side measurement of one decode step (cache write of a token per sequence + fused paged decode)
     on a ragged batch: `lens` tokens already held per sequence, shuffled 16-token pages, vLLM's padded
     page format.  The cache is filled through the write kernel from one 65 536-token block of
     N(0,1)+outlier K/V that is reused for every chunk (contents do not change the timing).  Reports
-    ms per step, algorithmic GB/s (sum(lens) * hkv * (d + 8)) and tok/s."""
+    ms per step, algorithmic GB/s (sum(lens) * hkv * (d + 8)) and tok/s.  `hq` / `hkv` are THIS
+    rank's heads; with world > 1 the time is the max over ranks (strong scaling: the batch is fixed,
+    the heads are divided).  `dense_rows`: token rows of hkv * (d + 8) bytes rounded up to 16 instead
+    of the power-of-two slots of vLLM's page format."""
     from turboquant_vllm.kernels import ops
     from turboquant_vllm.quantizer import TurboQuantMSE
 
@@ -444,7 +584,7 @@ def ragged_decode_measurement(device, name, *, lens, hq, hkv, d, k_bits, v_bits,
     batch, total = lens_t.numel(), int(lens_t.sum())
     blocks = (lens_t + BS - 1) // BS
     nblk, max_blocks = int(blocks.sum()), int(blocks.max())
-    width = hkv * (1 << ((d + 8) - 1).bit_length())
+    width = (hkv * (d + 8) + 15) & ~15 if dense_rows else hkv * (1 << ((d + 8) - 1).bit_length())
     cache = torch.empty(nblk, BS, width, dtype=torch.uint8, device=device)
     perm = torch.randperm(nblk, device=device, generator=gen).to(torch.int32)
     first = torch.cumsum(blocks, 0) - blocks
@@ -474,20 +614,127 @@ def ragged_decode_measurement(device, name, *, lens, hq, hkv, d, k_bits, v_bits,
     def step():
         ops.tq4_write_and_attention(k[:batch], v[:batch], new_slots, even, odd, kb, vb, q, cache, block_table,
                                     seq_lens, kc, vc, rot, hkv, BS, None, out=out, workspace=ws)
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / iters
+    ms = device_time_ms(step, iters, world, device)
     alg = total * hkv * (d + 8)
+    peak, _ = measured_peak_gbs()
+    gbs = alg / (ms * 1e-3) / 1e9
     return {"config": name, "batch": batch, "tokens_held": total, "cache_mb": round(cache.numel() / 1e6),
-            "ms_per_step": round(ms, 4), "hbm_gbs": round(alg / (ms * 1e-3) / 1e9, 1),
+            "kv_heads_per_gpu": hkv, "row_bytes": width,
+            "ms_per_step": round(ms, 4), "hbm_gbs_per_gpu": round(gbs, 1), "frac": round(gbs / peak, 4),
             "tok_per_s": round(batch / (ms * 1e-3), 1)}
+
+
+def serving_mix_measurement(device, world, rank, dense_rows=False, iters=20):
+    """Asymmetric K4/V3 serving mix, one layer: batch 256 with context lengths ~U[512, 32768]
+    (seeded), cache write of one new token per sequence + paged decode, 32 q / 8 KV heads of
+    head_dim 128 divided over `world` ranks (strong scaling: the batch is fixed)."""
+    import random
+
+    rng = random.Random(7)
+    lens = [rng.randint(512, 32768) for _ in range(256)]
+    r = ragged_decode_measurement(
+        device, f"batch 256, ctx~U[512,32768], 32q/8kv heads over {world} GPU(s), D=128, K4/V3, "
+                + ("dense rows" if dense_rows else "vLLM padded pages"),
+        lens=lens, hq=HQ // world, hkv=HKV // world, d=D, k_bits=4, v_bits=3, iters=iters, world=world,
+        dense_rows=dense_rows)
+    r["scaling"] = "strong"
+    r["hbm_gbs_all_gpus"] = round(r["hbm_gbs_per_gpu"] * world, 1)
+    return r
+
+
+def build_split_kv_case(device, world, rank, *, batch, ctx, hq, hkv, d, seed):
+    """This rank's token slice of `batch` sequences of `ctx` tokens (contiguous, block aligned;
+    turboquant_vllm.parallel.split_sequence), written through the write kernel into a local paged
+    cache with shuffled pages.  K/V come from ONE seeded 32 768-token block of N(0,1)+outlier rows
+    reused cyclically by absolute position, so any rank can rebuild any slice."""
+    from turboquant_vllm import parallel
+    from turboquant_vllm.kernels import ops
+    from turboquant_vllm.quantizer import TurboQuantMSE
+
+    kq = TurboQuantMSE(d, 4, seed=42)
+    rot, even, odd, kc, kb = kq.device_primitives(device)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    period = 32768
+    k = torch.randn(period, hkv, d, device=device, generator=gen)
+    v = torch.randn(period, hkv, d, device=device, generator=gen)
+    for ch in (3, 17, 64, 101):
+        if ch < d:
+            k[..., ch] *= 8.0
+            v[..., ch] *= 8.0
+    k, v = k.bfloat16(), v.bfloat16()
+    start, end = parallel.split_sequence(ctx, world, BS)[rank]
+    local = end - start
+    nb_seq = (local + BS - 1) // BS
+    nblk = max(1, batch * nb_seq)
+    width = hkv * (1 << ((d + 8) - 1).bit_length())
+    cache = torch.zeros(nblk, BS, width, dtype=torch.uint8, device=device)
+    gen2 = torch.Generator(device=device).manual_seed(seed + 1 + rank)
+    bt = torch.randperm(nblk, device=device, generator=gen2).view(batch, max(nb_seq, 1)).to(torch.int32).contiguous()
+    pos = torch.arange(local, device=device)
+    for b in range(batch):
+        for t0 in range(0, local, period):
+            n = min(period, local - t0)
+            p_ = pos[t0:t0 + n]
+            slots = bt[b].long()[p_ // BS] * BS + p_ % BS
+            src = (start + t0 + b * 977) % period  # sequences differ by a cyclic shift
+            idx = (torch.arange(n, device=device) + src) % period
+            ops.tq4_write_paged(k[idx], v[idx], cache, slots, even, odd, kb, kb)
+    seq_lens = torch.full((batch,), local, dtype=torch.int32, device=device)
+    g = torch.Generator().manual_seed(seed + 100)
+    q = torch.randn(batch, hq, d, generator=g).bfloat16().to(device)
+    return dict(cache=cache, bt=bt, seq_lens=seq_lens, q=q, rot=rot, kc=kc, local=local, width=width)
+
+
+def split_kv_measurement(device, world, rank, *, iters=20):
+    """Long-context sequence-split decode (Phi-3-mini shape: 32 q / 32 KV heads, head_dim 96, batch 8
+    x 131 072 tokens, K4/V4): every rank holds 1/world of every sequence, attends over its slice,
+    all ranks exchange (output, log-sum-exp) partials with one NCCL all-gather and merge locally
+    (turboquant_vllm.parallel.split_kv_decode).  Before timing, a small case checks that the
+    world-rank result equals the single-rank kernel run on the whole sequences."""
+    from turboquant_vllm import parallel
+    from turboquant_vllm.kernels import ops
+
+    hq = hkv = 32
+    d = 96
+    # ---- parity on a small case: N ranks vs one rank over the whole sequences ---------------------
+    small = dict(batch=4, ctx=2048, hq=hq, hkv=hkv, d=d, seed=41)
+    mine = build_split_kv_case(device, world, rank, **small)
+    got = parallel.split_kv_decode(mine["q"], mine["cache"], mine["bt"], mine["seq_lens"], mine["kc"], mine["kc"],
+                                   mine["rot"], hkv, BS, out_dtype=torch.float32)
+    whole = build_split_kv_case(device, 1, 0, **small)
+    want = ops.paged_tq4_attention(whole["q"], whole["cache"], whole["bt"], whole["seq_lens"], whole["kc"],
+                                   whole["kc"], whole["rot"], hkv, BS, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    cos = float(torch.nn.functional.cosine_similarity(got.flatten().double(), want.flatten().double(), dim=0))
+    max_abs = float((got - want).abs().max())
+    parity = {"case": "4 seqs x 2048 tokens", "cos": round(cos, 7), "max_abs": float(f"{max_abs:.3e}"),
+              "ok": bool(cos >= 0.99999 and max_abs <= 1e-4)}
+    del mine, whole
+    # ---- the timed case ---------------------------------------------------------------------------
+    batch, ctx = 8, 131072
+    c = build_split_kv_case(device, world, rank, batch=batch, ctx=ctx, hq=hq, hkv=hkv, d=d, seed=43)
+    events: list = []
+
+    def step():
+        parallel.split_kv_decode(c["q"], c["cache"], c["bt"], c["seq_lens"], c["kc"], c["kc"], c["rot"], hkv, BS,
+                                 exchange_events=events)
+    ms = device_time_ms(step, iters, world, device)
+    ex = [a.elapsed_time(b) for a, b in events[-iters:]]
+    ex_ms = sum(ex) / len(ex)
+    if world > 1:
+        t = torch.tensor([ex_ms], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ex_ms = float(t.item())
+    alg_rank = batch * c["local"] * hkv * (d + 8)
+    peak, _ = measured_peak_gbs()
+    gbs = alg_rank / (ms * 1e-3) / 1e9
+    return {"config": f"batch {batch} x {ctx} tokens, 32q/32kv, D=96, K4/V4, sequence split over {world} GPU(s), "
+                      "NCCL all-gather of (O, LSE) partials + local merge",
+            "tokens_per_rank_per_seq": c["local"], "ms_per_step": round(ms, 4),
+            "per_rank_gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+            "all_ranks_gbs": round(gbs * world, 1), "tok_per_s": round(batch / (ms * 1e-3), 1),
+            "allgather_us": round(ex_ms * 1e3, 1), "allgather_share": round(ex_ms / ms, 4),
+            "exchange_bytes": batch * hq * (d + 1) * 4, "scaling": "strong", "parity_vs_single_rank": parity}
 
 
 def hf_fused_measurement(device, batch=8, ctx=32768, hq=32, hkv=8, d=128, iters=50):
@@ -685,9 +932,10 @@ def run_reference(args, rank, world):
     torch.set_num_threads(cores)
     n_seqs = 2
     w = cpu_workload(n_seqs)
-    for _ in range(max(1, min(args.warmup, 3))):
+    warm = max(args.warmup, 3)  # the same rule as the GPU arm
+    for _ in range(warm):
         cpu_step(w)
-    steps = max(1, min(args.steps, 40))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_step(w)
@@ -698,7 +946,7 @@ def run_reference(args, rank, world):
               f"{steps} timed steps")
     return {
         "impl": "reference", "metric": "paged_tq4_decode_tok_per_s", "value": val, "unit": "tok/s",
-        "n_gpus": world, "steps": steps, "warmup": max(1, min(args.warmup, 3)),
+        "n_gpus": world, "steps": steps, "warmup": warm,
         "ms_per_step": round(dt / steps * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "Llama-3.1-8B-shaped single-layer paged TQ4 decode (CPU sample)",
@@ -725,12 +973,19 @@ def main():
     ap.add_argument("--e2e-serial", action="store_true",
                     help="end-to-end: copies and kernels of a step on one stream (no staging of the next step)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill measurement")
+    ap.add_argument("--no-side-configs", action="store_true",
+                    help="skip the serving-mix / long-context / sequence-split measurements after the headline")
+    ap.add_argument("--no-dense-rows", action="store_true",
+                    help="N > 1: skip the second timing of the headline step on dense token rows")
     ap.add_argument("--extra", default="", help="comma list of side measurements run after the timed region: "
                                                 "serving_mix, long_context, long_context_small, hf_fused")
     ap.add_argument("--row-bytes", type=int, default=0,
                     help="token-row stride of the cache in bytes (>= kv_heads*(head_dim+8), multiple of 16); "
                          "0 = vLLM's padded page format, which the reference uses")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly (no CUDA graph)")
+    ap.add_argument("--min-region", type=float, default=0.5,
+                    help="repeat the block of --steps timed steps until the timed region is this many seconds")
+    ap.add_argument("--max-blocks", type=int, default=2000)
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: run ONE rank's share of a W-GPU head-sharded job on this GPU")
     args = ap.parse_args()
@@ -758,6 +1013,9 @@ def main():
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
+    par = (line.get("split_kv") or {}).get("parity_vs_single_rank") if isinstance(line, dict) else None
+    if par is not None and not par.get("ok", False):
+        raise SystemExit(f"sequence-split decode disagrees with the single-rank kernel: {par}")
 
 
 if __name__ == "__main__":

@@ -141,6 +141,9 @@ def main() -> None:
         ("k4v3", 128, 2, 8, 3, True),
         ("d96", 96, 4, 4, 4, False),
         ("d64g7", 64, 1, 7, 4, False),
+        # K/V regions on 16-byte boundaries (KV heads a multiple of 4): the layout the tcgen05
+        # chunked-prefill kernel accepts
+        ("k4v4h4", 128, 4, 16, 4, True),
     ):
         kq = TurboQuantMSE(d, 4, seed=42)
         vq = kq if vbits == 4 else TurboQuantMSE(d, vbits, seed=42)

@@ -50,7 +50,7 @@ def _run(ops, mode, **kw):
 
 
 @pytest.mark.parametrize("mode", MODES)
-@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7"])
+@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7", "k4v4h4"])
 def test_decode_golden(ops, golden, tag, mode):
     """Decode against the output the reference's dequantize + fp32 SDPA produced."""
     g = golden("paged.npz")
@@ -65,7 +65,7 @@ def test_decode_golden(ops, golden, tag, mode):
 
 
 @pytest.mark.parametrize("mode", MODES + [3])
-@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7"])
+@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7", "k4v4h4"])
 @pytest.mark.parametrize("window", [None, 9])
 def test_prefill_golden(ops, golden, tag, window, mode):
     g = golden("paged.npz")

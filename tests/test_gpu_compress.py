@@ -119,7 +119,7 @@ def _regions(cache: torch.Tensor, h: int, d: int):
     return kp, kn, vp, vn, flat[:, tot:]
 
 
-@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7"])
+@pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7", "k4v4h4"])
 def test_write_paged_golden(ops, golden, tag):
     """Fused K+V cache write against the cache the reference's _compress_and_store produced."""
     g = golden("paged.npz")
@@ -153,19 +153,23 @@ def test_write_paged_slot_semantics(ops):
     ref = torch.zeros(4, bs, width, dtype=torch.uint8)
     O.write_paged(k, v, ref, slots, pr.rot, pr.kb, pr.vb)
     flat, rflat = cache.cpu().reshape(-1, width), ref.reshape(-1, width)
+    written = [5, 40, 7]
     for s_ in range(flat.shape[0]):
-        if s_ in (5, 40, 7):
-            assert index_mismatch(flat[s_:s_ + 1, :512].reshape(1, 8, 64),
-                                  rflat[s_:s_ + 1, :512].reshape(1, 8, 64)) <= 1e-2
+        if s_ in written:
             assert flat[s_].any()
         else:
             assert not flat[s_].any(), f"slot {s_} should be empty"
+    # K and V index bytes of the three written rows, the same 1e-4 gate as every other write test
+    lay = O.row_layout(8, 128)
+    for lo in (0, lay[1]):
+        assert index_mismatch(flat[written, lo:lo + 512].reshape(3, 8, 64),
+                              rflat[written, lo:lo + 512].reshape(3, 8, 64)) <= 1e-4
     # overwrite slot 5 with token 4
     ops.tq4_write_paged(k[4:5].cuda(), v[4:5].cuda(), cache, torch.tensor([5]).cuda(),
                         p["even"], p["odd"], p["kb"], p["vb"])
     O.write_paged(k[4:5], v[4:5], ref, torch.tensor([5]), pr.rot, pr.kb, pr.vb)
     assert index_mismatch(cache.cpu().reshape(-1, width)[5:6, :512].reshape(1, 8, 64),
-                          ref.reshape(-1, width)[5:6, :512].reshape(1, 8, 64)) <= 1e-2
+                          ref.reshape(-1, width)[5:6, :512].reshape(1, 8, 64)) <= 1e-4
 
 
 def test_write_paged_bad_slot_sets_flag(ops):
@@ -261,3 +265,33 @@ def test_write_paged_tensor_core_kernel_edges(ops, dtype, n_tok, strided):
     untouched = torch.ones(nblk * bs, dtype=torch.bool)
     untouched[slots[keep]] = False
     assert not got[untouched].any()
+
+
+@pytest.mark.parametrize("kernel", ["ffma", "tensor_core"])
+def test_norm_and_index_parity_statistics(ops, kernel, record_property, capsys):
+    """How close the two write kernels are to the oracle on 131 072 seeded vectors (head_dim 128):
+    fraction of fp32 norms that are bit-identical, largest norm distance in ulp, index mismatch
+    rate.  Gates: max 4 ulp, mismatch <= 1e-4 (the tensor-core kernel rotates with a split-TF32
+    product, so its index mismatch is small but not zero; its norms use the FFMA kernels' order)."""
+    pr = Prims(128)
+    p = pr.cuda()
+    n_tok, h = 16384, 8
+    k, _ = O.synthetic_kv(n_tok, h, 128, seed=5, dtype=torch.bfloat16)
+    if kernel == "ffma":  # at most 8192 vectors per call stay on the FFMA kernels
+        outs = [ops.tq4_compress(k[i:i + 1024].cuda(), p["even"], p["odd"], p["kb"]) for i in range(0, n_tok, 1024)]
+        packed = torch.cat([o[0] for o in outs]).cpu()
+        norms = torch.cat([o[1] for o in outs]).cpu()
+    else:
+        packed, norms = (x.cpu() for x in ops.tq4_compress(k.cuda(), p["even"], p["odd"], p["kb"]))
+    ref_p, ref_n = O.compress_rows(k, pr.rot, pr.kb)
+    ulps = ulp_diff(norms.reshape(-1), ref_n.reshape(-1))
+    frac_identical = float((ulps == 0).float().mean())
+    mism = index_mismatch(packed, ref_p)
+    for name, val in (("norm_bit_identical_frac", frac_identical), ("norm_max_ulp", int(ulps.max())),
+                      ("index_mismatch", mism)):
+        record_property(f"{kernel}_{name}", val)
+    with capsys.disabled():
+        print(f"\n[parity statistics] {kernel}: norms bit-identical {frac_identical:.4f}, max {int(ulps.max())} ulp, "
+              f"index mismatch {mism:.2e} over {n_tok * h} vectors")
+    assert ulps.max() <= MAX_NORM_ULP
+    assert mism <= MAX_INDEX_MISMATCH

@@ -225,3 +225,50 @@ def test_forward_guards(backend):
     assert not impl.forward(None, None, None, None, torch.zeros(1), None, output=out).any()
     with pytest.raises(NotImplementedError, match="output quantization"):
         impl.forward(None, None, None, None, None, None, output=out, output_scale=torch.ones(1))
+
+
+def test_cg_buffers_on_cpu_cache_lazy_and_eager(backend):
+    """`_init_cg_buffers` is pure allocation, so its shapes can be checked without a GPU: the
+    reference-named decompress targets exist after it, eagerly when the FlashAttention fallback is
+    reachable and on first access otherwise (reference: vllm/tq4_backend.py:503-514)."""
+    cache = torch.zeros(500, 16, 8 * 256, dtype=torch.uint8)
+    for fused in (True, False):
+        impl = _bare_impl(backend)
+        impl._fused_paged_available = fused
+        with pytest.raises(AttributeError):
+            impl._cg_decompress_k  # noqa: B018  (nothing before _init_cg_buffers)
+        impl._init_cg_buffers(cache, compute_dtype=torch.bfloat16)
+        assert impl._cg_buffers_ready
+        assert ("_cg_decompress_k" in impl.__dict__) is (not fused)
+        assert impl._cg_decompress_k.shape == (6144, 8, 128) and impl._cg_decompress_k.dtype == torch.bfloat16
+        assert impl._cg_decompress_v.shape == (6144, 8, 128)
+        assert impl._cg_prefill_k.shape == impl._cg_prefill_v.shape == (2048, 8, 128)
+        assert impl._max_prefill_blocks == 128
+        assert impl._cg_compress_row.shape == (1, 1088)
+        assert impl._cg_q_rot.shape == (1, 32, 128) and impl._cg_q_rot_cast.dtype == torch.bfloat16
+    with pytest.raises(AttributeError):
+        impl._not_an_attribute  # noqa: B018
+
+
+def test_device_error_flag_is_decoded_and_raised():
+    """The host layers turn a set device error flag into an exception (fed a fake flag value here)."""
+    from turboquant_vllm import _native as nv
+    from turboquant_vllm.kernels import ops
+
+    assert nv.describe_device_errors(0) == "no error"
+    assert "TQ4_DEV_BAD_SLOT" in nv.describe_device_errors(nv.DEV_BAD_SLOT)
+    text = nv.describe_device_errors(nv.DEV_BAD_BLOCK | nv.DEV_TIMEOUT | 64)
+    assert "TQ4_DEV_BAD_BLOCK" in text and "TQ4_DEV_TIMEOUT" in text and "0x40" in text
+    ops.raise_on_device_errors(torch.device("cpu"), "nowhere", flag=0)  # clean flag: no raise
+    with pytest.raises(RuntimeError, match=r"forward: TQ4 kernel reported .*TQ4_DEV_TIMEOUT.*flag 0x4"):
+        ops.raise_on_device_errors(torch.device("cpu"), "forward", flag=nv.DEV_TIMEOUT)
+
+
+def test_error_check_switch(monkeypatch):
+    from turboquant_vllm.kernels import ops
+
+    monkeypatch.delenv("TQ4_CHECK_ERRORS", raising=False)
+    assert ops.error_checks_enabled() is False
+    for val, want in (("1", True), ("true", True), ("0", False), ("", False)):
+        monkeypatch.setenv("TQ4_CHECK_ERRORS", val)
+        assert ops.error_checks_enabled() is want

@@ -97,7 +97,7 @@ def test_zero_vector_tie_rule():
     assert torch.all(packed == 0x77)
 
 
-PAGED_TAGS = ["k4v4", "k4v3", "d96", "d64g7"]
+PAGED_TAGS = ["k4v4", "k4v3", "d96", "d64g7", "k4v4h4"]
 
 
 def _paged(golden, tag):

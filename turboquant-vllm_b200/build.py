@@ -23,29 +23,45 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+def _deps() -> list[str]:
+    return glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + [
+        os.path.join(ROOT, "include", "tq4.h")]
+
+
 def needs_build() -> bool:
     if not os.path.exists(OUT):
         return True
     t = os.path.getmtime(OUT)
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(ROOT, "include", "tq4.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+    return any(os.path.getmtime(d) > t for d in sources() + _deps())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every .cu to an object file (in parallel, only those older than their inputs) and
+    link the shared library."""
     if not force and not needs_build():
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
+    obj_dir = os.path.join(HERE, "build")
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [
-        nvcc, "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo",
-        "-gencode", "arch=compute_100a,code=sm_100a",
-        "-I", os.path.join(ROOT, "include"), "-I", CSRC,
-        "-o", OUT,
-    ]
+    flags = ["-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo",
+             "-gencode", "arch=compute_100a,code=sm_100a",
+             "-I", os.path.join(ROOT, "include"), "-I", CSRC]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += sources()
-    subprocess.run(cmd, check=True)
+        flags += ["-Xptxas", "-v"]
+    hdr_time = max(os.path.getmtime(d) for d in _deps())
+    jobs, objs = [], []
+    for src in sources():
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        stale = force or verbose or not os.path.exists(obj) or os.path.getmtime(obj) < max(
+            os.path.getmtime(src), hdr_time)
+        if stale:
+            jobs.append((src, subprocess.Popen([nvcc, "-c", *flags, "-o", obj, src])))
+    failed = [src for src, p in jobs if p.wait() != 0]
+    if failed:
+        raise subprocess.CalledProcessError(1, f"nvcc -c {' '.join(failed)}")
+    subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", OUT, *objs], check=True)
     return OUT
 
 

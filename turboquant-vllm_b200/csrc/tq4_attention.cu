@@ -461,15 +461,7 @@ prologue_kernel(const AttnArgs a, const CompressArgs w, const int has_attn, cons
 template <int D>
 int launch_prologue_t(const AttnArgs* a, const CompressArgs* w, cudaStream_t st) {
   using P = PrologueCfg<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(prologue_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)P::smem_bytes) != cudaSuccess)
-      return TQ4_ERR_CUDA;
-    cudaFuncSetAttribute(prologue_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         cudaSharedmemCarveoutMaxShared);
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem<prologue_kernel<D>>((int)P::smem_bytes, true)) return TQ4_ERR_CUDA;
   const int64_t n_q = a ? (int64_t)a->sh.rows * a->sh.Hq : 0;
   const int64_t n_w = w ? w->n_tokens * w->num_heads * w->n_sources : 0;
   const int64_t chunks = (n_q + P::VC - 1) / P::VC + (n_w + P::VC - 1) / P::VC;
@@ -478,8 +470,11 @@ int launch_prologue_t(const AttnArgs* a, const CompressArgs* w, cudaStream_t st)
   if (blocks < 1) blocks = 1;
   static const AttnArgs no_attn{};
   static const CompressArgs no_write{};
+  // First kernel of an entry point: a plain stream-ordered launch.  It reads tensors the caller's
+  // preceding kernel may have produced (q, key, value, seq_lens), so it must not start before that
+  // kernel has completed, whatever launch style the caller's kernels use.
   if (launch_kernel(prologue_kernel<D>, dim3((unsigned)blocks + (a ? 1 : 0)), dim3(P::THREADS), P::smem_bytes,
-                    st, true, a ? *a : no_attn, w ? *w : no_write, a ? 1 : 0, w ? 1 : 0) != cudaSuccess)
+                    st, false, a ? *a : no_attn, w ? *w : no_write, a ? 1 : 0, w ? 1 : 0) != cudaSuccess)
     return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
@@ -694,13 +689,7 @@ template <int D, int GC>
 int launch_fp32_t(const AttnArgs& a, cudaStream_t st) {
   using Cfg = Fp32Cfg<D, GC>;
   const size_t smem = Cfg::smem_per_warp * kMaxWarpsPerCta;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attention_fp32_kernel<D, GC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-      return TQ4_ERR_CUDA;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem<attention_fp32_kernel<D, GC>>((int)smem)) return TQ4_ERR_CUDA;
   const int warps = a.sh.HPC * a.sh.TPC;
   if (launch_kernel(attention_fp32_kernel<D, GC>, dim3(a.sh.ctas * a.sh.n_slices), dim3(warps * 32), smem, st,
                     true, a) != cudaSuccess)
@@ -964,35 +953,29 @@ __global__ void __launch_bounds__(D) combine_kernel(const CombineArgs a) {
 }
 
 template <int D>
-int launch_combine_t(const CombineArgs& c, cudaStream_t st) {
+int launch_combine_t(const CombineArgs& c, cudaStream_t st, bool pdl) {
   constexpr size_t smem = ((size_t)(D <= 128 ? D * D : 0) + kCombHeads * D +
                            kCombMaxParts * kCombHeads + 2 * kCombHeads) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(combine_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
-      return TQ4_ERR_CUDA;
-    // same shared-memory carve-out as the attention kernel it follows: no reconfiguration between them
-    cudaFuncSetAttribute(combine_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         cudaSharedmemCarveoutMaxShared);
-    attr_set = true;
-  }
+  // (same shared-memory carve-out as the attention kernel it follows: no reconfiguration between them)
+  if (!ensure_dynamic_smem<combine_kernel<D>>((int)smem, true)) return TQ4_ERR_CUDA;
   const int64_t n_vec = (int64_t)c.rows * c.Hq;
   int64_t grid = (n_vec + kCombHeads - 1) / kCombHeads;
   if (grid > 3 * (int64_t)sm_count()) grid = 3 * (int64_t)sm_count();
-  if (launch_kernel(combine_kernel<D>, dim3((unsigned)grid), dim3(D), smem, st, true, c) != cudaSuccess)
+  if (launch_kernel(combine_kernel<D>, dim3((unsigned)grid), dim3(D), smem, st, pdl, c) != cudaSuccess)
     return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
   return TQ4_OK;
 }
 
-int launch_combine(const CombineArgs& c, int D, cudaStream_t st) {
+// pdl: the launch follows another kernel of the same entry point (false for the stand-alone merge,
+// whose partials come from the caller's preceding kernel or collective)
+int launch_combine(const CombineArgs& c, int D, cudaStream_t st, bool pdl) {
   if (c.rows == 0) return TQ4_OK;
   switch (D) {
-    case 64: return launch_combine_t<64>(c, st);
-    case 96: return launch_combine_t<96>(c, st);
-    case 128: return launch_combine_t<128>(c, st);
-    case 256: return launch_combine_t<256>(c, st);
+    case 64: return launch_combine_t<64>(c, st, pdl);
+    case 96: return launch_combine_t<96>(c, st, pdl);
+    case 128: return launch_combine_t<128>(c, st, pdl);
+    case 256: return launch_combine_t<256>(c, st, pdl);
   }
   return TQ4_ERR_UNSUPPORTED;
 }
@@ -1000,18 +983,11 @@ int launch_combine(const CombineArgs& c, int D, cudaStream_t st) {
 template <int D>
 int launch_qrot_plan_t(const AttnArgs& a, cudaStream_t st) {
   using Q = QrotCfg<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(qrot_plan_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Q::smem_bytes) != cudaSuccess)
-      return TQ4_ERR_CUDA;
-    cudaFuncSetAttribute(qrot_plan_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         cudaSharedmemCarveoutMaxShared);
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem<qrot_plan_kernel<D>>((int)Q::smem_bytes, true)) return TQ4_ERR_CUDA;
   const int64_t n_vec = (int64_t)a.sh.rows * a.sh.Hq;
   const unsigned grid = (unsigned)((n_vec + Q::VB - 1) / Q::VB) + 1;
-  if (launch_kernel(qrot_plan_kernel<D>, dim3(grid), dim3(Q::THREADS), Q::smem_bytes, st, true, a) !=
+  // (first kernel of an entry point: plain stream-ordered launch, see launch_prologue_t)
+  if (launch_kernel(qrot_plan_kernel<D>, dim3(grid), dim3(Q::THREADS), Q::smem_bytes, st, false, a) !=
       cudaSuccess)
     return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
@@ -1198,7 +1174,7 @@ static int attention_impl(
     c.lse_out = lse_out;
     c.out_rotated = out_rotated;
     prof_begin(TQ4_PROF_COMBINE, st);
-    rc = launch_combine(c, head_dim, st);
+    rc = launch_combine(c, head_dim, st, true);
     prof_end(TQ4_PROF_COMBINE, st);
     if (rc != TQ4_OK) return rc;
   }
@@ -1311,7 +1287,7 @@ extern "C" int tq4_combine_partials(const float* parts_o, const float* parts_lse
   c.out_dtype = out_dtype;
   c.out_token_stride = out_token_stride;
   c.out_head_stride = out_head_stride;
-  return launch_combine(c, head_dim, (cudaStream_t)stream);
+  return launch_combine(c, head_dim, (cudaStream_t)stream, false);
 }
 
 // ======================================================================================

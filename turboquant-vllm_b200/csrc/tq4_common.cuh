@@ -29,8 +29,11 @@ void prof_end(int kind, cudaStream_t st);
 // has finished, if that launch was made with launch_kernel(..., pdl = true); the dependent kernel
 // calls pdl_wait() before it reads or writes anything a predecessor touches: after the wait, the
 // preceding kernel has completed and its stores are visible.  Rules kept by every kernel here:
-//  * before pdl_wait() a kernel only reads caller inputs (q, centroids, Pi, seq_lens) and writes
-//    shared memory or registers;
+//  * the FIRST kernel an entry point launches is a plain stream-ordered launch (pdl = false): its
+//    inputs may come from the caller's preceding kernel, which may itself trigger dependents early;
+//  * the later kernels of the same entry point are launched with pdl = true; before pdl_wait() they
+//    only read caller inputs (which the first kernel's launch has already ordered behind the
+//    caller's work) and write shared memory or registers;
 //  * a kernel launched with pdl = true calls pdl_wait() on every path before it exits, so its own
 //    completion implies the completion of everything before it in the stream.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -149,15 +152,42 @@ __device__ __forceinline__ void load_strip(const void* const (&base)[V], float (
       out[i][v] = base[v] ? to_float<T>(reinterpret_cast<const T*>(base[v])[32 * i]) : 0.f;
 }
 
+// ---- per-device host state ---------------------------------------------------------------------
+// A process may drive several GPUs (a model spread over devices, one thread per GPU).  Function
+// attributes set with cudaFuncSetAttribute and device properties belong to ONE device, so
+// everything remembered on the host side is indexed by the ordinal of the current device.
+constexpr int kMaxDevices = 64;
+inline int device_ordinal() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
 inline int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
+  static int n[kMaxDevices];
+  const int dev = device_ordinal();
+  if (dev < 0) return 148;
+  if (n[dev] == 0) {
+    cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (n[dev] <= 0) n[dev] = 148;
   }
-  return n;
+  return n[dev];
+}
+
+// Opt `Kernel` in to `bytes` of dynamic shared memory on the current device (once per device and
+// kernel; again if a later call asks for more).
+template <auto Kernel>
+inline bool ensure_dynamic_smem(int bytes, bool max_carveout = false) {
+  static int set_bytes[kMaxDevices];
+  const int dev = device_ordinal();
+  if (dev < 0) return false;
+  if (set_bytes[dev] >= bytes && set_bytes[dev] > 0) return true;
+  if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+    return false;
+  if (max_carveout)
+    cudaFuncSetAttribute(Kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  set_bytes[dev] = bytes;
+  return true;
 }
 
 // Arguments of the compress / cache-write kernels (tq4_compress.cu) and of the write part of the

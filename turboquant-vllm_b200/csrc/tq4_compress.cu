@@ -331,13 +331,7 @@ int launch_compress(const CompressArgs& a, cudaStream_t st) {
     TQ4_CHECK_LAUNCH();
     return TQ4_OK;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(compress_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Cfg::smem_bytes) != cudaSuccess)
-      return TQ4_ERR_CUDA;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem<compress_kernel<D, T>>((int)Cfg::smem_bytes)) return TQ4_ERR_CUDA;
   const int64_t n_tiles = (total_rows + kRowsPerWarp - 1) / kRowsPerWarp;
   int64_t blocks = (n_tiles + kWarps - 1) / kWarps;
   const int64_t cap = (int64_t)sm_count() * 2;

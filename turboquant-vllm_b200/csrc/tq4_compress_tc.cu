@@ -450,14 +450,8 @@ static bool make_x_map(CUtensorMap* m, const void* x, int64_t rows) {
 
 template <typename T, bool XT>
 static int launch_tc_t(const CompressArgs& a, const CUtensorMap& m0, const CUtensorMap& m1, cudaStream_t st) {
-  static bool attr_set = false;
   const int smem = (int)kSmemBytes + (XT ? (int)kXBytes : 0) + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(compress_tc_kernel<T, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
-      return TQ4_ERR_CUDA;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem<compress_tc_kernel<T, XT>>(smem)) return TQ4_ERR_CUDA;
   const int64_t rows_per_src = a.n_tokens * a.num_heads;
   int64_t blocks = XT ? ((rows_per_src + kRows - 1) / kRows) * a.n_sources
                       : (rows_per_src * a.n_sources + kRows - 1) / kRows;

@@ -983,21 +983,22 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
   using C = MmaCfg<D, ALIGNED>;
   // All opt-in shared memory of the SM (one CTA per SM by design): the 64 KB table sits on a
   // 64 KB boundary of the shared window and whole rings are packed on both sides of it.
-  static int smem_total = 0;
-  auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA, BOX>;
-  if (smem_total == 0) {
-    int dev = 0, optin = 0;
-    cudaGetDevice(&dev);
+  constexpr auto kern = attention_mma_kernel<D, NB, ALIGNED, PAGE16, WARPS, TMA, BOX>;
+  static int smem_avail[kMaxDevices];  // opt-in limit minus the kernel's static shared memory, per device
+  const int dev = device_ordinal();
+  if (dev < 0) return TQ4_ERR_CUDA;
+  if (smem_avail[dev] == 0) {
+    int optin = 0;
     cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) return TQ4_ERR_CUDA;
-    const int want = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
-    const int stage = TMA ? (BOX == 3 ? 16 * kRowPitch : C::template tma_stage<VWIDE>()) : C::kStageBytes;
-    if (want < (int)kTableBytes + a.sh.HPC * a.sh.TPC * kStages * 2 * stage) return TQ4_ERR_UNSUPPORTED;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess)
-      return TQ4_ERR_CUDA;
-    smem_total = want;
+    smem_avail[dev] = optin - (int)fa.sharedSizeBytes;  // static + dynamic share the opt-in limit
   }
+  const int smem_total = smem_avail[dev];
+  const int stage = TMA ? (BOX == 3 ? 16 * kRowPitch : C::template tma_stage<VWIDE>()) : C::kStageBytes;
+  // the table may have to move up by almost its own size to reach a 64 KB boundary
+  if (smem_total < (int)kTableBytes + a.sh.HPC * a.sh.TPC * kStages * 2 * stage) return TQ4_ERR_UNSUPPORTED;
+  if (!ensure_dynamic_smem<kern>(smem_total)) return TQ4_ERR_CUDA;
   CUtensorMap tm_data, tm_v, tm_norm;
   memset(&tm_data, 0, sizeof(tm_data));
   memset(&tm_v, 0, sizeof(tm_v));

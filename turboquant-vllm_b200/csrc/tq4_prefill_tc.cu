@@ -598,14 +598,8 @@ bool make_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes) {
 
 template <int G>
 int launch_t(const AttnArgs& a, cudaStream_t st) {
-  static bool attr_set = false;
   const int smem = (int)kSmemBytes + 1024;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(prefill_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
-      return TQ4_ERR_CUDA;
-    attr_set = true;
-  }
+  if (!ensure_dynamic_smem<prefill_tc_kernel<G>>(smem)) return TQ4_ERR_CUDA;
   CUtensorMap tm_idx, tm_norm;
   memset(&tm_idx, 0, sizeof(tm_idx));
   memset(&tm_norm, 0, sizeof(tm_norm));

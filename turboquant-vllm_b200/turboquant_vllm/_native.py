@@ -6,6 +6,7 @@ device, the call raises.  The library is built in-tree by ``turboquant-vllm_b200
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
@@ -133,6 +134,43 @@ def require_cuda(*tensors: torch.Tensor) -> None:
                 "TQ4 kernels run on CUDA tensors only (sm_100a); got a tensor on "
                 f"{t.device}. There is no CPU fallback in this package."
             )
+
+
+_NO_GUARD = contextlib.nullcontext()
+
+
+def device_guard(device: torch.device):
+    """Context that makes ``device`` the current CUDA device for the duration of a library call.
+
+    The C entry points launch on the current device (kernel attributes, the SM count and the
+    built-in scratch are looked up for it), so tensors on ``cuda:1`` need ``cuda:1`` current even
+    when the caller left ``cuda:0`` selected, as HuggingFace models spread with ``device_map`` do.
+    """
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(idx)
+
+
+def call(device: torch.device, name: str, *args):
+    """Call entry point ``name`` with ``device`` current."""
+    with device_guard(device):
+        return getattr(lib(), name)(*args)
+
+
+_DEV_BITS = ((DEV_BAD_SLOT, "slot_mapping entry outside the cache (TQ4_DEV_BAD_SLOT)"),
+             (DEV_BAD_BLOCK, "block_table entry outside [0, num_blocks) or sequence longer than its "
+                             "block-table row (TQ4_DEV_BAD_BLOCK)"),
+             (DEV_TIMEOUT, "a bounded device-side wait gave up (TQ4_DEV_TIMEOUT)"))
+
+
+def describe_device_errors(flag: int) -> str:
+    """Text for the TQ4_DEV_* bits a kernel OR-ed into the device error flag."""
+    parts = [text for bit, text in _DEV_BITS if flag & bit]
+    rest = flag & ~(DEV_BAD_SLOT | DEV_BAD_BLOCK | DEV_TIMEOUT)
+    if rest:
+        parts.append(f"unknown bits {rest:#x}")
+    return "; ".join(parts) if parts else "no error"
 
 
 def stream_ptr(device: torch.device) -> int:

@@ -15,6 +15,7 @@ Everything runs through the C ABI in ``include/tq4.h``; CPU tensors are rejected
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -57,11 +58,41 @@ def error_flag(device: torch.device) -> torch.Tensor:
 
 
 def read_and_clear_errors(device: torch.device) -> int:
-    """Synchronising read of the device error flag (for tests and debugging)."""
+    """Synchronising read of the device error flag; clears it."""
     f = error_flag(device)
     v = int(f.item())
-    f.zero_()
+    if v:
+        f.zero_()
     return v
+
+
+def error_checks_enabled() -> bool:
+    """``TQ4_CHECK_ERRORS`` (``1/true/yes``): the host layers (vLLM impl, HF cache, split-KV decode)
+    read the device error flag after each call and raise.  Off by default: the read synchronises
+    the stream, and it cannot happen while a CUDA graph is being captured."""
+    return os.environ.get("TQ4_CHECK_ERRORS", "").lower() in ("1", "true", "yes")
+
+
+def raise_on_device_errors(device: torch.device, where: str, *, flag: int | None = None) -> None:
+    """Raise ``RuntimeError`` if a kernel reported an out-of-range slot or block id, or a device-side
+    wait that gave up (the offending work was skipped, so outputs are incomplete).
+
+    Reads and clears the device flag (synchronising); ``flag`` substitutes an already known value.
+    Skipped while the current stream is capturing a CUDA graph.
+    """
+    if flag is None:
+        if torch.cuda.is_current_stream_capturing():
+            return
+        flag = read_and_clear_errors(device)
+    if flag:
+        raise RuntimeError(f"{where}: TQ4 kernel reported {nv.describe_device_errors(flag)} "
+                           f"(flag {flag:#x}); the affected rows were skipped")
+
+
+def maybe_raise_on_device_errors(device: torch.device, where: str) -> None:
+    """:func:`raise_on_device_errors` when ``TQ4_CHECK_ERRORS`` is set."""
+    if error_checks_enabled():
+        raise_on_device_errors(device, where)
 
 
 def _inner_contiguous(t: torch.Tensor) -> torch.Tensor:
@@ -95,7 +126,7 @@ def tq4_compress(
     else:
         packed = torch.empty(n, h, d // 2, dtype=torch.uint8, device=x.device)
         norms = torch.empty(n, h, 1, dtype=torch.float32, device=x.device)
-    st = nv.lib().tq4_compress_rows(
+    st = nv.call(x.device, "tq4_compress_rows",
         x.data_ptr(), nv.dtype_code(x.dtype), n, h, d, x.stride(0), x.stride(1),
         rotation_T_even.data_ptr(), rotation_T_odd.data_ptr(),
         boundaries.data_ptr(), boundaries.numel(),
@@ -112,7 +143,7 @@ def tq4_pack_rotated(rotated: torch.Tensor, boundaries: torch.Tensor) -> torch.T
     rotated = rotated.contiguous()
     m, d = rotated.shape
     packed = torch.empty(m, d // 2, dtype=torch.uint8, device=rotated.device)
-    st = nv.lib().tq4_pack_rotated_rows(
+    st = nv.call(rotated.device, "tq4_pack_rotated_rows",
         rotated.data_ptr(), m, d, boundaries.data_ptr(), boundaries.numel(),
         packed.data_ptr(), nv.stream_ptr(rotated.device),
     )
@@ -139,7 +170,7 @@ def tq4_decompress(
     else:
         nv.require_cuda(out)
         assert out.is_contiguous() and out.numel() >= n * h * d
-    st = nv.lib().tq4_decompress_rows(
+    st = nv.call(packed.device, "tq4_decompress_rows",
         packed.data_ptr(), norms.data_ptr(), centroids.data_ptr(), centroids.numel(),
         n * h, d, out.data_ptr(), nv.dtype_code(out.dtype), nv.stream_ptr(packed.device),
     )
@@ -168,7 +199,7 @@ def tq4_decompress_cache(
         out_v = torch.empty(n, num_kv_heads, head_dim, dtype=dtype, device=kv_cache.device)
     assert out_k.dtype == out_v.dtype and out_k.is_contiguous() and out_v.is_contiguous()
     assert out_k.numel() >= n * num_kv_heads * head_dim and out_v.numel() >= n * num_kv_heads * head_dim
-    st = nv.lib().tq4_decompress_cache(
+    st = nv.call(kv_cache.device, "tq4_decompress_cache",
         kv_cache.data_ptr(), width, n, num_kv_heads, head_dim,
         k_centroids.data_ptr(), k_centroids.numel(), v_centroids.data_ptr(), v_centroids.numel(),
         out_k.data_ptr(), out_v.data_ptr(), nv.dtype_code(out_k.dtype), nv.stream_ptr(kv_cache.device),
@@ -203,7 +234,7 @@ def tq4_write_paged(
         slot_mapping = slot_mapping.to(torch.int64)
     slot_mapping = slot_mapping.contiguous()
     nb, bs, width = kv_cache.shape
-    st = nv.lib().tq4_write_paged(
+    st = nv.call(key.device, "tq4_write_paged",
         key.data_ptr(), value.data_ptr(), nv.dtype_code(key.dtype), n, h, d,
         key.stride(0), key.stride(1), value.stride(0), value.stride(1),
         slot_mapping.data_ptr(), slot_mapping.numel(),
@@ -294,8 +325,8 @@ def paged_tq4_attention(
                  key.stride(0), key.stride(1), value.stride(0), value.stride(1),
                  slot_mapping.data_ptr(), slot_mapping.numel(), rot_even.data_ptr(), rot_odd.data_ptr(),
                  k_bounds.data_ptr(), k_bounds.numel(), v_bounds.data_ptr(), v_bounds.numel())
-    entry = nv.lib().tq4_write_and_attention if write is not None else nv.lib().tq4_paged_attention
-    st = entry(
+    st = nv.call(
+        q.device, "tq4_write_and_attention" if write is not None else "tq4_paged_attention",
         *wargs,
         q.data_ptr(), nv.dtype_code(q.dtype), t, seq_lens.numel(), hq, num_kv_heads, d,
         q.stride(0), q.stride(1),
@@ -467,7 +498,7 @@ def combine_partials(
     w, t, hq, d = parts_o.shape
     if out is None:
         out = torch.empty(t, hq, d, dtype=out_dtype, device=parts_o.device)
-    st = nv.lib().tq4_combine_partials(
+    st = nv.call(parts_o.device, "tq4_combine_partials",
         parts_o.data_ptr(), parts_lse.data_ptr(), w, t, hq, d, rotation.data_ptr(),
         out.data_ptr(), nv.dtype_code(out.dtype), out.stride(0), out.stride(1),
         nv.stream_ptr(parts_o.device),
@@ -511,7 +542,7 @@ def paged_tq4_attention_static(
     assert rotation.dtype == torch.float32 and rotation.is_contiguous()
     if query_start_loc is not None:
         assert query_start_loc.dtype == torch.int32 and query_start_loc.is_contiguous()
-    st = nv.lib().tq4_paged_attention_static(
+    st = nv.call(q.device, "tq4_paged_attention_static",
         q.data_ptr(), nv.dtype_code(q.dtype), t, seq_lens.numel(), hq, num_kv_heads, d,
         q.stride(0), q.stride(1),
         kv_cache.data_ptr(), kv_cache.stride(0), kv_cache.stride(1), kv_cache.shape[0], block_size,
@@ -520,7 +551,7 @@ def paged_tq4_attention_static(
         rotation.data_ptr(), float(1.0 / math.sqrt(d) if sm_scale is None else sm_scale),
         int(bool(causal)), int(sliding_window or 0),
         out.data_ptr(), nv.dtype_code(out.dtype), out.stride(0), out.stride(1),
-        mode, None, nv.stream_ptr(q.device),
+        mode, error_flag(q.device).data_ptr(), nv.stream_ptr(q.device),
     )
     nv.check(st, "paged_tq4_attention_static")
     return out

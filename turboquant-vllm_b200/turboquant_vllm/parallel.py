@@ -77,13 +77,16 @@ def split_kv_decode(
     out_dtype: torch.dtype | None = None,
     attend: Callable | None = None,
     combine: Callable | None = None,
+    exchange_events: list | None = None,
 ) -> torch.Tensor:
     """Decode attention when each rank holds a token slice of every sequence.
 
     ``seq_lens_local[i]`` is the number of tokens of sequence i stored on THIS rank (0 allowed),
     ``block_table_local`` addresses this rank's cache.  Returns the full attention output
     ``[num_seqs, Hq, D]`` on every rank.  ``attend`` / ``combine`` default to the CUDA kernels
-    (injectable so that the wiring can be exercised without a GPU).
+    (injectable so that the wiring can be exercised without a GPU).  ``exchange_events``: a list
+    that receives one ``(start, end)`` pair of CUDA events recorded on the current stream around the
+    exchange (packing, all-gather, unpacking), for callers that want its share of the step.
     """
     from turboquant_vllm.kernels import ops
 
@@ -99,5 +102,15 @@ def split_kv_decode(
             return ops.combine_partials(po, pl, rotation, out_dtype=out_dtype or q.dtype)
     lse = torch.empty(t, hq, dtype=torch.float32, device=q.device)
     o_rot = attend(q, lse)
-    parts_o, parts_lse = gather_partials(o_rot, lse, group)
-    return combine(parts_o, parts_lse)
+    if exchange_events is not None and q.is_cuda:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        parts_o, parts_lse = gather_partials(o_rot, lse, group)
+        e1.record()
+        exchange_events.append((e0, e1))
+    else:
+        parts_o, parts_lse = gather_partials(o_rot, lse, group)
+    out = combine(parts_o, parts_lse)
+    if q.is_cuda:
+        ops.maybe_raise_on_device_errors(q.device, "split_kv_decode")
+    return out

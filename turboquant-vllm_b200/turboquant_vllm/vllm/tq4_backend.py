@@ -280,11 +280,35 @@ class TQ4AttentionImpl(FlashAttentionImpl):
             or getattr(self, "sinks", None) is not None
         )
 
+    # Decompress targets of the FlashAttention fallback.  The reference allocates them in
+    # _init_cg_buffers whatever path is active (tq4_backend.py:503-514); with the fused kernels they
+    # are dead weight (up to 2 x max_model_len x H x D elements), so here they come into being on
+    # first access: code and tests that read the attributes find them with the reference's shapes,
+    # a server that stays on the fused path never pays for them.
+    _LAZY_FALLBACK_ATTRS = frozenset(
+        {"_cg_decompress_k", "_cg_decompress_v", "_cg_prefill_k", "_cg_prefill_v", "_max_prefill_blocks"}
+    )
+
+    def __getattr__(self, name: str):
+        if name in TQ4AttentionImpl._LAZY_FALLBACK_ATTRS:
+            d = self.__dict__
+            if d.get("_cg_buffers_ready") and "_cg_cache_shape" in d:
+                self._init_fallback_buffers(None, d["_cg_compute_dtype"])
+                return d[name]
+        raise AttributeError(f"{type(self).__name__!r} object has no attribute {name!r}")
+
     def _init_cg_buffers(self, kv_cache: torch.Tensor, compute_dtype: torch.dtype) -> None:
         """One-time scratch allocation, sized from the cache and the scheduler limits."""
         num_blocks, block_size, _ = kv_cache.shape
         device = kv_cache.device
         h, d = self.num_kv_heads, self.head_size
+        self._cg_cache_shape = (num_blocks, block_size, device)
+        self._cg_compute_dtype = compute_dtype
+        self.__dict__.setdefault("_fallback_buffers_ready", False)
+        if self._fallback_buffers_ready:  # re-initialisation (e.g. another compute dtype)
+            self._fallback_buffers_ready = False
+            for name in TQ4AttentionImpl._LAZY_FALLBACK_ATTRS:
+                self.__dict__.pop(name, None)
         max_rows = max(1, min(self._max_prefill_len, num_blocks * block_size))
         self._cg_workspace = torch.empty(
             ops.attention_workspace_bytes(max_rows, self.num_heads, h, d),
@@ -303,11 +327,15 @@ class TQ4AttentionImpl(FlashAttentionImpl):
         logger.info("TQ4 scratch allocated: attention workspace %.1f MiB for %d query rows",
                     self._cg_workspace.numel() / 2**20, max_rows)
 
-    def _init_fallback_buffers(self, kv_cache: torch.Tensor, compute_dtype: torch.dtype) -> None:
-        """Decompress targets of the FlashAttention fallback (reference: tq4_backend.py:480-513)."""
-        num_blocks, block_size, _ = kv_cache.shape
+    def _init_fallback_buffers(self, kv_cache: torch.Tensor | None, compute_dtype: torch.dtype) -> None:
+        """Decompress targets of the FlashAttention fallback (reference: tq4_backend.py:480-513).
+        ``kv_cache=None`` sizes them from the cache seen by :meth:`_init_cg_buffers`."""
+        if kv_cache is not None:
+            num_blocks, block_size, device = kv_cache.shape[0], kv_cache.shape[1], kv_cache.device
+        else:
+            num_blocks, block_size, device = self._cg_cache_shape
         max_tokens = num_blocks * block_size
-        h, d, device = self.num_kv_heads, self.head_size, kv_cache.device
+        h, d = self.num_kv_heads, self.head_size
         dec_tokens = min(self._max_model_len, max_tokens)
         self._cg_decompress_k = torch.empty(dec_tokens, h, d, dtype=compute_dtype, device=device)
         self._cg_decompress_v = torch.empty_like(self._cg_decompress_k)
@@ -411,7 +439,7 @@ class TQ4AttentionImpl(FlashAttentionImpl):
         """Fallback prefill: write, rotate Q, decompress referenced blocks."""
         if kv_cache is not None and key is not None and value is not None:
             self._compress_and_store(key, value, kv_cache, attn_metadata.slot_mapping)
-        if not self._fallback_buffers_ready:
+        if not self.__dict__.get("_fallback_buffers_ready", False):
             self._init_fallback_buffers(kv_cache, query.dtype)
         q = query[: attn_metadata.num_actual_tokens]
         q_rot = (q.float() @ self._tq4_rotation.T).to(q.dtype)
@@ -432,7 +460,9 @@ class TQ4AttentionImpl(FlashAttentionImpl):
 
     def _fused_attention(self, query, kv_cache, attn_metadata, output, *, decode: bool, write=None):
         n = attn_metadata.num_actual_tokens
-        ws = self._cg_workspace if n <= self._cg_workspace_rows else None
+        ws = self.__dict__.get("_cg_workspace")
+        if ws is not None and n > self._cg_workspace_rows:
+            ws = None  # more rows than the scheduler limit announced: the shared grow-on-demand scratch
         if write is not None and not kv_cache.is_contiguous():
             self._compress_and_store(write[0], write[1], kv_cache, write[2])  # strided cache view
             write = None
@@ -449,6 +479,9 @@ class TQ4AttentionImpl(FlashAttentionImpl):
             sliding_window=self._sliding_window_tokens(),
             out=output[:n], workspace=ws, write=write,
         )
+        # opt-in (TQ4_CHECK_ERRORS=1): surface out-of-range slots / block ids and timed-out device
+        # waits as an exception instead of silently skipped rows; never during graph capture
+        ops.maybe_raise_on_device_errors(query.device, "TQ4AttentionImpl.forward")
         return output
 
     def _fused_decode_path(self, query, key, value, kv_cache, attn_metadata, output):
