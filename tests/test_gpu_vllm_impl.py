@@ -431,7 +431,8 @@ def test_paged_decompress_dedup_remap_and_overflow(backend, caplog):
     sl = torch.tensor([40, 17], dtype=torch.int32)
     kp, vp, remap = impl._decompress_cache_paged(cache, bt[:2].cuda(), sl.cuda(), torch.float16,
                                                   out_k=impl._cg_prefill_k, out_v=impl._cg_prefill_v)
-    used = sorted({int(bt[0, 0]), int(bt[0, 1]), int(bt[0, 2])})
+    used = sorted({int(bt[0, 0]), int(bt[0, 1]), int(bt[0, 2]), int(bt[1, 0]), int(bt[1, 1])})
+    assert len(used) == 4  # five referenced entries, one block shared
     assert kp.shape == (len(used), BS, H_KV, D) and remap.dtype == torch.int32
     assert kp.data_ptr() == impl._cg_prefill_k.data_ptr()  # the pre-allocated buffer was used
     for i, s in enumerate(sl.tolist()):
