@@ -46,6 +46,8 @@ typedef enum {
 #define TQ4_DEV_BAD_SLOT 1  /* slot_mapping entry >= num_cache_slots            */
 #define TQ4_DEV_BAD_BLOCK 2 /* block_table entry outside [0, num_blocks)         */
 #define TQ4_DEV_TIMEOUT 4   /* a bounded device-side wait gave up                */
+#define TQ4_DEV_WRITE_ORDER 8 /* tq4_write_and_attention: a new token's slot is not the last position of its
+                                 sequence; it was written, but this call's attention may not have seen it */
 
 /* Library identification: returns e.g. "tq4-sm100a 0.1". Host call. */
 const char* tq4_version(void);
@@ -177,8 +179,16 @@ int tq4_paged_attention(const void* q, int q_dtype, int64_t num_rows, int num_se
  * (same meaning and checks); the cache must be block-major contiguous
  * (cache_block_stride == block_size * cache_token_stride), which makes the flat slot
  * s = block * block_size + offset of slot_mapping address row s at cache + s * cache_token_stride.
- * n_tokens == 0 reduces to tq4_paged_attention, num_rows == 0 to tq4_write_paged.  Writes of more
- * than a few thousand vectors and head_dim 256 run the separate write kernel first.
+ * n_tokens == 0 reduces to tq4_paged_attention, num_rows == 0 to tq4_write_paged.
+ * Decode calls (query_start_loc == NULL) of up to 512 rows at head_dim <= 128 run as TWO launches:
+ * the attention kernel plans its tiles, rotates the queries and compresses the new tokens itself,
+ * then the merge kernel.  There token i must be the newest token of sequence i, i.e.
+ * slot_mapping[i] addresses position seq_lens[i] - 1 through block_table (what a decode step of a
+ * serving engine passes): the CTA that reads a sequence's last tile is the one that writes the
+ * token into it.  A token whose slot is elsewhere is still written, and TQ4_DEV_WRITE_ORDER is
+ * raised because this call's attention may have read that slot before the write; a token of a
+ * sequence with seq_lens[i] == 0 must have a negative slot.  Other calls (chunked prefill, more
+ * rows, head_dim 256) run the write kernel first, then prologue, attention and merge.
  * Replaces: the body of TQ4AttentionImpl.forward for a decode batch,
  *           src/turboquant_vllm/vllm/tq4_backend.py (_compress_and_store + _fused_decode_path).
  */

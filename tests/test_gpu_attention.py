@@ -305,9 +305,16 @@ def test_decode_full_size_properties(ops, mode):
     (32, 8, 128, 16, 4, 4, torch.bfloat16), (8, 2, 64, 32, 4, 3, torch.float16),
     (12, 4, 96, 16, 4, 4, torch.float32), (8, 4, 256, 16, 4, 4, torch.bfloat16),
 ])
-def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, vbits, dtype, mode):
-    """The fused step (cache write folded into the attention's first kernel) must leave the same
-    cache bytes and return the same output, bit for bit, as tq4_write_paged + attention."""
+def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, vbits, dtype, mode, monkeypatch):
+    """One decode step as a single call against tq4_write_paged + attention as two calls.
+
+    Decode calls at head_dim <= 128 compress the new tokens inside the attention kernel, rotating on
+    tensor cores with split fp16 operands: norms are bit-identical to the write kernel's, indices
+    agree to the 1e-4 bound of the write path (a coordinate within ~1e-7 of a bucket boundary may
+    land in the neighbouring bucket), and whenever the cache bytes agree the outputs are equal bit
+    for bit.  With TQ4_NO_FUSED_WRITE=1 (the write kernel runs first) everything is bit-identical."""
+    from tests.helpers import index_mismatch
+
     pr = Prims(d, kbits, vbits)
     p = pr.cuda()
     seq_lens = [70, 33, 129, 1, 16]
@@ -324,21 +331,72 @@ def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, v
     common = dict(block_table=bt.cuda(), seq_lens=case["seq_lens"].cuda(), k_centroids=p["kc"],
                   v_centroids=p["vc"], rotation=p["rot"], num_kv_heads=hkv, block_size=bs,
                   out_dtype=torch.float32)
-    cache_a, cache_b = case["cache"].cuda(), case["cache"].cuda()
+    wargs = (k_new, v_new, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"])
+    cache_a = case["cache"].cuda()
     ops.tq4_write_paged(k_new, v_new, cache_a, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"])
     out_a = _run(ops, mode, q=q, kv_cache=cache_a, **common)
-    out_b = _run(ops, mode, q=q, kv_cache=cache_b, **common,
-                 write=(k_new, v_new, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"]))
-    torch.cuda.synchronize()
-    assert torch.equal(cache_a, cache_b)
-    assert torch.equal(out_a, out_b)
     assert not torch.equal(cache_a.cpu(), case["cache"])  # the write did change the cache
-    # and both agree with the oracle applied to the oracle-written cache
-    ref_cache = case["cache"].clone()
-    keep = slots >= 0
-    O.write_paged(k_new.cpu()[keep], v_new.cpu()[keep], ref_cache, slots[keep], pr.rot, pr.kb, pr.vb)
-    ref = O.paged_decode_fp32(q.cpu(), ref_cache, bt, seq_lens, pr.kc, pr.vc, pr.rot, hkv)
-    _check(out_b, ref)
+    ops.read_and_clear_errors(q.device)
+    for no_fused_write in (False, True):
+        if no_fused_write:
+            monkeypatch.setenv("TQ4_NO_FUSED_WRITE", "1")
+        cache_b = case["cache"].cuda()
+        out_b = _run(ops, mode, q=q, kv_cache=cache_b, **common, write=wargs)
+        torch.cuda.synchronize()
+        assert ops.read_and_clear_errors(q.device) == 0
+        lay = O.row_layout(hkv, d)
+        flat_a, flat_b = cache_a.cpu().view(-1, cache_a.shape[-1]), cache_b.cpu().view(-1, cache_b.shape[-1])
+        assert torch.equal(flat_a[:, lay[0]:lay[1]], flat_b[:, lay[0]:lay[1]])  # K norms, every row
+        assert torch.equal(flat_a[:, lay[2]:lay[3]], flat_b[:, lay[2]:lay[3]])  # V norms
+        assert torch.equal(flat_a[:, lay[3]:], flat_b[:, lay[3]:])              # padding untouched
+        rows = slots[slots >= 0]
+        for lo, hi in ((0, lay[0]), (lay[1], lay[2])):
+            a_idx = flat_a[rows, lo:hi].reshape(len(rows), hkv, d // 2)
+            b_idx = flat_b[rows, lo:hi].reshape(len(rows), hkv, d // 2)
+            if no_fused_write:
+                assert torch.equal(a_idx, b_idx)
+            else:
+                assert index_mismatch(a_idx, b_idx) <= 1e-4
+        others = torch.ones(flat_a.shape[0], dtype=torch.bool)
+        others[rows] = False
+        assert torch.equal(flat_a[others], flat_b[others])  # no other row was touched
+        if torch.equal(cache_a, cache_b):
+            assert torch.equal(out_a, out_b)
+        # and the step agrees with the oracle applied to the oracle-written cache
+        ref_cache = case["cache"].clone()
+        keep = slots >= 0
+        O.write_paged(k_new.cpu()[keep], v_new.cpu()[keep], ref_cache, slots[keep], pr.rot, pr.kb, pr.vb)
+        ref = O.paged_decode_fp32(q.cpu(), ref_cache, bt, seq_lens, pr.kc, pr.vc, pr.rot, hkv)
+        _check(out_b, ref)
+
+
+def test_fused_step_flags_a_slot_that_is_not_the_last_position(ops):
+    """The one-call decode step orders the write of token i before the read of sequence i's last
+    tile only; a slot elsewhere is still written, and reported through TQ4_DEV_WRITE_ORDER."""
+    from tests.helpers import index_mismatch
+    from turboquant_vllm import _native as nv
+
+    pr = Prims(128)
+    p = pr.cuda()
+    seq_lens, hkv, hq, bs = [70, 33], 8, 32, 16
+    case = build_paged_case(seq_lens, hkv, 128, bs, pr, seed=4, padded=True)
+    bt = case["block_table"]
+    slots = torch.tensor([int(bt[0, 0]) * bs + 3, int(bt[1, 2]) * bs + 0])  # position 3, position 32 = last
+    k_new, v_new = (x.cuda() for x in O.synthetic_kv(2, hkv, 128, seed=6, dtype=torch.bfloat16))
+    q = torch.randn(2, hq, 128, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
+    cache = case["cache"].cuda()
+    ops.read_and_clear_errors(q.device)
+    ops.paged_tq4_attention(q, cache, bt.cuda(), case["seq_lens"].cuda(), p["kc"], p["vc"], p["rot"], hkv, bs,
+                            write=(k_new, v_new, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"]))
+    torch.cuda.synchronize()
+    assert ops.read_and_clear_errors(q.device) == nv.DEV_WRITE_ORDER
+    want = case["cache"].cuda()  # what the write kernel leaves at those slots
+    ops.tq4_write_paged(k_new, v_new, want, slots.cuda(), p["even"], p["odd"], p["kb"], p["vb"])
+    lay = O.row_layout(hkv, 128)
+    got = cache.cpu().view(-1, cache.shape[-1])[slots]
+    ref = want.cpu().view(-1, want.shape[-1])[slots]
+    assert torch.equal(got[:, lay[0]:lay[1]], ref[:, lay[0]:lay[1]])  # norms: bit-identical
+    assert index_mismatch(got[:, :lay[0]].reshape(2, hkv, 64), ref[:, :lay[0]].reshape(2, hkv, 64)) <= 1e-4
 
 
 def test_prefill_more_rows_than_one_launch(ops):

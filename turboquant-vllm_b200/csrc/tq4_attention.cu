@@ -2,6 +2,8 @@
 // the split merge + un-rotation kernel, and the C entry points.
 #include <math_constants.h>
 
+#include <cstdlib>
+
 #include "tq4_attention.cuh"
 
 namespace tq4 {
@@ -1143,14 +1145,30 @@ static int attention_impl(
   a.sh.span_ctas = use_mma ? ctas * a.sh.TPC : ctas;
   a.sh.part_tpc = part_tpc;
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool no_fused = getenv("TQ4_NO_FUSED_PROLOGUE") != nullptr;
+  a.fused = use_mma && !use_prefill && query_start_loc == nullptr && num_rows <= kFusedMaxRows &&
+            head_dim <= 128 && !no_fused;
 
   for (int64_t r0 = 0; r0 < num_rows; r0 += kMaxRowsPerLaunch) {
     a.sh.rows = (int)((num_rows - r0) < kMaxRowsPerLaunch ? (num_rows - r0) : kMaxRowsPerLaunch);
     a.sh.row_offset = (int)r0;
-    prof_begin(TQ4_PROF_PROLOGUE, st);
-    int rc = launch_prologue(&a, r0 == 0 ? wr : nullptr, head_dim, st);
-    prof_end(TQ4_PROF_PROLOGUE, st);
-    if (rc != TQ4_OK) return rc;
+    int rc;
+    if (a.fused) {  // no prologue kernel; a decode step's cache write rides in the attention kernel
+      a.fused_write = nullptr;
+      if (wr && a.sh.NCH == 1 && wr->n_tokens <= num_rows && getenv("TQ4_NO_FUSED_WRITE") == nullptr) {
+        a.fused_write = wr;
+      } else if (wr) {
+        prof_begin(TQ4_PROF_WRITE, st);
+        rc = dispatch_compress(*wr, head_dim, wr->x_dtype, st);
+        prof_end(TQ4_PROF_WRITE, st);
+        if (rc != TQ4_OK) return rc;
+      }
+    } else {
+      prof_begin(TQ4_PROF_PROLOGUE, st);
+      rc = launch_prologue(&a, r0 == 0 ? wr : nullptr, head_dim, st);
+      prof_end(TQ4_PROF_PROLOGUE, st);
+      if (rc != TQ4_OK) return rc;
+    }
     prof_begin(TQ4_PROF_ATTENTION, st);
     rc = use_prefill ? launch_prefill_tc(a, st)
                      : (use_mma ? launch_attention_mma(a, st) : launch_attention_fp32(a, st));

@@ -24,6 +24,7 @@ constexpr int kMmaWarpsPerCta = 16;    // tensor-core LUT kernel (one CTA per SM
 constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace sizing (fp32 kernel)
 constexpr int kMaxSms = 160;               // tensor-core kernel: one CTA per SM, one span per warp phase
 constexpr int kMaxRowsPerLaunch = 4096;    // larger query batches are processed in pieces
+constexpr int kFusedMaxRows = 512;         // decode calls up to this size plan and rotate inside the attention kernel
 
 struct AttnPlan {
   float* q_rot;      // [rows][Hq][D] fp32, q * Pi^T
@@ -79,6 +80,8 @@ struct AttnArgs {
   float* lse_out;
   int out_rotated;
   int* err_flag;
+  int fused;  // tensor-core kernel: compute the tile plan and rotate the queries inside the kernel
+  const CompressArgs* fused_write;  // host side only: the step's cache write, done inside the fused kernel
 };
 
 inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }

@@ -220,5 +220,8 @@ int dispatch_compress(const CompressArgs& a, int head_dim, int dtype, cudaStream
 // tensor-core (tcgen05) compress kernel for large inputs at head_dim 128 (tq4_compress_tc.cu)
 bool compress_tc_eligible(const CompressArgs& a, int head_dim, int dtype);
 int launch_compress_tc(const CompressArgs& a, int dtype, cudaStream_t st);
+// pipelined tcgen05 kernel for dense 16-bit inputs at head_dim 128 (tq4_compress_tc16.cu)
+bool compress_tc16_eligible(const CompressArgs& a, int head_dim, int dtype);
+int launch_compress_tc16(const CompressArgs& a, int dtype, cudaStream_t st);
 
 }  // namespace tq4

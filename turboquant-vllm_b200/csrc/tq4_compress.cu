@@ -352,8 +352,10 @@ int dispatch_dtype(const CompressArgs& a, int dtype, cudaStream_t st) {
 }
 
 int dispatch_compress(const CompressArgs& a, int head_dim, int dtype, cudaStream_t st) {
-  if (a.n_tokens * a.num_heads * a.n_sources > kSmallRows && compress_tc_eligible(a, head_dim, dtype))
-    return launch_compress_tc(a, dtype, st);
+  if (a.n_tokens * a.num_heads * a.n_sources > kSmallRows) {
+    if (compress_tc16_eligible(a, head_dim, dtype)) return launch_compress_tc16(a, dtype, st);
+    if (compress_tc_eligible(a, head_dim, dtype)) return launch_compress_tc(a, dtype, st);
+  }
   switch (head_dim) {
     case 64: return dispatch_dtype<64>(a, dtype, st);
     case 96: return dispatch_dtype<96>(a, dtype, st);

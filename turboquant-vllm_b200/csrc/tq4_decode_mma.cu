@@ -41,6 +41,22 @@ namespace tq4 {
 namespace {
 
 constexpr uint32_t kTableBytes = 65536;
+
+// Timeline aid for tuning builds (-DTQ4_TRACE): lane 0 of every warp stamps %globaltimer at a few
+// points into a buffer read back with tq4_trace_read.  Compiled out of the shipped library.
+#ifdef TQ4_TRACE
+__device__ long long g_trace[160 * 16 * 8];
+#define TQ4_STAMP(i)                                                                             \
+  do {                                                                                           \
+    if ((threadIdx.x & 31) == 0) {                                                               \
+      long long t__;                                                                             \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                    \
+      g_trace[((blockIdx.x % 160) * 16 + (threadIdx.x >> 5)) * 8 + (i)] = t__;                   \
+    }                                                                                            \
+  } while (0)
+#else
+#define TQ4_STAMP(i) do {} while (0)
+#endif
 constexpr int kStages = 2;  // ring stages per warp, one PAIR of 16-token tiles each
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -220,6 +236,370 @@ struct MmaCfg {
   template <bool VWIDE> __host__ __device__ static constexpr int tma_stage() { return tma_kn<VWIDE>() + 512; }
 };
 
+
+// =====================================================================================================
+// Fused prologue (decode calls of at most kFusedMaxRows rows, head_dim <= 128): the attention kernel
+// itself computes the tile plan and rotates the queries, so a decode step needs no kernel in front
+// of it and no CTA waits for another.
+//
+//  * Plan: every warp scans the rows of the call (32 per step), sums their tile counts, derives the
+//    tiles per span and writes the plan arrays of the chunks it owns; all CTAs write the same
+//    values, each reads back only what it wrote itself (after a block barrier).
+//  * Rotation: a CTA rotates exactly the query rows its own spans touch (all heads of its slice):
+//    q_rot = q * Pi^T on mma.sync.m16n8k16 with both operands split into fp16 hi + lo terms
+//    (hi*hi + hi*lo + lo*hi, fp32 accumulate: about 2^-21 relative).  Pi (times 2^8, so that the lo
+//    terms stay normal numbers) sits in shared memory as two fp16 arrays in the 64 KB region that
+//    afterwards holds the dequantisation table; each query vector is scaled by a power of two
+//    into [1, 2) before its split.  Neighbouring CTAs that share a row compute the same values and
+//    store the same bits.
+// =====================================================================================================
+
+template <int D>
+struct RotCfg {
+  static constexpr int KS = D / 16;                      // k-steps
+  static constexpr int NQ = D / 32;                      // tasks along N (4 n-blocks of 8 outputs each)
+  static constexpr int PITCH = 2 * D + (D == 96 ? 32 : 0);  // bytes per row of a Pi half (fp16)
+  static constexpr bool XOR = D != 96;                   // 8-byte chunks XOR-swizzled by 4 * (row & 3)
+  static constexpr int LO_BASE = D * PITCH;              // the lo array follows the hi array
+  static_assert(2 * D * PITCH <= (int)kTableBytes, "both fp16 halves of Pi fit the table region");
+};
+
+template <int D>
+__device__ __forceinline__ uint32_t rot_chunk_off(int n, int kc) {  // byte offset of 8-byte chunk kc of row n
+  using R = RotCfg<D>;
+  return (uint32_t)(n * R::PITCH + ((R::XOR ? (kc ^ (4 * (n & 3))) : kc) << 3));
+}
+
+// fp16 hi / lo split of four floats -> (hi01, hi23, lo01, lo23)
+__device__ __forceinline__ void split4(const float (&x)[4], uint32_t& h01, uint32_t& h23, uint32_t& l01,
+                                       uint32_t& l23) {
+  float h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    h[i] = __half2float(__float2half_rn(x[i]));
+    l[i] = x[i] - h[i];
+  }
+  h01 = pack_h2(h[0], h[1]); h23 = pack_h2(h[2], h[3]);
+  l01 = pack_h2(l[0], l[1]); l23 = pack_h2(l[2], l[3]);
+}
+
+// Stage Pi * 2^8 as fp16 hi / lo arrays at shared address `tab` (all threads of the block).
+template <int D>
+__device__ __forceinline__ void stage_rotation_split(const float* __restrict__ rotation, uint32_t tab) {
+  constexpr int N4 = D * D / 4;
+  for (int i0 = threadIdx.x; i0 < N4; i0 += 4 * blockDim.x) {
+    float4 x[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < N4) x[u] = __ldg(reinterpret_cast<const float4*>(rotation) + i);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < N4) {
+        const int n = i / (D / 4), kc = i - n * (D / 4);
+        const float v[4] = {x[u].x * 256.f, x[u].y * 256.f, x[u].z * 256.f, x[u].w * 256.f};
+        uint32_t h01, h23, l01, l23;
+        split4(v, h01, h23, l01, l23);
+        const uint32_t off = tab + rot_chunk_off<D>(n, kc);
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off), "r"(h01), "r"(h23) : "memory");
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off + RotCfg<D>::LO_BASE), "r"(l01), "r"(l23) : "memory");
+      }
+    }
+  }
+}
+
+// Visible key range of decode row r (the single query of sequence r + row_offset).
+__device__ __forceinline__ void decode_row_range(const AttnArgs& a, int r, int& seq, int& start, int& end) {
+  const int gr = r + a.sh.row_offset;
+  seq = 0; start = 0; end = 0;
+  if (gr < a.sh.num_seqs) {
+    seq = gr;
+    const int len = max(0, __ldg(a.seq_lens + gr));
+    end = len;
+    start = a.sliding_window > 0 ? max(0, len - a.sliding_window) : 0;
+  }
+}
+
+__device__ __forceinline__ int warp_incl_scan(int v, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += up;
+  }
+  return v;
+}
+
+// The plan of a decode call, computed by one warp.  Writes the plan entries of the 32-row chunks
+// with chunk % n_warps == warp (and, warp 0, the totals); returns the rows [r_a, r_b] that hold the
+// first and the last tile of the tile range [T_a, T_b) given as multiples of tiles per span
+// (r_a = -1 if the range is empty).
+__device__ __forceinline__ void fused_plan(const AttnArgs& a, int warp, int n_warps, int lane,
+                                           int span_first, int span_count, int& r_a, int& r_b,
+                                           int& t_a, int& t_b) {
+  const AttnShape& sh = a.sh;
+  const AttnPlan& p = a.plan;
+  const int rows = sh.rows, n_chunks = (rows + 31) >> 5;
+  int local = 0;
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int r = ch * 32 + lane;
+    if (r < rows) {
+      int seq, start, end;
+      decode_row_range(a, r, seq, start, end);
+      local += end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  const int total = local;
+  const int tps = max(1, (total + sh.span_ctas - 1) / sh.span_ctas);
+  const long long T_a = (long long)span_first * tps;
+  const long long T_b = min((long long)total, T_a + (long long)span_count * tps);
+  r_a = -1;
+  r_b = -1;
+  t_a = (int)min(T_a, (long long)total);
+  t_b = (int)T_b;
+  int run_t = 0, run_s = 0;
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int r = ch * 32 + lane;
+    int seq = 0, start = 0, end = 0, nt = 0;
+    if (r < rows) {
+      decode_row_range(a, r, seq, start, end);
+      nt = end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
+    }
+    const int incl_t = warp_incl_scan(nt, lane);
+    const int b = run_t + incl_t - nt, e = b + nt;
+    const int ns = nt > 0 ? (e - 1) / tps - b / tps + 1 : 0;
+    const int incl_s = warp_incl_scan(ns, lane);
+    if (ch % n_warps == warp && r < rows) {
+      p.kv_start[r] = start;
+      p.kv_end[r] = end;
+      p.row_seq[r] = seq;
+      p.tile_prefix[r] = b;
+      p.slot_base[r] = run_s + incl_s - ns;
+    }
+    if (T_a < T_b) {
+      const unsigned ma = __ballot_sync(0xffffffffu, nt > 0 && b <= T_a && T_a < e);
+      const unsigned mb = __ballot_sync(0xffffffffu, nt > 0 && b <= T_b - 1 && T_b - 1 < e);
+      if (ma) r_a = ch * 32 + __ffs(ma) - 1;
+      if (mb) r_b = ch * 32 + __ffs(mb) - 1;
+    }
+    run_t += __shfl_sync(0xffffffffu, incl_t, 31);
+    run_s += __shfl_sync(0xffffffffu, incl_s, 31);
+  }
+  if (warp == 0 && lane == 0) {
+    p.tile_prefix[rows] = total;
+    p.slot_base[rows] = run_s;
+    p.scalars[0] = total;
+    p.scalars[1] = tps;
+  }
+}
+
+// Four consecutive elements e0 .. e0 + 3 of a query vector as floats.
+__device__ __forceinline__ void load_q4(const void* q, int dtype, int64_t idx, bool vec_ok, float (&x)[4]) {
+  if (vec_ok) {
+    if (dtype == TQ4_F32) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q) + idx));
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    } else {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(q) + idx));
+      if (dtype == TQ4_F16) {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        x[0] = f0.x; x[1] = f0.y; x[2] = f1.x; x[3] = f1.y;
+      } else {
+        x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xFFFF0000u);
+        x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xFFFF0000u);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = load_as_float(q, dtype, idx + i);
+  }
+}
+
+// Rotation work of a CTA, on mma.sync (see the header of this section):
+//  * q_rot rows [r_a, r_b] x heads [h0, h0 + nh) = q * Pi^T;
+//  * with `w` (a decode step's cache write): for every row of [r_a, r_b] whose LAST tile lies in the
+//    CTA's tile range [t_a, t_b), the K and V vectors of that row's new token for the KV heads
+//    [kvh0, kvh0 + nkv): norm (summed in the order of the compress kernels, so the stored norms are
+//    bit-identical to theirs), x / (norm + 1e-10), rotation, bucketize, nibble pack, stored at the
+//    token's slot.  The CTA that reads a row's last tile is the one that writes it, so a block
+//    barrier (plus the generic -> async proxy fence) orders the write before the read.
+// Work is cut into tasks of 16 vectors x 32 outputs, handed out to the warps round robin.  Lane
+// (g, c) of a warp owns, per k-step s, the four contiguous elements 16 s + 4 c .. + 3 of vectors g
+// and g + 8 (the k order inside a step is a permutation applied to both operands, which leaves the
+// sum unchanged).  s_bounds: [2][16] sorted boundaries of K and V padded with +inf.
+template <int D>
+__device__ __forceinline__ void fused_rotate(const AttnArgs& a, const CompressArgs* w, const float* s_bounds,
+                                             uint32_t tab, int warp, int n_warps, int lane, int r_a, int r_b,
+                                             int t_a, int t_b, int h0, int nh, int kvh0, int nkv) {
+  using R = RotCfg<D>;
+  const AttnShape& sh = a.sh;
+  const AttnPlan& p = a.plan;
+  const int g = lane >> 2, c = lane & 3;
+  const int n_rows = r_b - r_a + 1;
+  const int n_q = n_rows * nh;
+  const int n_w = w ? n_rows * 2 * nkv : 0;
+  const int n_vec = n_q + n_w;
+  const int n_tasks = ((n_vec + 15) >> 4) * R::NQ;
+  const int qes = a.q_dtype == TQ4_F32 ? 4 : 2;
+  const bool q_vec_ok = ((uintptr_t)a.q % 16 == 0) && (a.q_token_stride * qes) % 16 == 0 &&
+                        (a.q_head_stride * qes) % 16 == 0;
+  const RowLayout lay = row_layout(sh.Hkv, D);
+  for (int task = warp; task < n_tasks; task += n_warps) {
+    const int grp = task / R::NQ, nq = task - grp * R::NQ;
+    uint32_t ah[R::KS][4], al[R::KS][4];  // A fragments (a0..a3) of the hi and lo terms
+    float inv_scale[2], nrm[2];
+    int64_t q_out[2];         // q rows: offset into q_rot, else -1
+    uint8_t* w_idx[2];        // write rows: the head's packed index bytes in the cache row, else nullptr
+    float* w_norm[2];
+    int w_src[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {  // vector g (hf = 0) and vector g + 8 (hf = 1)
+      const int v = grp * 16 + g + 8 * hf;
+      q_out[hf] = -1;
+      w_idx[hf] = nullptr;
+      w_norm[hf] = nullptr;
+      w_src[hf] = 0;
+      const void* src_ptr = nullptr;
+      int src_dtype = a.q_dtype;
+      int64_t base = 0;
+      bool vec_ok = q_vec_ok;
+      if (v < n_q) {
+        const int ri = v / nh, h = h0 + (v - ri * nh);
+        const int r = r_a + ri;
+        q_out[hf] = ((int64_t)r * sh.Hq + h) * D;
+        src_ptr = a.q;
+        base = ((int64_t)r + sh.row_offset) * a.q_token_stride + (int64_t)h * a.q_head_stride + 4 * c;
+      } else if (v < n_vec) {
+        const int wi = v - n_q;
+        const int ri = wi / (2 * nkv), rem = wi - ri * (2 * nkv);
+        const int src = rem / nkv, kvh = kvh0 + (rem - src * nkv);
+        const int r = r_a + ri;
+        const int tok = r + sh.row_offset;
+        const int kv_start = p.kv_start[r], kv_end = p.kv_end[r];
+        const int nt = kv_end > kv_start ? (kv_end + kTileTokens - 1) / kTileTokens - kv_start / kTileTokens : 0;
+        const int last_tile = p.tile_prefix[r] + nt - 1;
+        if (nt > 0 && last_tile >= t_a && last_tile < t_b && tok < w->n_tokens && tok < w->n_slots) {
+          const int64_t slot = w->slot_mapping[tok];
+          if (slot >= w->num_cache_slots) {
+            if (c == 0 && w->err_flag) atomicOr(w->err_flag, TQ4_DEV_BAD_SLOT);
+          } else if (slot >= 0) {
+            // the write is ordered before this call's reads only if the slot is the row's last position
+            const int pos = kv_end - 1;
+            const int blk = __ldg(a.block_table + (int64_t)p.row_seq[r] * a.bt_stride + pos / a.block_size);
+            if ((int64_t)blk * a.block_size + pos % a.block_size != slot && c == 0 && w->err_flag)
+              atomicOr(w->err_flag, TQ4_DEV_WRITE_ORDER);
+            uint8_t* rowp = w->cache + slot * w->cache_token_stride;
+            w_idx[hf] = rowp + (src == 0 ? lay.k_idx : lay.v_idx) + kvh * (D / 2);
+            w_norm[hf] = reinterpret_cast<float*>(rowp + (src == 0 ? lay.k_norm : lay.v_norm) + kvh * 4);
+            w_src[hf] = src;
+            src_ptr = w->x[src];
+            src_dtype = w->x_dtype;
+            const int es = src_dtype == TQ4_F32 ? 4 : 2;
+            vec_ok = ((uintptr_t)src_ptr % 16 == 0) && (w->token_stride[src] * es) % 16 == 0 &&
+                     (w->head_stride[src] * es) % 16 == 0;
+            base = (int64_t)tok * w->token_stride[src] + (int64_t)kvh * w->head_stride[src] + 4 * c;
+          }
+        }
+      }
+      float x[R::KS][4];
+#pragma unroll
+      for (int s = 0; s < R::KS; ++s) {
+        if (src_ptr) load_q4(src_ptr, src_dtype, base + 16 * s, vec_ok, x[s]);
+        else x[s][0] = x[s][1] = x[s][2] = x[s][3] = 0.f;
+      }
+      // ---- squared norm in the order of the compress kernels: element k belongs to partial
+      // l = k mod 32 (an ascending FMA chain over k = l, l + 32, ...), the partials are merged by the
+      // butterfly 16, 8, 4, 2, 1.  This lane holds l = 4 c + e and l + 16 (k-steps 2 i and 2 i + 1).
+      {
+        float pa[4], pb[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          pa[e] = 0.f;
+          pb[e] = 0.f;
+#pragma unroll
+          for (int i = 0; i < R::KS / 2; ++i) {
+            pa[e] = fmaf(x[2 * i][e], x[2 * i][e], pa[e]);
+            pb[e] = fmaf(x[2 * i + 1][e], x[2 * i + 1][e], pb[e]);
+          }
+          pa[e] = pa[e] + pb[e];                                       // l ^ 16
+          pa[e] = pa[e] + __shfl_xor_sync(0xffffffffu, pa[e], 2);      // l ^ 8  (lane c ^ 2)
+          pa[e] = pa[e] + __shfl_xor_sync(0xffffffffu, pa[e], 1);      // l ^ 4  (lane c ^ 1)
+        }
+        const float d0 = pa[0] + pa[2], d1 = pa[1] + pa[3];            // l ^ 2
+        nrm[hf] = sqrtf(d0 + d1);                                       // l ^ 1
+      }
+      float amax = 0.f;
+      if (w_idx[hf]) {
+        const float den = nrm[hf] + 1e-10f;
+#pragma unroll
+        for (int s = 0; s < R::KS; ++s)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[s][i] = x[s][i] / den;
+      }
+#pragma unroll
+      for (int s = 0; s < R::KS; ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(x[s][i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      // power of two that brings the largest element into [1, 2); exact in both directions
+      float sc = 1.f, isc = 1.f;
+      if (amax > 0.f && amax < CUDART_INF_F) {
+        const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
+        const int exc = min(max(ex, -100), 100);
+        sc = __uint_as_float((uint32_t)(127 - exc) << 23);
+        isc = __uint_as_float((uint32_t)(127 + exc) << 23);
+      }
+      inv_scale[hf] = isc * (1.f / 256.f);
+#pragma unroll
+      for (int s = 0; s < R::KS; ++s) {
+        const float y[4] = {x[s][0] * sc, x[s][1] * sc, x[s][2] * sc, x[s][3] * sc};
+        uint32_t h01, h23, l01, l23;
+        split4(y, h01, h23, l01, l23);
+        // a0 / a1 = (row g / g + 8, first k pair), a2 / a3 = (row g / g + 8, second k pair)
+        ah[s][hf] = h01; ah[s][2 + hf] = h23;
+        al[s][hf] = l01; al[s][2 + hf] = l23;
+      }
+    }
+    const bool any_row = q_out[0] >= 0 || q_out[1] >= 0 || w_idx[0] != nullptr || w_idx[1] != nullptr;
+    if (!__any_sync(0xffffffffu, any_row)) continue;  // e.g. a group of write rows that end elsewhere
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+      const int n = (nq * 4 + nb) * 8 + g;  // this lane's B column (output coordinate)
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < R::KS; ++s) {
+        const uint32_t off = tab + rot_chunk_off<D>(n, 4 * s + c);
+        uint32_t bh[2], bl[2];
+        lds_words<8>(off, bh);
+        lds_words<8>(off + R::LO_BASE, bl);
+        mma16816(acc, al[s][0], al[s][1], al[s][2], al[s][3], bh[0], bh[1]);
+        mma16816(acc, ah[s][0], ah[s][1], ah[s][2], ah[s][3], bl[0], bl[1]);
+        mma16816(acc, ah[s][0], ah[s][1], ah[s][2], ah[s][3], bh[0], bh[1]);
+      }
+      const int n0 = (nq * 4 + nb) * 8 + 2 * c;  // C columns of this lane: coordinates n0 (even), n0 + 1
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const float y0 = acc[2 * hf] * inv_scale[hf], y1 = acc[2 * hf + 1] * inv_scale[hf];
+        if (q_out[hf] >= 0) {
+          *reinterpret_cast<float2*>(p.q_rot + q_out[hf] + n0) = make_float2(y0, y1);
+        } else if (w_idx[hf]) {
+          const float* bd = s_bounds + 16 * w_src[hf];
+          w_idx[hf][n0 >> 1] = (uint8_t)((bucketize_sorted16(y0, bd) << 4) | bucketize_sorted16(y1, bd));
+        }
+      }
+    }
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+      if (w_idx[hf] && nq == 0 && c == 0) *w_norm[hf] = nrm[hf];
+  }
+  if (w) asm volatile("fence.proxy.async.global;" ::: "memory");  // the cache rows are read back by bulk tensor copies
+}
+
 // byte offset (within a head's D/2 V bytes) of this thread's m-block i
 template <int D>
 __device__ __forceinline__ int v_byte_of_mblock(int g, int i) {
@@ -233,7 +613,7 @@ __device__ __forceinline__ int v_byte_of_mblock(int g, int i) {
 // with an extra "half" dimension fetches both index tiles, and one both norm tiles.
 template <int D, int NB, bool ALIGNED, bool PAGE16, int WARPS, bool TMA, int BOX>
 __global__ void __launch_bounds__(WARPS * 32, 1)
-attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
+attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write, const uint32_t smem_total,
                      const __grid_constant__ CUtensorMap tm_data,
                      const __grid_constant__ CUtensorMap tm_v,
                      const __grid_constant__ CUtensorMap tm_norm) {
@@ -266,6 +646,37 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
     if (threadIdx.x == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
     return;
   }
+  TQ4_STAMP(0);
+  // ---- fused prologue: tile plan + query rotation for the rows this CTA's spans touch ------------
+  if (a.fused) {
+    if constexpr (D <= 128) {
+      const int n_warps = blockDim.x >> 5;
+      const int cta_f = blockIdx.x % sh.ctas, slice_f = blockIdx.x / sh.ctas;
+      int r_a, r_b, t_a, t_b;
+      fused_plan(a, warp, n_warps, lane, cta_f * sh.TPC, sh.TPC, r_a, r_b, t_a, t_b);
+      TQ4_STAMP(1);
+      stage_rotation_split<D>(a.rotation, tab);
+      if (has_write && threadIdx.x < 32) {  // sorted boundaries of K and V, padded with +inf
+        const int src = threadIdx.x >> 4, i = threadIdx.x & 15;
+        s_cent[src][i] = i < w.n_bounds[src] ? w.bounds[src][i] : CUDART_INF_F;
+      }
+      __syncthreads();
+      TQ4_STAMP(2);
+      if (r_a >= 0 && r_b >= r_a) {
+        const int vh0 = slice_f * sh.HPC, vh1 = vh0 + sh.HPC - 1;
+        const int h0 = (vh0 / sh.NCH) * sh.G + (vh0 % sh.NCH) * sh.GC;
+        const int c1 = vh1 % sh.NCH;
+        const int h1 = (vh1 / sh.NCH) * sh.G + c1 * sh.GC + min(sh.GC, sh.G - c1 * sh.GC);
+        const int kvh0 = vh0 / sh.NCH, kvh1 = vh1 / sh.NCH;
+        // (a KV head shared by two slices, G > 8, is written by the slice that holds its first chunk)
+        const int kv_first = (vh0 % sh.NCH) ? kvh0 + 1 : kvh0;
+        fused_rotate<D>(a, has_write ? &w : nullptr, &s_cent[0][0], tab, warp, n_warps, lane, r_a, r_b, t_a, t_b,
+                        h0, h1 - h0, kv_first, kvh1 - kv_first + 1);
+      }
+    }
+    __syncthreads();  // plan and rotated queries are visible to the block; the table region is free
+    TQ4_STAMP(3);
+  }
   // ---- replicated byte -> half2 tables: slot l < 32 = K table of lane l, slot 32 + l = V -------
   if (threadIdx.x < 2 * TQ4_MAX_CENTROIDS) {
     const int w = threadIdx.x >> 4, i = threadIdx.x & 15;
@@ -294,6 +705,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
   // plan, the rotated queries and the cache, which the preceding kernels produce
   pdl_trigger();
   pdl_wait();
+  TQ4_STAMP(4);
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
   const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
   // Row g of the score MMA / k-slot of the PV MMA does not hold token g of the tile but token
@@ -797,6 +1209,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
             dead = true;
             break;
           }
+          if (gk == 0 && k == 0) TQ4_STAMP(5);
           compute_pair(st, pos_c, ok_cur, pos_c + kTileTokens <= last_pos);
           pos_c += step_tok;
           ok_cur = ok_next;
@@ -892,6 +1305,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       }
     }
 
+    TQ4_STAMP(6);
     // ---- write this warp's partial for the segment ---------------------------------------------
     const int slot = p.slot_base[r] + (span - row_t0 / tps);
     const int64_t pidx = slot;
@@ -924,6 +1338,7 @@ attention_mma_kernel(const AttnArgs a, const uint32_t smem_total,
       while (p.tile_prefix[r + 1] <= t) ++r;
     }
   }
+  TQ4_STAMP(7);
 }
 
 // ---- TMA tensor maps over the paged cache: dims (row bytes, tokens in a block, blocks) -----------
@@ -1013,7 +1428,10 @@ int launch_mma_t(const AttnArgs& a, cudaStream_t st) {
     return TQ4_ERR_CUDA;
   }
   const int warps = a.sh.HPC * a.sh.TPC;
-  if (launch_kernel(kern, dim3(a.sh.ctas * a.sh.n_slices), dim3(warps * 32), (size_t)smem_total, st, true, a,
+  static const CompressArgs no_write{};
+  // with the fused prologue this is the first kernel to read the caller's tensors: a plain launch
+  if (launch_kernel(kern, dim3(a.sh.ctas * a.sh.n_slices), dim3(warps * 32), (size_t)smem_total, st, !a.fused, a,
+                    a.fused && a.fused_write ? *a.fused_write : no_write, a.fused && a.fused_write ? 1 : 0,
                     (uint32_t)smem_total, tm_data, tm_v, tm_norm) != cudaSuccess)
     return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
@@ -1102,6 +1520,15 @@ bool attention_mma_supported(const AttnShape& sh, int block_size, const uint8_t*
   (void)block_size; (void)cache; (void)block_stride;
   return supported_head_dim(sh.D) && sh.GC <= 8 && token_stride % 4 == 0;
 }
+
+#ifdef TQ4_TRACE
+}  // namespace tq4
+// Copies the 160 x 16 x 8 timeline stamps of the last launch to the host (tuning builds only).
+extern "C" int tq4_trace_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, tq4::g_trace, sizeof(long long) * 160 * 16 * 8) == cudaSuccess ? 0 : 1;
+}
+namespace tq4 {
+#endif
 
 int launch_attention_mma(const AttnArgs& a, cudaStream_t st) {
   switch (a.sh.D) {

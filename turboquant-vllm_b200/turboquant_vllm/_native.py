@@ -19,7 +19,7 @@ _lib = None
 F32, F16, BF16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
-DEV_BAD_SLOT, DEV_BAD_BLOCK, DEV_TIMEOUT = 1, 2, 4
+DEV_BAD_SLOT, DEV_BAD_BLOCK, DEV_TIMEOUT, DEV_WRITE_ORDER = 1, 2, 4, 8
 STATIC_SCRATCH_BYTES = 32 << 20
 
 # name -> (restype, argtypes); must list every symbol of include/tq4.h
@@ -161,13 +161,15 @@ def call(device: torch.device, name: str, *args):
 _DEV_BITS = ((DEV_BAD_SLOT, "slot_mapping entry outside the cache (TQ4_DEV_BAD_SLOT)"),
              (DEV_BAD_BLOCK, "block_table entry outside [0, num_blocks) or sequence longer than its "
                              "block-table row (TQ4_DEV_BAD_BLOCK)"),
-             (DEV_TIMEOUT, "a bounded device-side wait gave up (TQ4_DEV_TIMEOUT)"))
+             (DEV_TIMEOUT, "a bounded device-side wait gave up (TQ4_DEV_TIMEOUT)"),
+             (DEV_WRITE_ORDER, "a fused decode step wrote a token to a slot that is not the last position of "
+                               "its sequence (TQ4_DEV_WRITE_ORDER)"))
 
 
 def describe_device_errors(flag: int) -> str:
     """Text for the TQ4_DEV_* bits a kernel OR-ed into the device error flag."""
     parts = [text for bit, text in _DEV_BITS if flag & bit]
-    rest = flag & ~(DEV_BAD_SLOT | DEV_BAD_BLOCK | DEV_TIMEOUT)
+    rest = flag & ~(DEV_BAD_SLOT | DEV_BAD_BLOCK | DEV_TIMEOUT | DEV_WRITE_ORDER)
     if rest:
         parts.append(f"unknown bits {rest:#x}")
     return "; ".join(parts) if parts else "no error"
