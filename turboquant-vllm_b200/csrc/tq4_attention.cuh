@@ -132,7 +132,7 @@ int launch_attention_mma(const AttnArgs& a, cudaStream_t st);  // returns TQ4_ER
 // tensor-core (tcgen05) chunked-prefill kernel (tq4_prefill_tc.cu): writes one dense partial per row
 // (normalised rotated output in plan.part_o [rows][Hq][D], natural-log LSE in plan.part_m [rows][Hq])
 bool prefill_tc_supported(const AttnArgs& a);
-int launch_prefill_tc(const AttnArgs& a, cudaStream_t st);
+int launch_prefill_tc(const AttnArgs& a, cudaStream_t st, bool fast);
 int mma_warps_per_cta(int D, int GC, int Hkv, int64_t token_stride = 0);
 bool attention_mma_supported(const AttnShape& sh, int block_size, const uint8_t* cache,
                              int64_t block_stride, int64_t token_stride);

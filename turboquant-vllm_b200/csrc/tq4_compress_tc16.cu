@@ -43,7 +43,9 @@ constexpr uint32_t kTileBytes = 2 * kBlockBytes; // a tile = two K-blocks
 constexpr int kMaxTerms = 3;
 constexpr uint32_t kOffB = 0;                                  // terms x 2 K-blocks of Pi
 constexpr uint32_t kOffA = kMaxTerms * kTileBytes;             // stages x 2 K-blocks of X
-constexpr uint32_t kSmemBytes = kOffA + kStages * kTileBytes;  // 192 KB
+constexpr int kCells = 256, kCellCopies = 4;                   // bucketize table, see CellTable
+constexpr uint32_t kOffCells = kOffA + kStages * kTileBytes;
+constexpr uint32_t kSmemBytes = kOffCells + 2 * kCellCopies * kCells * 8;  // 192 KB + 16 KB
 constexpr uint32_t kTmemCols = 256;                            // two accumulators of 128 fp32 columns
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -159,11 +161,68 @@ __device__ __forceinline__ void chunk_to_float(const uint4& v, float (&x)[8]) {
   }
 }
 
+// idx = #{b : b < y} over 15 ascending boundaries (padded with +inf) held in REGISTERS: a four-level
+// binary search whose next boundary is picked with selects, so nothing in it touches memory (the
+// shared-memory version is a chain of four dependent loads per coordinate, which two epilogue
+// warps per scheduler cannot hide).  NaN compares false at every level -> 0.
+__device__ __forceinline__ int bucketize_reg(float y, const float (&b)[15]) {
+  const bool c1 = y > b[7];
+  const bool c2 = y > (c1 ? b[11] : b[3]);
+  const float t3 = c2 ? (c1 ? b[13] : b[5]) : (c1 ? b[9] : b[1]);
+  const bool c3 = y > t3;
+  const float lo4 = c2 ? (c1 ? b[12] : b[4]) : (c1 ? b[8] : b[0]);
+  const float hi4 = c2 ? (c1 ? b[14] : b[6]) : (c1 ? b[10] : b[2]);
+  const bool c4 = y > (c3 ? hi4 : lo4);
+  return (c1 ? 8 : 0) + (c2 ? 4 : 0) + (c3 ? 2 : 0) + (c4 ? 1 : 0);
+}
+
+// Bucketize by table.  The real line is cut into kCells uniform cells between the lowest and the
+// highest boundary; cell(y) = clamp(floor(y * scale + off)) is monotone in y, so every boundary in
+// a lower cell is below y and every boundary in a higher cell above it, and only a boundary in
+// y's own cell needs a comparison:  idx = base[cell] + (y > inner[cell]).  That is exact, costs one
+// 8-byte shared-memory load and six ALU instructions per coordinate (the register search: 19), and
+// needs cells finer than the closest pair of boundaries, which the builder checks (a codebook that
+// fails the check keeps the register search).  kCellCopies copies, one per lane & 3, thin out bank
+// conflicts.  Built in the kernel with the arithmetic the lookups use.
+struct CellParams {
+  float scale, off;
+  int ok;
+};
+__device__ __forceinline__ int cell_of(float y, float scale, float off) {
+  return min(max(__float2int_rd(fmaf(y, scale, off)), 0), kCells - 1);
+}
+// one warp builds the table of one source: float2 {inner boundary or +inf, base count (int bits)}
+__device__ __forceinline__ void build_cells(const float* b16, int nb, float2* tab, CellParams* prm, int lane) {
+  const float lo = nb > 0 ? b16[0] : 0.f, hi = nb > 0 ? b16[nb - 1] : 0.f;
+  const float scale = hi > lo ? (float)(kCells - 2) / (hi - lo) : 1.f;
+  const float off = 1.f - lo * scale;
+  bool ok = true;
+  for (int q = lane; q < kCells; q += 32) {
+    int base = 0, inside = 0;
+    float inner = CUDART_INF_F;
+    for (int i = 0; i < nb; ++i) {
+      const int cb = cell_of(b16[i], scale, off);
+      base += cb < q ? 1 : 0;
+      if (cb == q) { ++inside; inner = b16[i]; }
+    }
+    ok = ok && inside <= 1;
+#pragma unroll
+    for (int cpy = 0; cpy < kCellCopies; ++cpy) tab[cpy * kCells + q] = make_float2(inner, __int_as_float(base));
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0) {
+    prm->scale = scale;
+    prm->off = off;
+    prm->ok = ok ? 1 : 0;
+  }
+}
+
 struct Bars {
   uint64_t full[kStages];    // TMA -> consumers: the stage's tile has landed
   uint64_t empty[kStages];   // consumers -> TMA: MMAs (1 commit) and the norm readers (4 warps) are done with it
   uint64_t tfull[kAccs];     // MMA -> epilogue: the accumulator holds the tile's product
   uint64_t tempty[kAccs];    // epilogue (4 warps) -> MMA: the accumulator has been read
+  uint64_t pi;               // the raw rotation matrix has landed in the staging area
 };
 
 template <typename T>
@@ -176,6 +235,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
   __shared__ uint32_t s_tmem;
   __shared__ int s_dead;
   __shared__ float s_bounds[2][16];
+  __shared__ CellParams s_cells[2];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   unsigned char* sm = smem_raw + (base - smem_addr(smem_raw));
@@ -194,8 +254,17 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       bar_init(smem_addr(&s_bars.tfull[c]), 1);
       bar_init(smem_addr(&s_bars.tempty[c]), 4);
     }
+    bar_init(smem_addr(&s_bars.pi), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     s_dead = 0;
+    // the caller's Pi^T halves (2 x 32 KB fp32) by two bulk copies into the still unused input stages
+    const uint32_t bar = smem_addr(&s_bars.pi);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * kD * (kD / 2) * 4u) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(base + kOffA), "l"(a.rot_even), "r"((uint32_t)(kD * (kD / 2) * 4)), "r"(bar) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(base + kOffA + (uint32_t)(kD * (kD / 2) * 4)), "l"(a.rot_odd), "r"((uint32_t)(kD * (kD / 2) * 4)), "r"(bar) : "memory");
   }
   if (warp == 1) {  // the issuing warp owns the tensor-memory allocation
     __syncwarp();
@@ -204,15 +273,20 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // ---- Pi as the B operand: B[n = j][k = d] = Pi[j][d] in 16-bit terms, K-major, swizzled ---------
-  // rot_even[k * 64 + p] = Pi[2p][k], rot_odd[k * 64 + p] = Pi[2p + 1][k]; consecutive threads take
-  // consecutive j (coalesced over p), a thread converts 8 consecutive k of its row j at a time
+  // rot_even[k * 64 + p] = Pi[2p][k], rot_odd[k * 64 + p] = Pi[2p + 1][k], read from the staging area
+  __syncthreads();  // the barrier is initialised, the copies are issued, the boundaries are in shared memory
+  if (warp >= 2 && warp < 2 + a.n_sources)
+    build_cells(s_bounds[warp - 2], a.n_bounds[warp - 2],
+                reinterpret_cast<float2*>(sm + kOffCells) + (warp - 2) * kCellCopies * kCells, &s_cells[warp - 2], lane);
+  const bool pi_ok = bar_wait_bounded(smem_addr(&s_bars.pi), 0u, &s_dead);
+  const float* raw = reinterpret_cast<const float*>(sm + kOffA);
   for (int i = tid; i < kD * (kD / 8); i += kThreads) {
     const int j = i & 127, k8 = i >> 7;  // row j, k = 8 * k8 .. + 7
-    const float* src = (j & 1 ? a.rot_odd : a.rot_even) + (j >> 1);
+    const float* src = raw + (j & 1) * (kD * (kD / 2)) + (j >> 1);
     uint16_t t[kMaxTerms][8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      float rest = __ldg(src + (8 * k8 + e) * (kD / 2)) * F::kScale;
+      float rest = src[(8 * k8 + e) * (kD / 2)] * F::kScale;
 #pragma unroll
       for (int m = 0; m < F::kTerms; ++m) t[m][e] = F::term(rest);
     }
@@ -237,7 +311,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
   const int64_t tiles_per_src = (rows_per_src + kRows - 1) / kRows;
   const int64_t n_tiles = tiles_per_src * a.n_sources;
   const int64_t my_tiles = (int64_t)blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  bool ok = true;
+  bool ok = pi_ok;
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -337,7 +411,19 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       uint32_t packed[16];  // 128 indices = 64 bytes
-      const float* b = s_bounds[src];
+      float b[15];
+#pragma unroll
+      for (int i = 0; i < 15; ++i) b[i] = s_bounds[src][i];
+      const float c_scale = s_cells[src].scale, c_off = s_cells[src].off;
+      const bool by_table = s_cells[src].ok != 0;
+      const float2* cells = reinterpret_cast<const float2*>(sm + kOffCells) + (src * kCellCopies + (lane & 3)) * kCells;
+      auto bucket = [&](float y) -> int {
+        if (by_table) {
+          const float2 e = cells[cell_of(y, c_scale, c_off)];
+          return __float_as_int(e.y) + (y > e.x ? 1 : 0);
+        }
+        return bucketize_reg(y, b);
+      };
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint32_t v[32];
@@ -347,8 +433,8 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
           uint32_t word = 0;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int ie = bucketize_sorted16(__uint_as_float(v[8 * w + 2 * e]) * scale, b);
-            const int io = bucketize_sorted16(__uint_as_float(v[8 * w + 2 * e + 1]) * scale, b);
+            const int ie = bucket(__uint_as_float(v[8 * w + 2 * e]) * scale);
+            const int io = bucket(__uint_as_float(v[8 * w + 2 * e + 1]) * scale);
             word |= (uint32_t)((ie << 4) | io) << (8 * e);
           }
           packed[4 * q + w] = word;
@@ -462,6 +548,7 @@ bool compress_tc16_eligible(const CompressArgs& a, int head_dim, int dtype) {
     if (((uintptr_t)a.x[s] & 15) || a.head_stride[s] != kD || a.token_stride[s] != (int64_t)a.num_heads * kD)
       return false;
   }
+  if (((uintptr_t)a.rot_even | (uintptr_t)a.rot_odd) & 15) return false;  // bulk copies of the rotation halves
   return true;
 }
 

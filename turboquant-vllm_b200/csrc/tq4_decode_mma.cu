@@ -45,13 +45,13 @@ constexpr uint32_t kTableBytes = 65536;
 // Timeline aid for tuning builds (-DTQ4_TRACE): lane 0 of every warp stamps %globaltimer at a few
 // points into a buffer read back with tq4_trace_read.  Compiled out of the shipped library.
 #ifdef TQ4_TRACE
-__device__ long long g_trace[160 * 16 * 8];
+__device__ long long g_trace[160 * 16 * 16];
 #define TQ4_STAMP(i)                                                                             \
   do {                                                                                           \
     if ((threadIdx.x & 31) == 0) {                                                               \
       long long t__;                                                                             \
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                    \
-      g_trace[((blockIdx.x % 160) * 16 + (threadIdx.x >> 5)) * 8 + (i)] = t__;                   \
+      g_trace[((blockIdx.x % 160) * 16 + (threadIdx.x >> 5)) * 16 + (i)] = t__;                   \
     }                                                                                            \
   } while (0)
 #else
@@ -287,15 +287,16 @@ __device__ __forceinline__ void split4(const float (&x)[4], uint32_t& h01, uint3
 template <int D>
 __device__ __forceinline__ void stage_rotation_split(const float* __restrict__ rotation, uint32_t tab) {
   constexpr int N4 = D * D / 4;
-  for (int i0 = threadIdx.x; i0 < N4; i0 += 4 * blockDim.x) {
-    float4 x[4];
+  constexpr int kBatch = 8;  // 16-byte loads in flight per thread (Pi is L2-resident: one round trip per batch)
+  for (int i0 = threadIdx.x; i0 < N4; i0 += kBatch * blockDim.x) {
+    float4 x[kBatch];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
       const int i = i0 + u * blockDim.x;
       if (i < N4) x[u] = __ldg(reinterpret_cast<const float4*>(rotation) + i);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kBatch; ++u) {
       const int i = i0 + u * blockDim.x;
       if (i < N4) {
         const int n = i / (D / 4), kc = i - n * (D / 4);
@@ -306,6 +307,35 @@ __device__ __forceinline__ void stage_rotation_split(const float* __restrict__ r
         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off), "r"(h01), "r"(h23) : "memory");
         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off + RotCfg<D>::LO_BASE), "r"(l01), "r"(l23) : "memory");
       }
+    }
+  }
+}
+
+// The same in two phases for blocks that hold the whole matrix in one batch of loads (kPiBatch per
+// thread): the loads are issued first, the plan is computed while they are in flight, then the
+// values are split and stored.
+constexpr int kPiBatch = 8;
+template <int D>
+__device__ __forceinline__ void pi_load(const float* __restrict__ rotation, float4 (&x)[kPiBatch]) {
+#pragma unroll
+  for (int u = 0; u < kPiBatch; ++u) {
+    const int i = threadIdx.x + u * blockDim.x;
+    if (i < D * D / 4) x[u] = __ldg(reinterpret_cast<const float4*>(rotation) + i);
+  }
+}
+template <int D>
+__device__ __forceinline__ void pi_store(const float4 (&x)[kPiBatch], uint32_t tab) {
+#pragma unroll
+  for (int u = 0; u < kPiBatch; ++u) {
+    const int i = threadIdx.x + u * blockDim.x;
+    if (i < D * D / 4) {
+      const int n = i / (D / 4), kc = i - n * (D / 4);
+      const float v[4] = {x[u].x * 256.f, x[u].y * 256.f, x[u].z * 256.f, x[u].w * 256.f};
+      uint32_t h01, h23, l01, l23;
+      split4(v, h01, h23, l01, l23);
+      const uint32_t off = tab + rot_chunk_off<D>(n, kc);
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off), "r"(h01), "r"(h23) : "memory");
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off + RotCfg<D>::LO_BASE), "r"(l01), "r"(l23) : "memory");
     }
   }
 }
@@ -331,69 +361,82 @@ __device__ __forceinline__ int warp_incl_scan(int v, int lane) {
   return v;
 }
 
-// The plan of a decode call, computed by one warp.  Writes the plan entries of the 32-row chunks
-// with chunk % n_warps == warp (and, warp 0, the totals); returns the rows [r_a, r_b] that hold the
-// first and the last tile of the tile range [T_a, T_b) given as multiples of tiles per span
-// (r_a = -1 if the range is empty).
-__device__ __forceinline__ void fused_plan(const AttnArgs& a, int warp, int n_warps, int lane,
-                                           int span_first, int span_count, int& r_a, int& r_b,
-                                           int& t_a, int& t_b) {
+// Tiles of a row that sees keys [start, end).
+__device__ __forceinline__ int row_tiles(int start, int end) {
+  return end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
+}
+
+// What one warp knows about the plan of a decode call after scanning the sequence lengths once
+// (registers only; nothing is read back from global memory).
+struct WarpPlan {
+  int total, tps;        // tiles of the call, tiles per span
+  int r0, r0_t0, r0_slot;  // first row of the warp's span (-1: the span is empty), its first tile, its first partial slot
+  int r_a, r_b;          // rows holding the first and the last tile of the CTA's tile range (-1: empty range)
+  int t_a, t_b;          // the CTA's tile range
+  bool rb_ends;          // row r_b's last tile lies inside the range (rows r_a .. r_b - 1 always end inside)
+};
+
+// The plan of a decode call as one warp needs it.  Code that runs once per launch pays for every
+// instruction it fetches, so this is two short rolled loops over chunks of 32 rows: the first sums
+// the tile counts, the second scans them (the sequence lengths are read again; they sit in L1 by
+// then) and derives the partial slots per row and the rows that hold the tiles the warp and its
+// CTA start and end with.  CTA 0 also stores the slot prefix the merge kernel reads after this
+// kernel has finished.
+__device__ __forceinline__ WarpPlan fused_plan(const AttnArgs& a, int warp, int n_warps, int lane,
+                                               int span, int span_first, int span_count) {
   const AttnShape& sh = a.sh;
-  const AttnPlan& p = a.plan;
   const int rows = sh.rows, n_chunks = (rows + 31) >> 5;
+  auto tiles_of = [&](int r) -> int {
+    int seq, start = 0, end = 0;
+    if (r < rows) decode_row_range(a, r, seq, start, end);
+    return row_tiles(start, end);
+  };
   int local = 0;
-  for (int ch = 0; ch < n_chunks; ++ch) {
-    const int r = ch * 32 + lane;
-    if (r < rows) {
-      int seq, start, end;
-      decode_row_range(a, r, seq, start, end);
-      local += end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
-    }
-  }
+#pragma unroll 4
+  for (int ch = 0; ch < n_chunks; ++ch) local += tiles_of(ch * 32 + lane);  // (independent loads, in flight together)
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-  const int total = local;
-  const int tps = max(1, (total + sh.span_ctas - 1) / sh.span_ctas);
-  const long long T_a = (long long)span_first * tps;
-  const long long T_b = min((long long)total, T_a + (long long)span_count * tps);
-  r_a = -1;
-  r_b = -1;
-  t_a = (int)min(T_a, (long long)total);
-  t_b = (int)T_b;
+  WarpPlan wp;
+  wp.total = local;
+  wp.tps = max(1, (wp.total + sh.span_ctas - 1) / sh.span_ctas);
+  const int T_a = (int)min((long long)span_first * wp.tps, (long long)wp.total);
+  const int T_b = (int)min((long long)wp.total, (long long)T_a + (long long)span_count * wp.tps);
+  const long long T_w = (long long)span * wp.tps;  // first tile of the warp's own span
+  wp.t_a = T_a;
+  wp.t_b = T_b;
+  wp.r0 = wp.r_a = wp.r_b = -1;
+  wp.r0_t0 = wp.r0_slot = 0;
+  wp.rb_ends = false;
   int run_t = 0, run_s = 0;
+#pragma unroll 1
   for (int ch = 0; ch < n_chunks; ++ch) {
-    const int r = ch * 32 + lane;
-    int seq = 0, start = 0, end = 0, nt = 0;
-    if (r < rows) {
-      decode_row_range(a, r, seq, start, end);
-      nt = end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
-    }
+    const int nt = tiles_of(ch * 32 + lane);
     const int incl_t = warp_incl_scan(nt, lane);
     const int b = run_t + incl_t - nt, e = b + nt;
-    const int ns = nt > 0 ? (e - 1) / tps - b / tps + 1 : 0;
+    const int ns = nt > 0 ? (e - 1) / wp.tps - b / wp.tps + 1 : 0;
     const int incl_s = warp_incl_scan(ns, lane);
-    if (ch % n_warps == warp && r < rows) {
-      p.kv_start[r] = start;
-      p.kv_end[r] = end;
-      p.row_seq[r] = seq;
-      p.tile_prefix[r] = b;
-      p.slot_base[r] = run_s + incl_s - ns;
+    const int pre_s = run_s + incl_s - ns;
+    if (blockIdx.x == 0 && ch % n_warps == warp && ch * 32 + lane < rows)
+      a.plan.slot_base[ch * 32 + lane] = pre_s;
+    // rows that hold: the warp's first tile, the CTA's first tile, the CTA's last tile
+    const unsigned mw = __ballot_sync(0xffffffffu, nt > 0 && b <= T_w && T_w < e);
+    const unsigned ma = __ballot_sync(0xffffffffu, T_a < T_b && nt > 0 && b <= T_a && T_a < e);
+    const unsigned mb = __ballot_sync(0xffffffffu, T_a < T_b && nt > 0 && b < T_b && T_b <= e);
+    if (mw) {
+      wp.r0 = ch * 32 + __ffs(mw) - 1;
+      wp.r0_t0 = __shfl_sync(0xffffffffu, b, __ffs(mw) - 1);
+      wp.r0_slot = __shfl_sync(0xffffffffu, pre_s, __ffs(mw) - 1);
     }
-    if (T_a < T_b) {
-      const unsigned ma = __ballot_sync(0xffffffffu, nt > 0 && b <= T_a && T_a < e);
-      const unsigned mb = __ballot_sync(0xffffffffu, nt > 0 && b <= T_b - 1 && T_b - 1 < e);
-      if (ma) r_a = ch * 32 + __ffs(ma) - 1;
-      if (mb) r_b = ch * 32 + __ffs(mb) - 1;
+    if (ma) wp.r_a = ch * 32 + __ffs(ma) - 1;
+    if (mb) {
+      wp.r_b = ch * 32 + __ffs(mb) - 1;
+      wp.rb_ends = __shfl_sync(0xffffffffu, e, __ffs(mb) - 1) == T_b;
     }
     run_t += __shfl_sync(0xffffffffu, incl_t, 31);
     run_s += __shfl_sync(0xffffffffu, incl_s, 31);
   }
-  if (warp == 0 && lane == 0) {
-    p.tile_prefix[rows] = total;
-    p.slot_base[rows] = run_s;
-    p.scalars[0] = total;
-    p.scalars[1] = tps;
-  }
+  if (blockIdx.x == 0 && warp == 0 && lane == 0) a.plan.slot_base[rows] = run_s;
+  return wp;
 }
 
 // Four consecutive elements e0 .. e0 + 3 of a query vector as floats.
@@ -419,185 +462,242 @@ __device__ __forceinline__ void load_q4(const void* q, int dtype, int64_t idx, b
   }
 }
 
-// Rotation work of a CTA, on mma.sync (see the header of this section):
-//  * q_rot rows [r_a, r_b] x heads [h0, h0 + nh) = q * Pi^T;
-//  * with `w` (a decode step's cache write): for every row of [r_a, r_b] whose LAST tile lies in the
-//    CTA's tile range [t_a, t_b), the K and V vectors of that row's new token for the KV heads
-//    [kvh0, kvh0 + nkv): norm (summed in the order of the compress kernels, so the stored norms are
-//    bit-identical to theirs), x / (norm + 1e-10), rotation, bucketize, nibble pack, stored at the
-//    token's slot.  The CTA that reads a row's last tile is the one that writes it, so a block
-//    barrier (plus the generic -> async proxy fence) orders the write before the read.
-// Work is cut into tasks of 16 vectors x 32 outputs, handed out to the warps round robin.  Lane
-// (g, c) of a warp owns, per k-step s, the four contiguous elements 16 s + 4 c .. + 3 of vectors g
-// and g + 8 (the k order inside a step is a permutation applied to both operands, which leaves the
-// sum unchanged).  s_bounds: [2][16] sorted boundaries of K and V padded with +inf.
+// Rotation work of a CTA, on mma.sync (see the header of this section).  The vectors of a CTA are
+//  * q rows [r_a, r_b] x heads [h0, h0 + nh), rotated into the q_rot scratch, and
+//  * with `w` (a decode step's cache write) the K and V vectors of the new token of every row of
+//    [r_a, r_b] whose LAST tile lies in the CTA's tile range, for the KV heads [kvh0, kvh0 + nkv):
+//    norm (summed in the order of the compress kernels, so the stored norms are bit-identical to
+//    theirs), x / (norm + 1e-10), rotation, bucketize, nibble pack, stored at the token's slot.  The
+//    CTA that reads a row's last tile is the one that writes it, so a block barrier (plus the
+//    generic -> async proxy fence) orders the write before the read.
+// They are handled in GROUPS of 16.  fused_prep_group (one warp per group) turns a group into the
+// A operand of the product -- 16 x D fp16 hi and lo tiles in the warp's (still idle) ring memory,
+// each vector scaled by a power of two into [1, 2) -- plus 16 bytes of bookkeeping per vector;
+// fused_mma_tasks multiplies (group, 32 output coordinates) tasks, handed out to all warps round
+// robin.  Both are short rolled loops: code that runs once per launch costs its instruction
+// fetches.  Lane (g, c) owns, per k-step s, the four contiguous elements 16 s + 4 c .. + 3 of
+// vectors g and g + 8 (the k order inside a step is a permutation applied to both operands).
+struct RotRows {
+  int r_a, r_b;      // query rows of the CTA
+  bool rb_ends;      // row r_b's last tile belongs to the CTA (rows before it always end inside)
+  int h0, nh;        // query heads of the CTA's slice
+  int kvh0, nkv;     // KV heads of the CTA's slice
+  int n_q, n_vec;    // query vectors, all vectors (queries first, then K / V vectors of the new tokens)
+};
+// per-vector bookkeeping word: where the result goes
+constexpr unsigned long long kRowInvalid = 1ull << 63, kRowWrite = 1ull << 62, kRowV = 1ull << 61;
+constexpr unsigned long long kRowOffMask = (1ull << 61) - 1;
 template <int D>
-__device__ __forceinline__ void fused_rotate(const AttnArgs& a, const CompressArgs* w, const float* s_bounds,
-                                             uint32_t tab, int warp, int n_warps, int lane, int r_a, int r_b,
-                                             int t_a, int t_b, int h0, int nh, int kvh0, int nkv) {
+struct GroupMem {  // byte offsets inside a warp's ring memory
+  static constexpr int kHalf = 16 * RotCfg<D>::PITCH;  // one 16 x D fp16 tile
+  static constexpr int kInfo = 2 * kHalf;              // 16 x {u64 where, f32 1 / scale, f32 norm}
+  static constexpr int kBytes = kInfo + 16 * 16;
+};
+
+template <int D>
+__device__ __forceinline__ void fused_prep_group(const AttnArgs& a, const CompressArgs& w, bool has_write,
+                                                 const RotRows& rr, int group, uint32_t mem, int lane) {
   using R = RotCfg<D>;
   const AttnShape& sh = a.sh;
-  const AttnPlan& p = a.plan;
   const int g = lane >> 2, c = lane & 3;
-  const int n_rows = r_b - r_a + 1;
-  const int n_q = n_rows * nh;
-  const int n_w = w ? n_rows * 2 * nkv : 0;
-  const int n_vec = n_q + n_w;
-  const int n_tasks = ((n_vec + 15) >> 4) * R::NQ;
-  const int qes = a.q_dtype == TQ4_F32 ? 4 : 2;
-  const bool q_vec_ok = ((uintptr_t)a.q % 16 == 0) && (a.q_token_stride * qes) % 16 == 0 &&
-                        (a.q_head_stride * qes) % 16 == 0;
   const RowLayout lay = row_layout(sh.Hkv, D);
-  for (int task = warp; task < n_tasks; task += n_warps) {
-    const int grp = task / R::NQ, nq = task - grp * R::NQ;
-    uint32_t ah[R::KS][4], al[R::KS][4];  // A fragments (a0..a3) of the hi and lo terms
-    float inv_scale[2], nrm[2];
-    int64_t q_out[2];         // q rows: offset into q_rot, else -1
-    uint8_t* w_idx[2];        // write rows: the head's packed index bytes in the cache row, else nullptr
-    float* w_norm[2];
-    int w_src[2];
-#pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {  // vector g (hf = 0) and vector g + 8 (hf = 1)
-      const int v = grp * 16 + g + 8 * hf;
-      q_out[hf] = -1;
-      w_idx[hf] = nullptr;
-      w_norm[hf] = nullptr;
-      w_src[hf] = 0;
-      const void* src_ptr = nullptr;
-      int src_dtype = a.q_dtype;
-      int64_t base = 0;
-      bool vec_ok = q_vec_ok;
-      if (v < n_q) {
-        const int ri = v / nh, h = h0 + (v - ri * nh);
-        const int r = r_a + ri;
-        q_out[hf] = ((int64_t)r * sh.Hq + h) * D;
-        src_ptr = a.q;
-        base = ((int64_t)r + sh.row_offset) * a.q_token_stride + (int64_t)h * a.q_head_stride + 4 * c;
-      } else if (v < n_vec) {
-        const int wi = v - n_q;
-        const int ri = wi / (2 * nkv), rem = wi - ri * (2 * nkv);
-        const int src = rem / nkv, kvh = kvh0 + (rem - src * nkv);
-        const int r = r_a + ri;
-        const int tok = r + sh.row_offset;
-        const int kv_start = p.kv_start[r], kv_end = p.kv_end[r];
-        const int nt = kv_end > kv_start ? (kv_end + kTileTokens - 1) / kTileTokens - kv_start / kTileTokens : 0;
-        const int last_tile = p.tile_prefix[r] + nt - 1;
-        if (nt > 0 && last_tile >= t_a && last_tile < t_b && tok < w->n_tokens && tok < w->n_slots) {
-          const int64_t slot = w->slot_mapping[tok];
-          if (slot >= w->num_cache_slots) {
-            if (c == 0 && w->err_flag) atomicOr(w->err_flag, TQ4_DEV_BAD_SLOT);
-          } else if (slot >= 0) {
-            // the write is ordered before this call's reads only if the slot is the row's last position
-            const int pos = kv_end - 1;
-            const int blk = __ldg(a.block_table + (int64_t)p.row_seq[r] * a.bt_stride + pos / a.block_size);
-            if ((int64_t)blk * a.block_size + pos % a.block_size != slot && c == 0 && w->err_flag)
-              atomicOr(w->err_flag, TQ4_DEV_WRITE_ORDER);
-            uint8_t* rowp = w->cache + slot * w->cache_token_stride;
-            w_idx[hf] = rowp + (src == 0 ? lay.k_idx : lay.v_idx) + kvh * (D / 2);
-            w_norm[hf] = reinterpret_cast<float*>(rowp + (src == 0 ? lay.k_norm : lay.v_norm) + kvh * 4);
-            w_src[hf] = src;
-            src_ptr = w->x[src];
-            src_dtype = w->x_dtype;
-            const int es = src_dtype == TQ4_F32 ? 4 : 2;
-            vec_ok = ((uintptr_t)src_ptr % 16 == 0) && (w->token_stride[src] * es) % 16 == 0 &&
-                     (w->head_stride[src] * es) % 16 == 0;
-            base = (int64_t)tok * w->token_stride[src] + (int64_t)kvh * w->head_stride[src] + 4 * c;
-          }
+#pragma unroll 1
+  for (int hf = 0; hf < 2; ++hf) {  // vector g, then vector g + 8 of the group
+    const int row = g + 8 * hf, v = group * 16 + row;
+    unsigned long long where = kRowInvalid;
+    const void* src_ptr = nullptr;
+    int src_dtype = a.q_dtype;
+    int64_t base = 0, ts = a.q_token_stride, hs = a.q_head_stride;
+    if (v < rr.n_q) {
+      const int ri = v / rr.nh, h = rr.h0 + (v - ri * rr.nh);
+      const int r = rr.r_a + ri;
+      where = (unsigned long long)(((int64_t)r * sh.Hq + h) * D);
+      src_ptr = a.q;
+      base = ((int64_t)r + sh.row_offset) * ts + (int64_t)h * hs;
+    } else if (v < rr.n_vec) {
+      const int wi = v - rr.n_q;
+      const int ri = wi / (2 * rr.nkv), rem = wi - ri * (2 * rr.nkv);
+      const int src = rem >= rr.nkv ? 1 : 0, kvh = rr.kvh0 + rem - src * rr.nkv;
+      const int r = rr.r_a + ri, tok = r + sh.row_offset;
+      if (tok < w.n_tokens && tok < w.n_slots) {
+        // the loads below do not depend on one another: one memory round trip
+        int seq, kv_start, kv_end;
+        decode_row_range(a, r, seq, kv_start, kv_end);
+        const int64_t slot = __ldg(w.slot_mapping + tok);
+        const int pos = max(kv_end - 1, 0);
+        const int blk = __ldg(a.block_table + (int64_t)seq * a.bt_stride + pos / a.block_size);
+        const bool ends_here = kv_end > kv_start && (r < rr.r_b || rr.rb_ends);
+        if (ends_here && slot >= w.num_cache_slots) {
+          if (c == 0 && w.err_flag) atomicOr(w.err_flag, TQ4_DEV_BAD_SLOT);
+        } else if (ends_here && slot >= 0) {
+          // the write is ordered before this call's reads only if the slot is the row's last position
+          if ((int64_t)blk * a.block_size + pos % a.block_size != slot && c == 0 && w.err_flag)
+            atomicOr(w.err_flag, TQ4_DEV_WRITE_ORDER);
+          where = kRowWrite | (src ? kRowV : 0ull) |
+                  (unsigned long long)(slot * w.cache_token_stride + (src ? lay.v_idx : lay.k_idx) + kvh * (D / 2));
         }
-      }
-      float x[R::KS][4];
-#pragma unroll
-      for (int s = 0; s < R::KS; ++s) {
-        if (src_ptr) load_q4(src_ptr, src_dtype, base + 16 * s, vec_ok, x[s]);
-        else x[s][0] = x[s][1] = x[s][2] = x[s][3] = 0.f;
-      }
-      // ---- squared norm in the order of the compress kernels: element k belongs to partial
-      // l = k mod 32 (an ascending FMA chain over k = l, l + 32, ...), the partials are merged by the
-      // butterfly 16, 8, 4, 2, 1.  This lane holds l = 4 c + e and l + 16 (k-steps 2 i and 2 i + 1).
-      {
-        float pa[4], pb[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          pa[e] = 0.f;
-          pb[e] = 0.f;
-#pragma unroll
-          for (int i = 0; i < R::KS / 2; ++i) {
-            pa[e] = fmaf(x[2 * i][e], x[2 * i][e], pa[e]);
-            pb[e] = fmaf(x[2 * i + 1][e], x[2 * i + 1][e], pb[e]);
-          }
-          pa[e] = pa[e] + pb[e];                                       // l ^ 16
-          pa[e] = pa[e] + __shfl_xor_sync(0xffffffffu, pa[e], 2);      // l ^ 8  (lane c ^ 2)
-          pa[e] = pa[e] + __shfl_xor_sync(0xffffffffu, pa[e], 1);      // l ^ 4  (lane c ^ 1)
-        }
-        const float d0 = pa[0] + pa[2], d1 = pa[1] + pa[3];            // l ^ 2
-        nrm[hf] = sqrtf(d0 + d1);                                       // l ^ 1
-      }
-      float amax = 0.f;
-      if (w_idx[hf]) {
-        const float den = nrm[hf] + 1e-10f;
-#pragma unroll
-        for (int s = 0; s < R::KS; ++s)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) x[s][i] = x[s][i] / den;
-      }
-#pragma unroll
-      for (int s = 0; s < R::KS; ++s)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(x[s][i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      // power of two that brings the largest element into [1, 2); exact in both directions
-      float sc = 1.f, isc = 1.f;
-      if (amax > 0.f && amax < CUDART_INF_F) {
-        const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
-        const int exc = min(max(ex, -100), 100);
-        sc = __uint_as_float((uint32_t)(127 - exc) << 23);
-        isc = __uint_as_float((uint32_t)(127 + exc) << 23);
-      }
-      inv_scale[hf] = isc * (1.f / 256.f);
-#pragma unroll
-      for (int s = 0; s < R::KS; ++s) {
-        const float y[4] = {x[s][0] * sc, x[s][1] * sc, x[s][2] * sc, x[s][3] * sc};
-        uint32_t h01, h23, l01, l23;
-        split4(y, h01, h23, l01, l23);
-        // a0 / a1 = (row g / g + 8, first k pair), a2 / a3 = (row g / g + 8, second k pair)
-        ah[s][hf] = h01; ah[s][2 + hf] = h23;
-        al[s][hf] = l01; al[s][2 + hf] = l23;
+        src_ptr = src ? w.x[1] : w.x[0];
+        src_dtype = w.x_dtype;
+        ts = src ? w.token_stride[1] : w.token_stride[0];
+        hs = src ? w.head_stride[1] : w.head_stride[0];
+        base = (int64_t)tok * ts + (int64_t)kvh * hs;
       }
     }
-    const bool any_row = q_out[0] >= 0 || q_out[1] >= 0 || w_idx[0] != nullptr || w_idx[1] != nullptr;
-    if (!__any_sync(0xffffffffu, any_row)) continue;  // e.g. a group of write rows that end elsewhere
+    const int es = src_dtype == TQ4_F32 ? 4 : 2;
+    const bool vec_ok = ((uintptr_t)src_ptr % 16 == 0) && (ts * es) % 16 == 0 && (hs * es) % 16 == 0;
+    float x[R::KS][4];
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb) {
-      const int n = (nq * 4 + nb) * 8 + g;  // this lane's B column (output coordinate)
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < R::KS; ++s) {
+      if (src_ptr) load_q4(src_ptr, src_dtype, base + 16 * s + 4 * c, vec_ok, x[s]);
+      else x[s][0] = x[s][1] = x[s][2] = x[s][3] = 0.f;
+    }
+    // ---- squared norm in the order of the compress kernels: element k belongs to partial
+    // l = k mod 32 (an ascending FMA chain over k = l, l + 32, ...), the partials are merged by the
+    // butterfly 16, 8, 4, 2, 1.  This lane holds l = 4 c + e and l + 16 (k-steps 2 i and 2 i + 1).
+    float pa[4];
 #pragma unroll
-      for (int s = 0; s < R::KS; ++s) {
-        const uint32_t off = tab + rot_chunk_off<D>(n, 4 * s + c);
-        uint32_t bh[2], bl[2];
-        lds_words<8>(off, bh);
-        lds_words<8>(off + R::LO_BASE, bl);
-        mma16816(acc, al[s][0], al[s][1], al[s][2], al[s][3], bh[0], bh[1]);
-        mma16816(acc, ah[s][0], ah[s][1], ah[s][2], ah[s][3], bl[0], bl[1]);
-        mma16816(acc, ah[s][0], ah[s][1], ah[s][2], ah[s][3], bh[0], bh[1]);
+    for (int e = 0; e < 4; ++e) {
+      float p0 = 0.f, p1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < R::KS / 2; ++i) {
+        p0 = fmaf(x[2 * i][e], x[2 * i][e], p0);
+        p1 = fmaf(x[2 * i + 1][e], x[2 * i + 1][e], p1);
       }
-      const int n0 = (nq * 4 + nb) * 8 + 2 * c;  // C columns of this lane: coordinates n0 (even), n0 + 1
+      pa[e] = p0 + p1;                                                // l ^ 16
+      pa[e] = pa[e] + __shfl_xor_sync(0xffffffffu, pa[e], 2);         // l ^ 8  (lane c ^ 2)
+      pa[e] = pa[e] + __shfl_xor_sync(0xffffffffu, pa[e], 1);         // l ^ 4  (lane c ^ 1)
+    }
+    const float nrm = sqrtf((pa[0] + pa[2]) + (pa[1] + pa[3]));       // l ^ 2, l ^ 1
+    // write vectors are normalised first (x * (1 / den) is within an ulp of x / den); then every
+    // vector is scaled by the power of two that brings its largest element into [1, 2)
+    const float pre = (where & kRowWrite) ? 1.f / (nrm + 1e-10f) : 1.f;
+    float amax = 0.f;
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const float y0 = acc[2 * hf] * inv_scale[hf], y1 = acc[2 * hf + 1] * inv_scale[hf];
-        if (q_out[hf] >= 0) {
-          *reinterpret_cast<float2*>(p.q_rot + q_out[hf] + n0) = make_float2(y0, y1);
-        } else if (w_idx[hf]) {
-          const float* bd = s_bounds + 16 * w_src[hf];
-          w_idx[hf][n0 >> 1] = (uint8_t)((bucketize_sorted16(y0, bd) << 4) | bucketize_sorted16(y1, bd));
-        }
+    for (int s = 0; s < R::KS; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x[s][i] *= pre;
+        amax = fmaxf(amax, fabsf(x[s][i]));
       }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    float sc = 1.f, isc = 1.f;
+    if (amax > 0.f && amax < CUDART_INF_F) {
+      const int exc = min(max((int)((__float_as_uint(amax) >> 23) & 0xFFu) - 127, -100), 100);
+      sc = __uint_as_float((uint32_t)(127 - exc) << 23);
+      isc = __uint_as_float((uint32_t)(127 + exc) << 23);
     }
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf)
-      if (w_idx[hf] && nq == 0 && c == 0) *w_norm[hf] = nrm[hf];
+    for (int s = 0; s < R::KS; ++s) {
+      const float y[4] = {x[s][0] * sc, x[s][1] * sc, x[s][2] * sc, x[s][3] * sc};
+      uint32_t h01, h23, l01, l23;
+      split4(y, h01, h23, l01, l23);
+      const uint32_t off = mem + rot_chunk_off<D>(row, 4 * s + c);
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off), "r"(h01), "r"(h23) : "memory");
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(off + GroupMem<D>::kHalf), "r"(l01), "r"(l23) : "memory");
+    }
+    if (c == 0) {
+      const uint32_t io = mem + GroupMem<D>::kInfo + row * 16;
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(io), "r"((uint32_t)where), "r"((uint32_t)(where >> 32)) : "memory");
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(io + 8), "r"(__float_as_uint(isc * (1.f / 256.f))),
+                   "r"(__float_as_uint(nrm)) : "memory");
+    }
   }
-  if (w) asm volatile("fence.proxy.async.global;" ::: "memory");  // the cache rows are read back by bulk tensor copies
+}
+
+// One task: the 16 vectors of the group staged at `mem` times the output coordinates
+// [32 nq, 32 nq + 32) of Pi (hi / lo fp16 at `tab`), two n-blocks at a time.
+template <int D>
+__device__ __forceinline__ void fused_mma_task(const AttnArgs& a, const CompressArgs& w, const float* s_bounds,
+                                               uint32_t tab, uint32_t mem, int nq, int lane) {
+  using R = RotCfg<D>;
+  const int g = lane >> 2, c = lane & 3;
+  // where the two vectors of this lane (g and g + 8) go
+  unsigned long long where[2];
+  float inv_scale[2], nrm[2];
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    uint32_t q4[4];
+    lds_words<16>(mem + GroupMem<D>::kInfo + (g + 8 * hf) * 16, q4);
+    where[hf] = (unsigned long long)q4[0] | ((unsigned long long)q4[1] << 32);
+    inv_scale[hf] = __uint_as_float(q4[2]);
+    nrm[hf] = __uint_as_float(q4[3]);
+  }
+  const bool any_row = !(where[0] & kRowInvalid) || !(where[1] & kRowInvalid);
+  if (!__any_sync(0xffffffffu, any_row)) return;  // e.g. new tokens of rows that end in another CTA
+  TQ4_STAMP(8);
+  // 8-byte chunk 4 s + c of row n sits at n * PITCH + 8 * ((4 s + c) ^ x) with x = 4 * (n & 3) (no XOR
+  // at head_dim 96); every row this lane touches (g, g + 8, 8 * block + g) has n & 3 = g & 3, so the
+  // chunk offset of k-step s is the same for all of them
+  const uint32_t gx = R::XOR ? (uint32_t)(g & 3) : 0u;
+  const uint32_t a_row = mem + g * R::PITCH + 8 * c;
+  // the four n-blocks of the task advance together, each with a main (hi * hi) and a correction
+  // (lo * hi + hi * lo) accumulator: eight independent chains of 8 / 16 dependent MMAs
+  const uint32_t b_row = tab + (nq * 32 + g) * R::PITCH + 8 * c;
+  float acc[4][4], cor[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = cor[j][e] = 0.f;
+#pragma unroll 2
+  for (int s = 0; s < R::KS; ++s) {
+    const uint32_t ko = 32u * ((uint32_t)s ^ gx);
+    uint32_t ah0[2], ah1[2], al0[2], al1[2];
+    lds_words<8>(a_row + ko, ah0);
+    lds_words<8>(a_row + ko + 8 * R::PITCH, ah1);
+    lds_words<8>(a_row + ko + GroupMem<D>::kHalf, al0);
+    lds_words<8>(a_row + ko + GroupMem<D>::kHalf + 8 * R::PITCH, al1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t bh[2], bl[2];
+      lds_words<8>(b_row + ko + j * 8 * R::PITCH, bh);
+      lds_words<8>(b_row + ko + j * 8 * R::PITCH + R::LO_BASE, bl);
+      mma16816(acc[j], ah0[0], ah1[0], ah0[1], ah1[1], bh[0], bh[1]);
+      mma16816(cor[j], al0[0], al1[0], al0[1], al1[1], bh[0], bh[1]);
+      mma16816(cor[j], ah0[0], ah1[0], ah0[1], ah1[1], bl[0], bl[1]);
+    }
+  }
+#pragma unroll 1
+  for (int j = 0; j < 4; ++j) {
+    const int n0 = (nq * 4 + j) * 8 + 2 * c;  // C columns of this lane: coordinates n0 (even), n0 + 1
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      // (indexing the accumulators with the rolled j would spill them: select instead)
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+        if (jj == j) {
+          y0 = (acc[jj][2 * hf] + cor[jj][2 * hf]) * inv_scale[hf];
+          y1 = (acc[jj][2 * hf + 1] + cor[jj][2 * hf + 1]) * inv_scale[hf];
+        }
+      const unsigned long long wh = where[hf];
+      if (wh & kRowInvalid) continue;
+      if (!(wh & kRowWrite)) {
+        *reinterpret_cast<float2*>(a.plan.q_rot + (int64_t)(wh & kRowOffMask) + n0) = make_float2(y0, y1);
+      } else {
+        const float* bd = s_bounds + ((wh & kRowV) ? 16 : 0);
+        w.cache[(int64_t)(wh & kRowOffMask) + (n0 >> 1)] =
+            (uint8_t)((bucketize_sorted16(y0, bd) << 4) | bucketize_sorted16(y1, bd));
+      }
+    }
+  }
+  // the fp32 norm of a written vector is stored once, by the task of the first 32 coordinates
+  if (nq == 0 && c == 0) {
+    const RowLayout lay = row_layout(a.sh.Hkv, D);
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const unsigned long long wh = where[hf];
+      if ((wh & kRowInvalid) || !(wh & kRowWrite)) continue;
+      // index bytes of head h start at region + h * D/2, its norm at region_norm + h * 4
+      const int64_t off = (int64_t)(wh & kRowOffMask);
+      const int64_t row_start = off / w.cache_token_stride * w.cache_token_stride;
+      const int in_row = (int)(off - row_start);
+      const int region = (wh & kRowV) ? lay.v_idx : lay.k_idx;
+      const int h = (in_row - region) / (D / 2);
+      *reinterpret_cast<float*>(w.cache + row_start + ((wh & kRowV) ? lay.v_norm : lay.k_norm) + 4 * h) = nrm[hf];
+    }
+  }
+  TQ4_STAMP(9);
 }
 
 // byte offset (within a head's D/2 V bytes) of this thread's m-block i
@@ -647,65 +747,7 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
     return;
   }
   TQ4_STAMP(0);
-  // ---- fused prologue: tile plan + query rotation for the rows this CTA's spans touch ------------
-  if (a.fused) {
-    if constexpr (D <= 128) {
-      const int n_warps = blockDim.x >> 5;
-      const int cta_f = blockIdx.x % sh.ctas, slice_f = blockIdx.x / sh.ctas;
-      int r_a, r_b, t_a, t_b;
-      fused_plan(a, warp, n_warps, lane, cta_f * sh.TPC, sh.TPC, r_a, r_b, t_a, t_b);
-      TQ4_STAMP(1);
-      stage_rotation_split<D>(a.rotation, tab);
-      if (has_write && threadIdx.x < 32) {  // sorted boundaries of K and V, padded with +inf
-        const int src = threadIdx.x >> 4, i = threadIdx.x & 15;
-        s_cent[src][i] = i < w.n_bounds[src] ? w.bounds[src][i] : CUDART_INF_F;
-      }
-      __syncthreads();
-      TQ4_STAMP(2);
-      if (r_a >= 0 && r_b >= r_a) {
-        const int vh0 = slice_f * sh.HPC, vh1 = vh0 + sh.HPC - 1;
-        const int h0 = (vh0 / sh.NCH) * sh.G + (vh0 % sh.NCH) * sh.GC;
-        const int c1 = vh1 % sh.NCH;
-        const int h1 = (vh1 / sh.NCH) * sh.G + c1 * sh.GC + min(sh.GC, sh.G - c1 * sh.GC);
-        const int kvh0 = vh0 / sh.NCH, kvh1 = vh1 / sh.NCH;
-        // (a KV head shared by two slices, G > 8, is written by the slice that holds its first chunk)
-        const int kv_first = (vh0 % sh.NCH) ? kvh0 + 1 : kvh0;
-        fused_rotate<D>(a, has_write ? &w : nullptr, &s_cent[0][0], tab, warp, n_warps, lane, r_a, r_b, t_a, t_b,
-                        h0, h1 - h0, kv_first, kvh1 - kv_first + 1);
-      }
-    }
-    __syncthreads();  // plan and rotated queries are visible to the block; the table region is free
-    TQ4_STAMP(3);
-  }
-  // ---- replicated byte -> half2 tables: slot l < 32 = K table of lane l, slot 32 + l = V -------
-  if (threadIdx.x < 2 * TQ4_MAX_CENTROIDS) {
-    const int w = threadIdx.x >> 4, i = threadIdx.x & 15;
-    const float* cent = w ? a.v_centroids : a.k_centroids;
-    const int nc = w ? a.n_v_centroids : a.n_k_centroids;
-    s_cent[w][i] = i < nc ? __fmul_rn(w ? a.lut_scale_v : a.lut_scale_k, cent[i]) : 0.f;
-  }
-  __syncthreads();
-  {
-    // the 32 lane copies of an entry are contiguous: four per 16-byte store
-    uint4* t = reinterpret_cast<uint4*>(smem_raw + (tab - base));
-    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
-      const int byte = i >> 4, w = (i >> 3) & 1;
-      const uint32_t v = pack_h2(s_cent[w][byte >> 4], s_cent[w][byte & 15]);
-      t[i] = make_uint4(v, v, v, v);
-    }
-  }
-  if (TMA && lane == 0) {
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&s_bar[warp][s]), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  __syncthreads();
-  // everything above used only caller inputs and shared memory; from here on the kernel reads the
-  // plan, the rotated queries and the cache, which the preceding kernels produce
-  pdl_trigger();
-  pdl_wait();
-  TQ4_STAMP(4);
+  // ---- lane- and warp-constant addressing (pure arithmetic) ----------------------------------------
   const uint32_t lb_k = tab + lane * 4, lb_v = tab + 128 + lane * 4;
   const uint32_t bar0 = smem_u32(&s_bar[warp][0]);
   // Row g of the score MMA / k-slot of the PV MMA does not hold token g of the tile but token
@@ -723,10 +765,16 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
   };
   const int rg = sigma(g), rc0 = sigma(2 * c), rc1 = sigma(2 * c + 1);
   constexpr bool SWZ = TMA && D == 128 && !VWIDE && !ROWBOX;  // 64-byte rows: CU_TENSOR_MAP_SWIZZLE_64B
+  const int cta = blockIdx.x % sh.ctas, slice = blockIdx.x / sh.ctas;
+  const int vh = slice * sh.HPC + warp % sh.HPC, ts = warp / sh.HPC;
+  const int kvh = vh / sh.NCH, chunk = vh % sh.NCH;
+  const int qh0 = kvh * sh.G + chunk * sh.GC;
+  const int gcount = min(sh.GC, sh.G - chunk * sh.GC);
+  const RowLayout lay = row_layout(sh.Hkv, D);
   // byte offsets of this head's K norm / V indices / V norm relative to the 16-byte boundary below
-  const int kn_sub = (row_layout(sh.Hkv, D).k_norm + 4 * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15;
-  const int vn_sub = (row_layout(sh.Hkv, D).v_norm + 4 * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15;
-  const int v_sub = VWIDE ? ((row_layout(sh.Hkv, D).v_idx + C::HALF * ((blockIdx.x / sh.ctas * sh.HPC + warp % sh.HPC) / sh.NCH)) & 15) : 0;
+  const int kn_sub = (lay.k_norm + 4 * kvh) & 15;
+  const int vn_sub = (lay.v_norm + 4 * kvh) & 15;
+  const int v_sub = VWIDE ? ((lay.v_idx + C::HALF * kvh) & 15) : 0;
   auto tile_off = [&](int row, int byte) -> uint32_t {  // offset of (row, byte) inside a [16][D/2] tile
     return SWZ ? (uint32_t)(row * 64 + ((((byte >> 4) ^ (row >> 1)) & 3) << 4) + (byte & 15))
                : (uint32_t)(row * C::HALF + byte);
@@ -750,18 +798,8 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
   constexpr uint32_t kNormRow8 = ROWBOX ? 8 * kRowPitch : 128;
   uint32_t gk = 0;      // tiles this warp has pushed through the ring (stage = gk % kStages)
   bool dead = false;    // a bounded wait gave up: stop issuing work, fall through to the end
-
-  const int cta = blockIdx.x % sh.ctas, slice = blockIdx.x / sh.ctas;
-  const int vh = slice * sh.HPC + warp % sh.HPC, ts = warp / sh.HPC;
-  const int kvh = vh / sh.NCH, chunk = vh % sh.NCH;
-  const int qh0 = kvh * sh.G + chunk * sh.GC;
-  const int gcount = min(sh.GC, sh.G - chunk * sh.GC);
   // every warp phase streams its own contiguous span of the tile stream: span index = cta * TPC + ts
   const int span = cta * sh.TPC + ts;
-  const int total = p.scalars[0], tps = p.scalars[1];
-  const int t_begin = span * tps, t_end = min(total, t_begin + tps);
-  if (t_begin >= t_end) return;
-  const RowLayout lay = row_layout(sh.Hkv, D);
   const int k_off = lay.k_idx + kvh * C::HALF + c * C::KBY;  // this thread's K chunk
   // x coordinates (bytes within a token row, 16-byte aligned) of this head's four TMA boxes
   const int x_k = lay.k_idx + kvh * C::HALF, x_v = (lay.v_idx + kvh * C::HALF) & ~15;
@@ -773,11 +811,185 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
   const uint32_t ts32 = (uint32_t)a.cache_token_stride;
   const int bs_shift = (a.block_size & (a.block_size - 1)) == 0 ? __ffs(a.block_size) - 1 : -1;
 
+  // The box copies of one tile pair into ring stage st (tiles at positions pos and pos + 16 of pages
+  // ba / bb; `two` = the second tile exists), issued by one elected lane onto the stage's barrier.
+  // Returns the validity mask of the pair's 32 tokens (an out-of-range page is reported and masked).
+  auto tma_issue_pair = [&](uint32_t st, int pos, int ba, int bb, bool two) -> uint32_t {
+    const uint32_t nblk = (uint32_t)a.num_blocks;
+    uint32_t okm = 0xFFFFFFFFu;
+    if ((uint32_t)ba >= nblk || (two && (uint32_t)bb >= nblk)) {  // rare: report, mask the tile
+      okm = ((uint32_t)ba < nblk ? 0xFFFFu : 0u) | ((uint32_t)bb < nblk ? 0xFFFF0000u : 0u);
+      if (a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+    }
+    const uint32_t sb = ring + st * (2 * kStage), bar = bar0 + st * 8;
+    const int bs_mask = a.block_size - 1;  // power of two (checked by the host)
+    const int in_a = pos & bs_mask, in_b = (pos + kTileTokens) & bs_mask;
+    if (elect_one()) {
+      mbar_expect_tx(bar, two ? 2 * kTmaStage : kTmaStage);
+      if (MERGED) {
+        tma_load_4d(sb, &tm_data, x_k, in_a, 0, ba, bar);
+        tma_load_4d(sb + kTmaKN, &tm_norm, x_kn, in_a, 0, ba, bar);
+        if (two) {
+          tma_load_4d(sb + kStage, &tm_data, x_k, in_b, 0, bb, bar);
+          tma_load_4d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, 0, bb, bar);
+        }
+      } else if (ROWBOX) {  // one box per tile: the 16 whole token rows of the only KV head
+        tma_load_3d(sb, &tm_data, 0, in_a, ba, bar);
+        if (two) tma_load_3d(sb + kStage, &tm_data, 0, in_b, bb, bar);
+      } else {
+        tma_load_3d(sb, &tm_data, x_k, in_a, ba, bar);
+        tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_a, ba, bar);
+        tma_load_3d(sb + kTmaKN, &tm_norm, x_kn, in_a, ba, bar);
+        tma_load_3d(sb + kTmaVN, &tm_norm, x_vn, in_a, ba, bar);
+        if (two) {
+          tma_load_3d(sb + kStage, &tm_data, x_k, in_b, bb, bar);
+          tma_load_3d(sb + kStage + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_b, bb, bar);
+          tma_load_3d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, bb, bar);
+          tma_load_3d(sb + kStage + kTmaVN, &tm_norm, x_vn, in_b, bb, bar);
+        }
+      }
+    }
+    return okm;
+  };
+
+  // this warp's ring barriers (used by this warp only: warp-level ordering is enough)
+  if (TMA && lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&s_bar[warp][s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+
+  // ---- plan state of the warp: its span and the row it is in ---------------------------------------
+  int total = 0, tps = 1, t_begin = 0, t_end = 0;
+  int r = 0;               // current row
+  int f_t0 = 0, f_slot = 0;  // fused plan: first tile and first partial slot of row r
+  bool pre_issued = false;   // fused plan: the first tile pair of the span is already in flight
+  uint32_t pre_ok = 0xFFFFFFFFu;
+  bool pre_can = false, pre_two = false;  // ... its position and page ids, fetched ahead of the issue
+  int pre_pos = 0, pre_ba = 0, pre_bb = 0;
+
+  // ---- fused prologue: tile plan, query rotation and the step's cache write ------------------------
+  if (a.fused) {
+    if constexpr (D <= 128) {
+      const int n_warps = blockDim.x >> 5;
+      const bool pi_one_batch = D * D / 4 <= kPiBatch * (int)blockDim.x;
+      float4 pi_regs[kPiBatch];
+      if (pi_one_batch) pi_load<D>(a.rotation, pi_regs);  // in flight while the plan is computed
+      const WarpPlan wp = fused_plan(a, warp, n_warps, lane, span, cta * sh.TPC, sh.TPC);
+      total = wp.total;
+      tps = wp.tps;
+      t_begin = (int)min((long long)span * tps, (long long)total);
+      t_end = min(total, t_begin + tps);
+      r = max(wp.r0, 0);
+      f_t0 = wp.r0_t0;
+      f_slot = wp.r0_slot;
+      TQ4_STAMP(1);
+      if constexpr (TMA) {
+        // page ids of the span's first tile pair: fetched now, used after the rotation (the copies go
+        // into the ring memory that stages the rotation's operands until then)
+        if (t_begin < t_end && wp.r0 >= 0 && bs_shift >= 0) {
+          int seq, kv_start, kv_end;
+          decode_row_range(a, r, seq, kv_start, kv_end);
+          const int seg_end = min(f_t0 + row_tiles(kv_start, kv_end), t_end);
+          const int tile0 = kv_start / kTileTokens;
+          const int last_pos = (tile0 + (seg_end - 1 - f_t0)) * kTileTokens;
+          const int32_t* bt = a.block_table + (int64_t)seq * a.bt_stride;
+          pre_pos = (tile0 + (t_begin - f_t0)) * kTileTokens;
+          pre_two = pre_pos + kTileTokens <= last_pos;
+          pre_ba = __ldg(bt + (pre_pos >> bs_shift));
+          pre_bb = __ldg(bt + (min(pre_pos + kTileTokens, last_pos) >> bs_shift));
+          pre_can = true;
+        }
+      }
+      static_assert(GroupMem<D>::kBytes <= (int)kRing, "a group of 16 staged vectors fits a warp's ring memory");
+      if (pi_one_batch) pi_store<D>(pi_regs, tab);
+      else stage_rotation_split<D>(a.rotation, tab);
+      if (has_write && threadIdx.x < 32) {  // sorted boundaries of K and V, padded with +inf
+        const int src = threadIdx.x >> 4, i = threadIdx.x & 15;
+        s_cent[src][i] = i < w.n_bounds[src] ? w.bounds[src][i] : CUDART_INF_F;
+      }
+      RotRows rr;
+      rr.r_a = wp.r_a;
+      rr.r_b = wp.r_b;
+      rr.rb_ends = wp.rb_ends;
+      {
+        const int vh0 = slice * sh.HPC, vh1 = vh0 + sh.HPC - 1, c1 = vh1 % sh.NCH;
+        rr.h0 = (vh0 / sh.NCH) * sh.G + (vh0 % sh.NCH) * sh.GC;
+        rr.nh = (vh1 / sh.NCH) * sh.G + c1 * sh.GC + min(sh.GC, sh.G - c1 * sh.GC) - rr.h0;
+        rr.kvh0 = vh0 / sh.NCH;
+        rr.nkv = vh1 / sh.NCH - rr.kvh0 + 1;
+      }
+      const int n_rows = (wp.r_a >= 0 && wp.r_b >= wp.r_a) ? wp.r_b - wp.r_a + 1 : 0;
+      rr.n_q = n_rows * rr.nh;
+      rr.n_vec = rr.n_q + (has_write ? n_rows * 2 * rr.nkv : 0);
+      const int n_groups = (rr.n_vec + 15) >> 4;
+      auto ring_of = [&](int wi) -> uint32_t {
+        return wi < (int)n_a ? base + wi * kRing : tab + kTableBytes + (wi - n_a) * kRing;
+      };
+#pragma unroll 1
+      for (int g0 = 0; g0 == 0 || g0 < n_groups; g0 += n_warps) {  // (n_groups is the same in every warp of the CTA)
+        if (g0 + warp < n_groups) fused_prep_group<D>(a, w, has_write != 0, rr, g0 + warp, ring, lane);
+        __syncthreads();  // Pi and the round's groups are staged
+        if (g0 == 0) TQ4_STAMP(2);
+        const int n_round = min(n_warps, n_groups - g0);
+#pragma unroll 1
+        for (int t_ = warp; t_ < n_round * RotCfg<D>::NQ; t_ += n_warps)
+          fused_mma_task<D>(a, w, &s_cent[0][0], tab, ring_of(t_ / RotCfg<D>::NQ), t_ % RotCfg<D>::NQ, lane);
+        if (g0 + n_warps < n_groups) __syncthreads();  // the rings are staged again by the next round
+      }
+      TQ4_STAMP(10);
+      // the written cache rows are read back by bulk tensor copies (async proxy) after the barrier
+      if (has_write) asm volatile("fence.proxy.async.global;" ::: "memory");
+      TQ4_STAMP(11);
+    }
+    __syncthreads();  // rotated queries and written tokens are visible to the block; the table region is free
+    TQ4_STAMP(3);
+    if constexpr (TMA) {
+      // the first tile pair goes into flight now and lands while the table is built
+      if (pre_can) {
+        pre_ok = tma_issue_pair(0, pre_pos, pre_ba, pre_bb, pre_two);
+        pre_issued = true;
+      }
+    }
+  }
+  // ---- replicated byte -> half2 tables: slot l < 32 = K table of lane l, slot 32 + l = V -------
+  if (threadIdx.x < 2 * TQ4_MAX_CENTROIDS) {
+    const int w_ = threadIdx.x >> 4, i = threadIdx.x & 15;
+    const float* cent = w_ ? a.v_centroids : a.k_centroids;
+    const int nc = w_ ? a.n_v_centroids : a.n_k_centroids;
+    s_cent[w_][i] = i < nc ? __fmul_rn(w_ ? a.lut_scale_v : a.lut_scale_k, cent[i]) : 0.f;
+  }
+  __syncthreads();
+  {
+    // the 32 lane copies of an entry are contiguous: four per 16-byte store
+    uint4* t = reinterpret_cast<uint4*>(smem_raw + (tab - base));
+    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
+      const int byte = i >> 4, w_ = (i >> 3) & 1;
+      const uint32_t v = pack_h2(s_cent[w_][byte >> 4], s_cent[w_][byte & 15]);
+      t[i] = make_uint4(v, v, v, v);
+    }
+  }
+  __syncthreads();
+  // everything above used only caller inputs and shared memory (a launch with the fused prologue is
+  // a plain one); without it the kernel now reads the plan and the rotated queries of the prologue
+  // kernel and the cache the write kernel filled
+  pdl_trigger();
+  pdl_wait();
+  TQ4_STAMP(4);
+  if (!a.fused) {
+    total = p.scalars[0];
+    tps = p.scalars[1];
+    t_begin = (int)min((long long)span * tps, (long long)total);
+    t_end = min(total, t_begin + tps);
+  }
+  if (t_begin >= t_end) return;
+
   // first row of the span: the largest r with tile_prefix[r] <= t_begin (the array is
   // non-decreasing).  Two levels of 32-way search: two dependent memory round trips instead of
   // log2(rows) of a binary search.
-  int r;
-  {
+  if (!a.fused) {
     const int rows = sh.rows;
     const int stride = (rows + 31) / 32;
     const int v1 = __ldg(p.tile_prefix + min(lane * stride, rows));
@@ -796,10 +1008,20 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
 
   int t = t_begin;
   while (t < t_end) {
-    const int row_t0 = p.tile_prefix[r], row_t1 = p.tile_prefix[r + 1];
+    int row_t0, row_t1, kv_start, kv_end, row_seq;
+    if (a.fused) {  // from the sequence length: the plan arrays are not read back
+      decode_row_range(a, r, row_seq, kv_start, kv_end);
+      row_t0 = f_t0;
+      row_t1 = f_t0 + row_tiles(kv_start, kv_end);
+    } else {
+      row_t0 = p.tile_prefix[r];
+      row_t1 = p.tile_prefix[r + 1];
+      kv_start = p.kv_start[r];
+      kv_end = p.kv_end[r];
+      row_seq = p.row_seq[r];
+    }
     const int seg_end = min(row_t1, t_end);
-    const int kv_start = p.kv_start[r], kv_end = p.kv_end[r];
-    const int32_t* bt = a.block_table + (int64_t)p.row_seq[r] * a.bt_stride;
+    const int32_t* bt = a.block_table + (int64_t)row_seq * a.bt_stride;
     const int tile0 = kv_start / kTileTokens;
 
     // ---- query fragments: column g of n-block nb = head nb*4 + g/2, term g%2 (hi / lo) ------
@@ -1148,50 +1370,16 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
       if (n_pairs > 0) {
         const int step_tok = step * kTileTokens;
         const int last_pos = pos0_of(seg_end - 1);  // first token of the segment's last tile
-        const uint32_t nblk = (uint32_t)a.num_blocks;
-        const int bs_mask = a.block_size - 1;  // power of two (checked by the host)
         auto load_blk = [&](int pos) -> int { return __ldg(bt + (min(pos, last_pos) >> bs_shift)); };
         auto issue = [&](uint32_t st, int pos, int ba, int bb) -> uint32_t {
-          const bool two = pos + kTileTokens <= last_pos;
-          uint32_t okm = 0xFFFFFFFFu;
-          if ((uint32_t)ba >= nblk || (two && (uint32_t)bb >= nblk)) {  // rare: report, mask the tile
-            okm = ((uint32_t)ba < nblk ? 0xFFFFu : 0u) | ((uint32_t)bb < nblk ? 0xFFFF0000u : 0u);
-            if (a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
-          }
-          const uint32_t sb = ring + st * (2 * kStage), bar = bar0 + st * 8;
-          const int in_a = pos & bs_mask, in_b = (pos + kTileTokens) & bs_mask;
-          if (elect_one()) {
-            mbar_expect_tx(bar, two ? 2 * kTmaStage : kTmaStage);
-            if (MERGED) {
-              tma_load_4d(sb, &tm_data, x_k, in_a, 0, ba, bar);
-              tma_load_4d(sb + kTmaKN, &tm_norm, x_kn, in_a, 0, ba, bar);
-              if (two) {
-                tma_load_4d(sb + kStage, &tm_data, x_k, in_b, 0, bb, bar);
-                tma_load_4d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, 0, bb, bar);
-              }
-            } else if (ROWBOX) {  // one box per tile: the 16 whole token rows of the only KV head
-              tma_load_3d(sb, &tm_data, 0, in_a, ba, bar);
-              if (two) tma_load_3d(sb + kStage, &tm_data, 0, in_b, bb, bar);
-            } else {
-              tma_load_3d(sb, &tm_data, x_k, in_a, ba, bar);
-              tma_load_3d(sb + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_a, ba, bar);
-              tma_load_3d(sb + kTmaKN, &tm_norm, x_kn, in_a, ba, bar);
-              tma_load_3d(sb + kTmaVN, &tm_norm, x_vn, in_a, ba, bar);
-              if (two) {
-                tma_load_3d(sb + kStage, &tm_data, x_k, in_b, bb, bar);
-                tma_load_3d(sb + kStage + C::kTmaV, VWIDE ? &tm_v : &tm_data, x_v, in_b, bb, bar);
-                tma_load_3d(sb + kStage + kTmaKN, &tm_norm, x_kn, in_b, bb, bar);
-                tma_load_3d(sb + kStage + kTmaVN, &tm_norm, x_vn, in_b, bb, bar);
-              }
-            }
-          }
-          return okm;
+          return tma_issue_pair(st, pos, ba, bb, pos + kTileTokens <= last_pos);
         };
         uint32_t st = gk & 1u, ph = (gk >> 1) & 1u;  // stage and barrier parity of the current pair
         int pos_i = pos0_of(first), pos_c = pos_i;
         int blk_a = load_blk(pos_i), blk_b = load_blk(pos_i + kTileTokens);
         __syncwarp();
-        uint32_t ok_cur = issue(st, pos_i, blk_a, blk_b);
+        uint32_t ok_cur = pre_issued ? pre_ok : issue(st, pos_i, blk_a, blk_b);  // (pre-issued: stage 0, gk == 0)
+        pre_issued = false;
         pos_i += step_tok;
         blk_a = load_blk(pos_i);
         blk_b = load_blk(pos_i + kTileTokens);
@@ -1307,7 +1495,7 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
 
     TQ4_STAMP(6);
     // ---- write this warp's partial for the segment ---------------------------------------------
-    const int slot = p.slot_base[r] + (span - row_t0 / tps);
+    const int slot = (a.fused ? f_slot : p.slot_base[r]) + (span - row_t0 / tps);
     const int64_t pidx = slot;
     const float inv_av = 1.f / a.lut_scale_v;
 #pragma unroll
@@ -1334,8 +1522,18 @@ attention_mma_kernel(const AttnArgs a, const CompressArgs w, const int has_write
     }
     t = seg_end;
     if (t < t_end) {
-      ++r;
-      while (p.tile_prefix[r + 1] <= t) ++r;
+      if (a.fused) {  // next row that has tiles; its first tile and first partial slot follow from this row's
+        f_slot += (row_t1 - 1) / tps - row_t0 / tps + 1;
+        f_t0 = row_t1;
+        for (++r; r < sh.rows - 1; ++r) {
+          int sq, st_, en_;
+          decode_row_range(a, r, sq, st_, en_);
+          if (en_ > st_) break;
+        }
+      } else {
+        ++r;
+        while (p.tile_prefix[r + 1] <= t) ++r;
+      }
     }
   }
   TQ4_STAMP(7);
@@ -1523,9 +1721,9 @@ bool attention_mma_supported(const AttnShape& sh, int block_size, const uint8_t*
 
 #ifdef TQ4_TRACE
 }  // namespace tq4
-// Copies the 160 x 16 x 8 timeline stamps of the last launch to the host (tuning builds only).
+// Copies the 160 x 16 x 16 timeline stamps of the last launch to the host (tuning builds only).
 extern "C" int tq4_trace_read(long long* out) {
-  return cudaMemcpyFromSymbol(out, tq4::g_trace, sizeof(long long) * 160 * 16 * 8) == cudaSuccess ? 0 : 1;
+  return cudaMemcpyFromSymbol(out, tq4::g_trace, sizeof(long long) * 160 * 16 * 16) == cudaSuccess ? 0 : 1;
 }
 namespace tq4 {
 #endif

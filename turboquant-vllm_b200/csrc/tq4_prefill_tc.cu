@@ -145,8 +145,11 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// G = query heads per KV head (1, 2, 4 or 8); a block holds RB = 128 / G query rows
-template <int G>
+// G = query heads per KV head (1, 2, 4 or 8); a block holds RB = 128 / G query rows.
+// FAST: the queries and the probabilities enter the MMAs as ONE fp16 term each instead of hi + lo
+// (half the tensor work and no remainder arithmetic; their rounding, 2^-11 relative, then reaches
+// the output: about 1e-3 absolute instead of 1e-5).
+template <int G, bool FAST>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
                   const __grid_constant__ CUtensorMap tm_norm) {
@@ -251,7 +254,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       }
       const uint32_t off = (uint32_t)kb * 16384u + swz(m, c);
       *reinterpret_cast<uint4*>(sm + kOffQhi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      *reinterpret_cast<uint4*>(sm + kOffQlo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      if (!FAST) *reinterpret_cast<uint4*>(sm + kOffQlo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
     // hand qmax of row m to the thread that owns TMEM lane m (thread m): through the norm scratch
     if (kb == 0) reinterpret_cast<float*>(sm + kOffP)[m] = qmax * (a.scale_log2e / a.lut_scale_k);
@@ -352,8 +355,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       for (int s = 0; s < 4; ++s) {
         const uint64_t db = dk + (uint64_t)((kb * 8192 + 32 * s) >> 4);
         const uint64_t qo = (uint64_t)((kb * 16384 + 32 * s) >> 4);
-        mma_f16(tmem + kColS + 64 * (j & 1), d_qlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
-        mma_f16(tmem + kColS + 64 * (j & 1), d_qhi + qo, db, kDescS, 1u);
+        if (!FAST) mma_f16(tmem + kColS + 64 * (j & 1), d_qlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
+        mma_f16(tmem + kColS + 64 * (j & 1), d_qhi + qo, db, kDescS, (FAST && !(kb | s)) ? 0u : 1u);
       }
     mma_commit(bar_s0 + 8 * (j & 1));  // one barrier per S buffer: a waiter can never be two phases behind
   };
@@ -487,10 +490,10 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
           const __half2 hp = __floats2half2_rn(v0, v1);
           const float2 hf2 = __half22float2(hp);
           h[e] = *reinterpret_cast<const uint32_t*>(&hp);
-          lw[e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
+          if (!FAST) lw[e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
         }
         *reinterpret_cast<uint4*>(sm + kOffP + swz(row, 4 * hf + c)) = make_uint4(h[0], h[1], h[2], h[3]);
-        *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        if (!FAST) *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
       }
       l_run += lsum;  // (this thread's half of the row sum)
       // the values of tile j + 1 (only O += P V~ of the next iteration reads them): its buffer was freed
@@ -511,8 +514,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         const uint64_t dv = dvb + (uint64_t)((2048 * s) >> 4);
-        mma_f16(tmem + kColO, d_plo + (uint64_t)((32 * s) >> 4), dv, kDescO, (!o_zero || s) ? 1u : 0u);
-        mma_f16(tmem + kColO, d_p + (uint64_t)((32 * s) >> 4), dv, kDescO, 1u);
+        if (!FAST) mma_f16(tmem + kColO, d_plo + (uint64_t)((32 * s) >> 4), dv, kDescO, (!o_zero || s) ? 1u : 0u);
+        mma_f16(tmem + kColO, d_p + (uint64_t)((32 * s) >> 4), dv, kDescO, (FAST && o_zero && !s) ? 0u : 1u);
       }
       mma_commit(bar_o);
       // the packed stage of tile j was dequantised one iteration ago: refill it with tile j + 2
@@ -596,17 +599,17 @@ bool make_map(CUtensorMap* m, const AttnArgs& a, uint32_t box_bytes) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int G>
+template <int G, bool FAST>
 int launch_t(const AttnArgs& a, cudaStream_t st) {
   const int smem = (int)kSmemBytes + 1024;
-  if (!ensure_dynamic_smem<prefill_tc_kernel<G>>(smem)) return TQ4_ERR_CUDA;
+  if (!ensure_dynamic_smem<prefill_tc_kernel<G, FAST>>(smem)) return TQ4_ERR_CUDA;
   CUtensorMap tm_idx, tm_norm;
   memset(&tm_idx, 0, sizeof(tm_idx));
   memset(&tm_norm, 0, sizeof(tm_norm));
   if (!make_map(&tm_idx, a, 64) || !make_map(&tm_norm, a, 16)) return TQ4_ERR_UNSUPPORTED;
   constexpr int RB = 128 / G;
   const unsigned blocks = (unsigned)((a.sh.rows + RB - 1) / RB + a.sh.num_seqs);  // upper bound
-  if (launch_kernel(prefill_tc_kernel<G>, dim3(blocks, (unsigned)a.sh.Hkv), dim3(kThreads), (size_t)smem, st,
+  if (launch_kernel(prefill_tc_kernel<G, FAST>, dim3(blocks, (unsigned)a.sh.Hkv), dim3(kThreads), (size_t)smem, st,
                     true, a, tm_idx, tm_norm) != cudaSuccess)
     return TQ4_ERR_CUDA;
   TQ4_CHECK_LAUNCH();
@@ -626,12 +629,12 @@ bool prefill_tc_supported(const AttnArgs& a) {
          lay.v_idx % 16 == 0 && a.num_blocks < (1ll << 31) && encode_fn() != nullptr;
 }
 
-int launch_prefill_tc(const AttnArgs& a, cudaStream_t st) {
+int launch_prefill_tc(const AttnArgs& a, cudaStream_t st, bool fast) {
   switch (a.sh.G) {
-    case 1: return launch_t<1>(a, st);
-    case 2: return launch_t<2>(a, st);
-    case 4: return launch_t<4>(a, st);
-    case 8: return launch_t<8>(a, st);
+    case 1: return fast ? launch_t<1, true>(a, st) : launch_t<1, false>(a, st);
+    case 2: return fast ? launch_t<2, true>(a, st) : launch_t<2, false>(a, st);
+    case 4: return fast ? launch_t<4, true>(a, st) : launch_t<4, false>(a, st);
+    case 8: return fast ? launch_t<8, true>(a, st) : launch_t<8, false>(a, st);
   }
   return TQ4_ERR_UNSUPPORTED;
 }

@@ -282,7 +282,8 @@ def paged_tq4_attention(
     ``query_start_loc=None``: decode, row i is the one new token of sequence i.  Otherwise
     int32 ``[num_seqs + 1]`` offsets of each sequence's query chunk (bottom-right aligned
     causal mask).  ``mode``: 0 auto, 1 fp32 CUDA-core kernel, 2 streaming tensor-core LUT kernel,
-    3 chunked-prefill tcgen05 kernel (head_dim 128 only).
+    3 chunked-prefill tcgen05 kernel (head_dim 128 only), 4 the same with single fp16 terms for
+    queries and probabilities (faster, about 1e-3 absolute error; never picked automatically).
     """
     nv.require_cuda(q, kv_cache, block_table, seq_lens, k_centroids, v_centroids, rotation)
     t, hq, d = q.shape
