@@ -16,7 +16,10 @@
  *   - `err_flag` (optional, may be NULL) is a device int that kernels OR with a
  *     TQ4_DEV_* bit when they meet an out-of-range slot / block id; the offending access
  *     is skipped, never performed;
- *   - the library is stateless and thread-compatible (the caller serialises per stream).
+ *   - the library keeps no state between calls except per-device lookups it makes once (kernel
+ *     attributes, SM count, the address of the built-in scratch), so one process may drive several
+ *     GPUs: make the device of the tensors current before a call.  It is thread-compatible (the
+ *     caller serialises per stream).
  *
  * Each entry point cites the interface of the reference project (turboquant-vllm v1.5.0,
  * paths relative to its root) that it replaces.
@@ -44,7 +47,8 @@ typedef enum {
 
 /* bits OR-ed into *err_flag by kernels */
 #define TQ4_DEV_BAD_SLOT 1  /* slot_mapping entry >= num_cache_slots            */
-#define TQ4_DEV_BAD_BLOCK 2 /* block_table entry outside [0, num_blocks)         */
+#define TQ4_DEV_BAD_BLOCK 2 /* block_table entry outside [0, num_blocks), or a seq_len beyond the
+                               bt_stride * block_size tokens a block-table row can address (cut there) */
 #define TQ4_DEV_TIMEOUT 4   /* a bounded device-side wait gave up                */
 #define TQ4_DEV_WRITE_ORDER 8 /* tq4_write_and_attention: a new token's slot is not the last position of its
                                  sequence; it was written, but this call's attention may not have seen it */
@@ -57,6 +61,12 @@ const char* tq4_status_string(int status);
 /*
  * Compress rows:  x[(n,h), 0:D]  ->  packed[(n,h), 0:D/2] (u8), norms[(n,h)] (f32).
  * norm = ||x||_2 (fp32); y = (x / (norm + 1e-10)) * Pi^T; idx = #{b : b < y}; nibble pack.
+ * Exactness: given the same rotated coordinates y the bytes are bit-exact (tq4_pack_rotated_rows);
+ * end to end a coordinate within ~1e-7 of a boundary may land in the neighbouring bucket, because
+ * the rotation's summation order differs from the reference's matmul: at most 1e-4 of the indices
+ * (measured 6e-7 on the FFMA kernels, 5e-7 on the tensor-core kernels that take inputs of more
+ * than 8192 vectors at head_dim 128; setting TQ4_NO_TC in the environment keeps every input on the
+ * FFMA kernels).  Norms are within 3 ulp of a CPU torch.norm and identical across all kernels here.
  * Replaces: tq4_compress() + _tq4_compress_kernel, src/turboquant_vllm/triton/tq4_compress.py:46-148,173-245
  *           (arithmetic contract = its PyTorch path, :248-295 / quantizer.py:112-151).
  * rot_t_even / rot_t_odd: [D, D/2] fp32, the even / odd columns of Pi^T (same split as the

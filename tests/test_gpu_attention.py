@@ -178,6 +178,27 @@ def test_prefill_tensor_core_kernel(ops, hq, hkv, bs, vbits):
         _check(out, ref)
 
 
+@pytest.mark.parametrize("mode", MODES)
+def test_seq_len_beyond_block_table_row_is_cut_and_flagged(ops, mode):
+    """A seq_len that needs more pages than a block-table row holds is cut at the row's capacity and
+    reported (TQ4_DEV_BAD_BLOCK); nothing is read past the row."""
+    pr = Prims(128)
+    p = pr.cuda()
+    h_kv, h_q, bs = 8, 32, 16
+    case = build_paged_case([48, 20], h_kv, 128, bs, pr, seed=31, padded=True)
+    bt = case["block_table"][:, :2].contiguous().cuda()  # rows of two pages: 32 tokens at most
+    q = torch.randn(2, h_q, 128, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    kw = dict(q=q, kv_cache=case["cache"].cuda(), block_table=bt, k_centroids=p["kc"], v_centroids=p["vc"],
+              rotation=p["rot"], num_kv_heads=h_kv, block_size=bs, out_dtype=torch.float32)
+    ops.read_and_clear_errors(q.device)
+    want = _run(ops, mode, seq_lens=torch.tensor([32, 20], dtype=torch.int32).cuda(), **kw)
+    assert ops.read_and_clear_errors(q.device) == 0
+    got = _run(ops, mode, seq_lens=torch.tensor([48, 20], dtype=torch.int32).cuda(), **kw)
+    torch.cuda.synchronize()
+    assert ops.read_and_clear_errors(q.device) == 2
+    assert torch.equal(got, want)
+
+
 def test_prefill_tensor_core_fast_mode(ops):
     """Mode 4, the tcgen05 prefill kernel with single fp16 terms for queries and probabilities: their
     2^-11 rounding reaches the output: it does NOT meet the 2e-3 max-abs bound of the parity gate

@@ -33,7 +33,7 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
     if (a.query_start_loc == nullptr) {
       seq = gr;
       if (seq < sh.num_seqs) {
-        const int len = max(0, a.seq_lens[seq]);
+        const int len = clamp_seq_len(a, max(0, a.seq_lens[seq]));
         end = len;
         start = a.sliding_window > 0 ? max(0, len - a.sliding_window) : 0;
       } else {
@@ -49,7 +49,7 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
       seq = lo;
       if (seq < sh.num_seqs && gr < a.query_start_loc[sh.num_seqs]) {
         const int q0 = a.query_start_loc[seq], q1 = a.query_start_loc[seq + 1];
-        const int len = max(0, a.seq_lens[seq]);
+        const int len = clamp_seq_len(a, max(0, a.seq_lens[seq]));
         const int pos = len - (q1 - q0) + (gr - q0);
         end = a.causal ? pos + 1 : len;
         end = max(0, min(end, len));

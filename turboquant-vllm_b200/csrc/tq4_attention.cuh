@@ -84,6 +84,18 @@ struct AttnArgs {
   const CompressArgs* fused_write;  // host side only: the step's cache write, done inside the fused kernel
 };
 
+// A sequence cannot be longer than its block-table row (the C interface carries the row stride, not
+// the row's width: the stride bounds it).  A longer seq_len is cut there and reported, so no kernel
+// reads a page id past the row.
+__device__ __forceinline__ int clamp_seq_len(const AttnArgs& a, int len) {
+  const long long cap = (long long)a.bt_stride * a.block_size;
+  if ((long long)len > cap) {
+    if (a.err_flag) atomicOr(a.err_flag, TQ4_DEV_BAD_BLOCK);
+    len = (int)cap;
+  }
+  return len;
+}
+
 inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
 
 // Split Hq query heads over warps: a VIRTUAL head is one KV head plus up to 8 of its query

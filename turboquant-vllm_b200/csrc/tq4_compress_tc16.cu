@@ -11,14 +11,18 @@
 // boundary (bound 1e-4 of the indices).  Norms are summed in exactly the order of the FMA kernels
 // (lane-strided FMAs, butterfly tree), so they are bit-identical to them.
 //
-// One persistent CTA per SM, warp-specialised, three input stages and two accumulators in flight:
+// One persistent CTA per SM, warp-specialised, four input stages and four accumulators in flight:
 //   warp 0      TMA producer: the 128 rows of a tile as two 64-column boxes (128-byte swizzle)
 //   warp 1      MMA issuer: 8 k-steps x terms of tcgen05.mma 128x128x16, then tcgen05.commit onto
 //               the stage's "empty" barrier and the accumulator's "full" barrier
-//   warps 2-5   epilogue group 0 (even tiles of the CTA), warps 6-9 epilogue group 1 (odd tiles):
+//   warps 2-17  four epilogue groups of four warps; tile i of the CTA belongs to group i % 4 and uses
+//               input stage i % 4 and accumulator i % 4, so every barrier is waited on by one group
+//               in tile order (a stage shared between groups could show a fast group an older
+//               phase).  The epilogue is CUDA-core work; four warps per scheduler hide its latencies:
 //               thread = row.  Sum of squares from the staged tile -> release the stage -> wait for
-//               the accumulator -> tcgen05.ld 4 x 32 columns -> scale, bucketize (binary search),
-//               nibble-pack -> 16-byte stores into the packed output or the paged cache row.
+//               the accumulator -> four times: tcgen05.ld of 32 columns, scale, bucketize (binary
+//               search over boundaries held in registers), nibble-pack, one 16-byte store into the
+//               packed output or the paged cache row.
 // Every mbarrier wait is bounded; a wait that gives up marks the CTA dead, all roles drain and the
 // kernel reports TQ4_DEV_TIMEOUT.  Tensor memory is released on every path.
 #include <cuda.h>
@@ -35,18 +39,16 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kRows = 128;                       // vectors per tile (MMA M, TMEM lanes)
-constexpr int kStages = 3;                       // input tiles in flight
-constexpr int kAccs = 2;                         // accumulators (one per epilogue group)
-constexpr int kThreads = 320;                    // producer, issuer, 2 x 4 epilogue warps
+constexpr int kStages = 4;                       // input stages = epilogue groups = accumulators
+constexpr int kAccs = kStages;                   // tile i of a CTA uses stage, accumulator and group i % 4
+constexpr int kThreads = 64 + kAccs * 128;       // producer, issuer, kAccs x 4 epilogue warps
 constexpr uint32_t kBlockBytes = kRows * 128;    // one K-block (64 16-bit columns) of an operand: 16 KB
 constexpr uint32_t kTileBytes = 2 * kBlockBytes; // a tile = two K-blocks
 constexpr int kMaxTerms = 3;
 constexpr uint32_t kOffB = 0;                                  // terms x 2 K-blocks of Pi
 constexpr uint32_t kOffA = kMaxTerms * kTileBytes;             // stages x 2 K-blocks of X
-constexpr int kCells = 256, kCellCopies = 4;                   // bucketize table, see CellTable
-constexpr uint32_t kOffCells = kOffA + kStages * kTileBytes;
-constexpr uint32_t kSmemBytes = kOffCells + 2 * kCellCopies * kCells * 8;  // 192 KB + 16 KB
-constexpr uint32_t kTmemCols = 256;                            // two accumulators of 128 fp32 columns
+constexpr uint32_t kSmemBytes = kOffA + kStages * kTileBytes;  // 96 KB of Pi terms + 128 KB of input stages
+constexpr uint32_t kTmemCols = kAccs * 128;                    // one accumulator of 128 fp32 columns per group
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // byte offset of (row, 16-byte chunk c of the row's 128 bytes) inside a K-block (128-byte swizzle)
@@ -176,47 +178,6 @@ __device__ __forceinline__ int bucketize_reg(float y, const float (&b)[15]) {
   return (c1 ? 8 : 0) + (c2 ? 4 : 0) + (c3 ? 2 : 0) + (c4 ? 1 : 0);
 }
 
-// Bucketize by table.  The real line is cut into kCells uniform cells between the lowest and the
-// highest boundary; cell(y) = clamp(floor(y * scale + off)) is monotone in y, so every boundary in
-// a lower cell is below y and every boundary in a higher cell above it, and only a boundary in
-// y's own cell needs a comparison:  idx = base[cell] + (y > inner[cell]).  That is exact, costs one
-// 8-byte shared-memory load and six ALU instructions per coordinate (the register search: 19), and
-// needs cells finer than the closest pair of boundaries, which the builder checks (a codebook that
-// fails the check keeps the register search).  kCellCopies copies, one per lane & 3, thin out bank
-// conflicts.  Built in the kernel with the arithmetic the lookups use.
-struct CellParams {
-  float scale, off;
-  int ok;
-};
-__device__ __forceinline__ int cell_of(float y, float scale, float off) {
-  return min(max(__float2int_rd(fmaf(y, scale, off)), 0), kCells - 1);
-}
-// one warp builds the table of one source: float2 {inner boundary or +inf, base count (int bits)}
-__device__ __forceinline__ void build_cells(const float* b16, int nb, float2* tab, CellParams* prm, int lane) {
-  const float lo = nb > 0 ? b16[0] : 0.f, hi = nb > 0 ? b16[nb - 1] : 0.f;
-  const float scale = hi > lo ? (float)(kCells - 2) / (hi - lo) : 1.f;
-  const float off = 1.f - lo * scale;
-  bool ok = true;
-  for (int q = lane; q < kCells; q += 32) {
-    int base = 0, inside = 0;
-    float inner = CUDART_INF_F;
-    for (int i = 0; i < nb; ++i) {
-      const int cb = cell_of(b16[i], scale, off);
-      base += cb < q ? 1 : 0;
-      if (cb == q) { ++inside; inner = b16[i]; }
-    }
-    ok = ok && inside <= 1;
-#pragma unroll
-    for (int cpy = 0; cpy < kCellCopies; ++cpy) tab[cpy * kCells + q] = make_float2(inner, __int_as_float(base));
-  }
-  ok = __all_sync(0xffffffffu, ok);
-  if (lane == 0) {
-    prm->scale = scale;
-    prm->off = off;
-    prm->ok = ok ? 1 : 0;
-  }
-}
-
 struct Bars {
   uint64_t full[kStages];    // TMA -> consumers: the stage's tile has landed
   uint64_t empty[kStages];   // consumers -> TMA: MMAs (1 commit) and the norm readers (4 warps) are done with it
@@ -235,7 +196,6 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
   __shared__ uint32_t s_tmem;
   __shared__ int s_dead;
   __shared__ float s_bounds[2][16];
-  __shared__ CellParams s_cells[2];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   unsigned char* sm = smem_raw + (base - smem_addr(smem_raw));
@@ -275,9 +235,6 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
   // ---- Pi as the B operand: B[n = j][k = d] = Pi[j][d] in 16-bit terms, K-major, swizzled ---------
   // rot_even[k * 64 + p] = Pi[2p][k], rot_odd[k * 64 + p] = Pi[2p + 1][k], read from the staging area
   __syncthreads();  // the barrier is initialised, the copies are issued, the boundaries are in shared memory
-  if (warp >= 2 && warp < 2 + a.n_sources)
-    build_cells(s_bounds[warp - 2], a.n_bounds[warp - 2],
-                reinterpret_cast<float2*>(sm + kOffCells) + (warp - 2) * kCellCopies * kCells, &s_cells[warp - 2], lane);
   const bool pi_ok = bar_wait_bounded(smem_addr(&s_bars.pi), 0u, &s_dead);
   const float* raw = reinterpret_cast<const float*>(sm + kOffA);
   for (int i = tid; i < kD * (kD / 8); i += kThreads) {
@@ -364,7 +321,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
     }
   } else {
     // ================= epilogue groups =================
-    const int grp = (warp - 2) >> 2;              // tiles i with i % 2 == grp, accumulator grp
+    const int grp = (warp - 2) >> 2;              // tiles i with i % kAccs == grp, accumulator grp
     const int quarter = warp & 3;                 // the 32 TMEM lanes this warp may read
     const int row_in_tile = 32 * quarter + lane;
     const RowLayout lay = row_layout(a.num_heads, kD);
@@ -406,50 +363,13 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       if (lane == 0) bar_arrive(smem_addr(&s_bars.empty[st]));  // this warp is done with the staged rows
       // one IEEE division per row; Y_raw * (1 / den) is within an ulp of Y_raw / den
       const float scale = (1.f / (nrm + 1e-10f)) * (1.f / F::kScale);
-
-      ok = __all_sync(0xffffffffu, bar_wait_bounded(smem_addr(&s_bars.tfull[acc]), (uint32_t)((i / kAccs) & 1), dead));
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t packed[16];  // 128 indices = 64 bytes
-      float b[15];
-#pragma unroll
-      for (int i = 0; i < 15; ++i) b[i] = s_bounds[src][i];
-      const float c_scale = s_cells[src].scale, c_off = s_cells[src].off;
-      const bool by_table = s_cells[src].ok != 0;
-      const float2* cells = reinterpret_cast<const float2*>(sm + kOffCells) + (src * kCellCopies + (lane & 3)) * kCells;
-      auto bucket = [&](float y) -> int {
-        if (by_table) {
-          const float2 e = cells[cell_of(y, c_scale, c_off)];
-          return __float_as_int(e.y) + (y > e.x ? 1 : 0);
-        }
-        return bucketize_reg(y, b);
-      };
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(acc * kD + 32 * q), v);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {  // 8 coordinates -> 4 bytes -> one word
-          uint32_t word = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int ie = bucket(__uint_as_float(v[8 * w + 2 * e]) * scale);
-            const int io = bucket(__uint_as_float(v[8 * w + 2 * e + 1]) * scale);
-            word |= (uint32_t)((ie << 4) | io) << (8 * e);
-          }
-          packed[4 * q + w] = word;
-        }
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) bar_arrive(smem_addr(&s_bars.tempty[acc]));  // the accumulator may be overwritten
+      // where this row goes (resolved before the accumulator is read: the loads overlap the wait)
+      uint8_t* dst_idx = nullptr;
+      float* dst_norm = nullptr;
       if (live) {
-        const int64_t row = (int64_t)src * rows_per_src + in_src;
         const unsigned rem = (unsigned)in_src;
         const unsigned tok = rem / (unsigned)a.num_heads;
         const int h = (int)(rem - tok * (unsigned)a.num_heads);
-        uint8_t* dst_idx = nullptr;
-        float* dst_norm = nullptr;
         if (a.cache != nullptr) {
           const int64_t slot = (int64_t)tok < a.n_slots ? a.slot_mapping[tok] : -1;
           if (slot >= a.num_cache_slots) {
@@ -460,22 +380,47 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
             dst_norm = reinterpret_cast<float*>(rowp + (src == 0 ? lay.k_norm : lay.v_norm) + h * 4);
           }
         } else {
+          const int64_t row = (int64_t)src * rows_per_src + in_src;
           dst_idx = a.packed_out + row * (kD / 2);
           dst_norm = a.norms_out + row;
         }
-        if (dst_idx) {
-          if (((uintptr_t)dst_idx & 15) == 0) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst_idx);
+      }
+      float b[15];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) d4[w] = make_uint4(packed[4 * w], packed[4 * w + 1], packed[4 * w + 2], packed[4 * w + 3]);
-          } else {  // rows are at least 4-byte aligned
-            uint32_t* d32 = reinterpret_cast<uint32_t*>(dst_idx);
+      for (int bi = 0; bi < 15; ++bi) b[bi] = s_bounds[src][bi];
+      const bool wide = dst_idx != nullptr && ((uintptr_t)dst_idx & 15) == 0;  // else rows are 4-byte aligned
+
+      ok = __all_sync(0xffffffffu, bar_wait_bounded(smem_addr(&s_bars.tfull[acc]), (uint32_t)((i / kAccs) & 1), dead));
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // four chunks of 32 coordinates -> 16 bytes each; the loop stays rolled so that its body (32
+      // register searches) fits the instruction cache
+#pragma unroll 1
+      for (int q = 0; q < 4; ++q) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(acc * kD + 32 * q), v);
+        uint32_t word[4];
 #pragma unroll
-            for (int w = 0; w < 16; ++w) d32[w] = packed[w];
+        for (int w = 0; w < 4; ++w) {  // 8 coordinates -> 4 bytes -> one word
+          word[w] = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ie = bucketize_reg(__uint_as_float(v[8 * w + 2 * e]) * scale, b);
+            const int io = bucketize_reg(__uint_as_float(v[8 * w + 2 * e + 1]) * scale, b);
+            word[w] |= (uint32_t)((ie << 4) | io) << (8 * e);
           }
-          *dst_norm = nrm;
+        }
+        if (wide) {
+          reinterpret_cast<uint4*>(dst_idx)[q] = make_uint4(word[0], word[1], word[2], word[3]);
+        } else if (dst_idx) {
+#pragma unroll
+          for (int w = 0; w < 4; ++w) reinterpret_cast<uint32_t*>(dst_idx)[4 * q + w] = word[w];
         }
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive(smem_addr(&s_bars.tempty[acc]));  // the accumulator may be overwritten
+      if (dst_norm) *dst_norm = nrm;
     }
   }
   if (!ok) {

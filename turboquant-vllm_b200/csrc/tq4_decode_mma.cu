@@ -346,7 +346,7 @@ __device__ __forceinline__ void decode_row_range(const AttnArgs& a, int r, int& 
   seq = 0; start = 0; end = 0;
   if (gr < a.sh.num_seqs) {
     seq = gr;
-    const int len = max(0, __ldg(a.seq_lens + gr));
+    const int len = clamp_seq_len(a, max(0, __ldg(a.seq_lens + gr)));
     end = len;
     start = a.sliding_window > 0 ? max(0, len - a.sliding_window) : 0;
   }
