@@ -188,8 +188,8 @@ int tq4_paged_attention(const void* q, int q_dtype, int64_t num_rows, int num_se
 
 /*
  * One decode step of a layer: tq4_write_paged of the new tokens followed by tq4_paged_attention,
- * with the cache write folded into the attention's first kernel (query rotation + tile plan), so
- * the step costs three launches instead of four.  Arguments are the union of the two calls
+ * with the cache write folded into the attention's first kernel, so the step costs two launches
+ * (decode) or three (other calls) instead of four.  Arguments are the union of the two calls
  * (same meaning and checks); the cache must be block-major contiguous
  * (cache_block_stride == block_size * cache_token_stride), which makes the flat slot
  * s = block * block_size + offset of slot_mapping address row s at cache + s * cache_token_stride.
