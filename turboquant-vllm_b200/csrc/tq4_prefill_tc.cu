@@ -13,9 +13,11 @@
 //   O += Plo V~ + Phi V~      (tcgen05.mma 128 x 128 x 16, V~ as an MN-major B operand)
 // At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
 // layout of one dense partial per row; the merge kernel un-rotates and stores them.
-// Warps 0-7 own the S / O rows, two threads per row (softmax, rescale, epilogue); warps 8-11
-// dequantise the next tile into the other K~ / V~ buffer meanwhile and one of their threads issues
-// the TMA copies and the MMAs.  Every wait is bounded.
+// Warps 0-7 own the S / O rows, two threads per row (softmax, rescale, epilogue); warps 8-15
+// dequantise the next tile into the other K~ / V~ buffer meanwhile (keys first, so that the next
+// scores can be issued early; then the values); one thread of warp 16 issues the TMA copies and the
+// MMAs (an MMA issue blocks while the tensor pipe's queue is full: a warp that also dequantises
+// would hold the others up at their barrier).  Every wait is bounded.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -25,11 +27,27 @@
 #include "tq4_attention.cuh"
 
 namespace tq4 {
+#ifdef TQ4_TRACE
+// Tuning builds only (-DTQ4_TRACE): the SM clock at points of the tile loop, for four warps of one
+// CTA, read back with tq4_prefill_trace_read.  Compiled out of the shipped library.
+__device__ long long g_ptrace[4][64][16];
+#define PF_STAMP(j, e)                                                                              \
+  do {                                                                                              \
+    if (blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (j) < 64 &&                             \
+        (warp == 0 || warp == 8 || warp == 15 || warp == 16))                                       \
+      g_ptrace[warp == 0 ? 0 : warp == 8 ? 1 : warp == 15 ? 2 : 3][j][e] = clock64();               \
+  } while (0)
+#else
+#define PF_STAMP(j, e) do {} while (0)
+#endif
 namespace {
 
 constexpr int kD = 128;
 constexpr int kBN = 64;                 // tokens per tile
-constexpr int kThreads = 384;             // warps 0-7: softmax (two threads per row), warps 8-11: dequantise, issue
+constexpr int kSmx = 256;                 // warps 0-7: softmax (two threads per row)
+constexpr int kDeq = 256;                 // warps 8-15: dequantise
+constexpr int kIssueWarp = (kSmx + kDeq) / 32;  // warp 16: issues the TMA copies and the MMAs
+constexpr int kThreads = kSmx + kDeq + 32;
 constexpr uint32_t kTmemCols = 256;     // S (two buffers): columns [0, 64) and [64, 128), O: columns [128, 256)
 constexpr uint32_t kColS = 0, kColO = 128;
 
@@ -119,14 +137,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
-      "%15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+      "%15, %16};"
       ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
-        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -221,29 +248,32 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   }
   // ---- the block's queries: row m = r * G + g, scaled by 1 / max|q|, split into fp16 hi + lo -----
   float qscale = 0.f;  // (softmax threads, their row) max|q| * sm_scale * log2(e) / alpha_k
-  if (tid < 256) {
-    const int m = tid >> 1, kb = tid & 1;  // two threads per row, one 64-column K-block each
+  if (tid < 512) {
+    constexpr int QT = 4, QD = kD / QT;  // QT threads stage a row, QD dims each
+    const int m = tid / QT, part = tid % QT;
+    const int d0 = part * QD, kb = d0 >> 6, c0 = (d0 & 63) >> 3;  // 64-column K-block, first 16-byte chunk
     const int r = m / G, g = m - r * G;
-    float v[64];
+    float v[QD];
     float qmax = 0.f;
     if (r < nrows) {
       const float4* src = reinterpret_cast<const float4*>(
-          p.q_rot + ((int64_t)(lr0 + r) * sh.Hq + kvh * G + g) * kD + 64 * kb);
+          p.q_rot + ((int64_t)(lr0 + r) * sh.Hq + kvh * G + g) * kD + d0);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < QD / 4; ++i) {
         const float4 x = src[i];
         v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
       }
 #pragma unroll
-      for (int i = 0; i < 64; ++i) qmax = fmaxf(qmax, fabsf(v[i]));
+      for (int i = 0; i < QD; ++i) qmax = fmaxf(qmax, fabsf(v[i]));
     } else {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) v[i] = 0.f;
+      for (int i = 0; i < QD; ++i) v[i] = 0.f;
     }
-    qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, 1));
+#pragma unroll
+    for (int o = 1; o < QT; o <<= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, o));
     const float inv = qmax > 0.f ? 1.f / qmax : 0.f;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < QD / 8; ++c) {
       uint32_t hi[4], lo[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -252,12 +282,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         hi[e] = pack_h2(h0, h1);
         lo[e] = pack_h2(x0 - h0, x1 - h1);
       }
-      const uint32_t off = (uint32_t)kb * 16384u + swz(m, c);
+      const uint32_t off = (uint32_t)kb * 16384u + swz(m, c0 + c);
       *reinterpret_cast<uint4*>(sm + kOffQhi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       if (!FAST) *reinterpret_cast<uint4*>(sm + kOffQlo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
-    // hand qmax of row m to the thread that owns TMEM lane m (thread m): through the norm scratch
-    if (kb == 0) reinterpret_cast<float*>(sm + kOffP)[m] = qmax * (a.scale_log2e / a.lut_scale_k);
+    // hand qmax of row m to the threads that own TMEM lane m: through the P area (not in use yet)
+    if (part == 0) reinterpret_cast<float*>(sm + kOffP)[m] = qmax * (a.scale_log2e / a.lut_scale_k);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -265,7 +295,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = s_tmem;
   // ---- softmax threads: warps 0-7; row = TMEM lane = 32 * (warp & 3) + lane, column half = warp >> 2
-  const bool smx = tid < 256;
+  const bool smx = tid < kSmx;
   const int row = 32 * (warp & 3) + lane, hf = (warp >> 2) & 1;
   if (smx) qscale = reinterpret_cast<const float*>(sm + kOffP)[row];
   __syncthreads();  // the P area is reused below
@@ -365,7 +395,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   bool o_zero = true;  // the O accumulator holds nothing yet (first PV overwrites)
   // ---- pipeline fill: tiles 0 and 1 in flight, tile 0 dequantised by everybody, S_0 issued ---------
   if (n_tiles > 0) {
-    if (warp == 8 && elect_one_sync()) {
+    if (warp == kIssueWarp && elect_one_sync()) {
       int b0[4], b1[4];
       load_blks(0, b0);
       if (n_tiles > 1) load_blks(1, b1);
@@ -378,40 +408,64 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     if (!ok0) s_info[3] = 1;
     __syncthreads();
-    if (!s_info[3] && warp == 8 && elect_one_sync()) {
+    if (!s_info[3] && warp == kIssueWarp && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       issue_s(0);
     }
   }
 
-  // ---- per tile: warps 0-3 turn S_j into P_j while warps 4-7 dequantise tile j+1; then one thread
-  //      issues S_{j+1} and O += P_j V~_j ----------------------------------------------------------------
-  for (int j = 0; j < n_tiles && !s_info[3]; ++j) {
+  int blk_next[4] = {0, 0, 0, 0};  // (warp 8) pages of the tile after next
+  if (warp == kIssueWarp && n_tiles > 2) load_blks(2, blk_next);
+  // ---- per tile: warps 0-7 turn S_j into P_j while warps 8-15 dequantise tile j+1 and issue S_{j+1};
+  //      then one thread issues O += P_j V~_j --------------------------------------------------------------
+  bool gave_up = n_tiles > 0 && s_info[3] != 0;  // a bounded wait ran out somewhere in the block
+  for (int j = 0; j < n_tiles && !gave_up; ++j) {
     const int t0 = t_first + j * kBN;
     bool ok = true;
-    int blk_next[4] = {0, 0, 0, 0};  // (warp 8) pages of tile j + 2, fetched while this tile is processed
-    if (warp == 8 && j + 2 < n_tiles) load_blks(j + 2, blk_next);
+    // The packed stage of tile j was dequantised during the previous iteration: tile j + 2 goes into
+    // it now, a whole iteration before its turn (its page ids were read an iteration ago; those of
+    // tile j + 3 are read now).
+    if (warp == kIssueWarp) {
+      if (j + 2 < n_tiles && elect_one_sync()) issue_tile(j + 2, blk_next);
+      __syncwarp();
+      if (j + 3 < n_tiles) load_blks(j + 3, blk_next);
+    }
+    PF_STAMP(j, 0);
     if (!smx) {
-      // buffer (j+1) & 1 was read by the MMAs of tile j-1: wait for them, then refill it
-      if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1));
       if (j + 1 < n_tiles) {
-        ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
-        dequant_tile(j + 1, tid - 256, 128, 0, 256);  // keys and norms; the softmax warps take the values
+        const bool deq = warp < kIssueWarp;
+        // K~ buffer (j+1) & 1, its norms and S buffer (j+1) & 1 were last used for tile j-1, whose
+        // scores the softmax warps consumed before the block barrier that ended the previous iteration
+        if (deq) {
+          ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1));
+          PF_STAMP(j, 1);
+          dequant_tile(j + 1, tid - kSmx, kDeq, 0, 256);  // keys and norms
+          PF_STAMP(j, 2);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
         // S_{j+1} goes into the other S buffer as soon as its K~ is in place: the softmax warps
         // find it ready when they finish tile j
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        asm volatile("bar.sync 5, 128;" ::: "memory");
-        const bool okw = __all_sync(0xffffffffu, ok);
-        if (okw && warp == 8 && elect_one_sync()) {
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(j + 1);
+        asm volatile("bar.sync 5, %0;" ::"n"(kDeq + 32) : "memory");
+        if (!deq) {
+          if (elect_one_sync()) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(j + 1);
+          }
+          PF_STAMP(j, 3);
+        } else {
+          // the values of tile j + 1 (only O += P V~ of the next iteration reads them): V~ buffer
+          // (j+1) & 1 was read by the MMAs of tile j-1
+          if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1)) && ok;
+          PF_STAMP(j, 4);
+          dequant_tile(j + 1, tid - kSmx, kDeq, 256, 512);
+          PF_STAMP(j, 5);
         }
       }
-      if (!ok) s_info[3] = 1;
     } else {
       ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      PF_STAMP(j, 1);
       const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
       const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
       // sc[i] = score of column i in the log2 domain (-inf = not visible).  Tiles strictly inside
@@ -419,41 +473,45 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       float sc[32];
       float mt = -CUDART_INF_F;
       const bool inner = __all_sync(0xffffffffu, ok && row_live && t0 >= kv_lo && t0 + kBN <= kv_hi);
-      {
-        uint32_t v[32];
-        if (ok) tmem_ld32(lane_base + kColS + 64 * (j & 1) + 32 * hf, v);
-        const float4* kn4 = reinterpret_cast<const float4*>(ns);
-        const float4* lg4 = reinterpret_cast<const float4*>(ns + 128);
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {  // 16 columns at a time (short register lifetimes)
+        uint32_t v[16];
+        if (ok) tmem_ld16(lane_base + kColS + 64 * (j & 1) + 32 * hf + 16 * hh, v);
+        const float4* kn4 = reinterpret_cast<const float4*>(ns + 16 * hh);
+        const float4* lg4 = reinterpret_cast<const float4*>(ns + 128 + 16 * hh);
         if (inner) {
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
+          for (int i4 = 0; i4 < 4; ++i4) {
             const float4 kn = kn4[i4], lg = lg4[i4];
             const float kk[4] = {kn.x, kn.y, kn.z, kn.w}, ll[4] = {lg.x, lg.y, lg.z, lg.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float s = (__uint_as_float(v[4 * i4 + e]) * kk[e]) * qscale;
-              sc[4 * i4 + e] = s;
+              sc[16 * hh + 4 * i4 + e] = s;
               mt = fmaxf(mt, s + ll[e]);
             }
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int pos = t0 + 32 * hf + i;
+          for (int i = 0; i < 16; ++i) {
+            const int pos = t0 + 32 * hf + 16 * hh + i;
             const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
-            const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[i]) : -CUDART_INF_F;
-            sc[i] = s;
-            mt = fmaxf(mt, vis ? s + ns[128 + i] : -CUDART_INF_F);
+            const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[16 * hh + i]) : -CUDART_INF_F;
+            sc[16 * hh + i] = s;
+            mt = fmaxf(mt, vis ? s + ns[128 + 16 * hh + i] : -CUDART_INF_F);
           }
         }
       }
       // the row's maximum over both halves (the decisions below must agree in its two threads)
+      PF_STAMP(j, 2);
       xchg[hf * 128 + row] = mt;
       pair_sync();
       mt = fmaxf(mt, xchg[(hf ^ 1) * 128 + row]);
+      PF_STAMP(j, 3);
       // P and O are still in use by the MMAs of tile j-1
       if (j >= 1) ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1))) && ok;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      PF_STAMP(j, 4);
       // lazily updated reference: moves only when a score (shifted by log2 of its value norm)
       // exceeds it by more than 2^8; then this row of O is rescaled in tensor memory
       const bool bump = mt > m_run + 8.f;
@@ -462,12 +520,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         if (bump) { m_run = mt; l_run *= alpha; }
         if (!o_zero && ok) {
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {  // this thread's 64 of the row's 128 columns
-            uint32_t v[32];
-            tmem_ld32(lane_base + kColO + 64 * hf + 32 * q, v);
+          for (int q = 0; q < 4; ++q) {  // this thread's 64 of the row's 128 columns
+            uint32_t v[16];
+            tmem_ld16(lane_base + kColO + 64 * hf + 16 * q, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st32(lane_base + kColO + 64 * hf + 32 * q, v);
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st16(lane_base + kColO + 64 * hf + 16 * q, v);
           }
         }
       }
@@ -496,19 +554,14 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         if (!FAST) *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
       }
       l_run += lsum;  // (this thread's half of the row sum)
-      // the values of tile j + 1 (only O += P V~ of the next iteration reads them): its buffer was freed
-      // by the MMAs of tile j - 1, which this thread has already waited for
-      if (j + 1 < n_tiles) {
-        ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1)) && ok;
-        dequant_tile(j + 1, tid, 256, 256, 512);
-      }
-      if (!ok) s_info[3] = 1;
+      PF_STAMP(j, 5);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (s_info[3]) break;
-    if (warp == 8 && elect_one_sync()) {
+    gave_up = __syncthreads_or(!ok) != 0;  // (the flag travels with the barrier: no shared-memory read)
+    PF_STAMP(j, 7);
+    if (gave_up) break;
+    if (warp == kIssueWarp && elect_one_sync()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint64_t dvb = d_v + (uint64_t)((j & 1) * (16384 >> 4));
 #pragma unroll
@@ -518,12 +571,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         mma_f16(tmem + kColO, d_p + (uint64_t)((32 * s) >> 4), dv, kDescO, (FAST && o_zero && !s) ? 0u : 1u);
       }
       mma_commit(bar_o);
-      // the packed stage of tile j was dequantised one iteration ago: refill it with tile j + 2
-      if (j + 2 < n_tiles) issue_tile(j + 2, blk_next);
     }
+    PF_STAMP(j, 8);
     o_zero = false;
   }
-  if (n_tiles > 0 && !s_info[3]) {  // the last tile's MMAs
+  if (gave_up && tid == 0) s_info[3] = 1;
+  if (n_tiles > 0 && !gave_up) {  // the last tile's MMAs
     if (!bar_wait_bounded(bar_o, (uint32_t)((n_tiles - 1) & 1))) s_info[3] = 1;
   }
   __syncthreads();
@@ -640,3 +693,9 @@ int launch_prefill_tc(const AttnArgs& a, cudaStream_t st, bool fast) {
 }
 
 }  // namespace tq4
+
+#ifdef TQ4_TRACE
+extern "C" int tq4_prefill_trace_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, tq4::g_ptrace, sizeof(long long) * 4 * 64 * 16) == cudaSuccess ? 0 : 1;
+}
+#endif
