@@ -15,9 +15,9 @@
 // layout of one dense partial per row; the merge kernel un-rotates and stores them.
 // Warps 0-7 own the S / O rows, two threads per row (softmax, rescale, epilogue); warps 8-15
 // dequantise the next tile into the other K~ / V~ buffer meanwhile (keys first, so that the next
-// scores can be issued early; then the values); one thread of warp 16 issues the TMA copies and the
-// MMAs (an MMA issue blocks while the tensor pipe's queue is full: a warp that also dequantises
-// would hold the others up at their barrier).  Every wait is bounded.
+// scores can be issued early; then the values) and one thread of warp 8 issues the TMA copies and
+// the MMAs.  (A seventeenth warp for the issuing alone was tried: five warps on one scheduler cut
+// the register budget to 96 and the loop ran no faster.)  Every wait is bounded.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -34,8 +34,8 @@ __device__ long long g_ptrace[4][64][16];
 #define PF_STAMP(j, e)                                                                              \
   do {                                                                                              \
     if (blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (j) < 64 &&                             \
-        (warp == 0 || warp == 8 || warp == 15 || warp == 16))                                       \
-      g_ptrace[warp == 0 ? 0 : warp == 8 ? 1 : warp == 15 ? 2 : 3][j][e] = clock64();               \
+        (warp == 0 || warp == 4 || warp == 8 || warp == 15))                                        \
+      g_ptrace[warp == 0 ? 0 : warp == 4 ? 1 : warp == 8 ? 2 : 3][j][e] = clock64();                \
   } while (0)
 #else
 #define PF_STAMP(j, e) do {} while (0)
@@ -46,8 +46,8 @@ constexpr int kD = 128;
 constexpr int kBN = 64;                 // tokens per tile
 constexpr int kSmx = 256;                 // warps 0-7: softmax (two threads per row)
 constexpr int kDeq = 256;                 // warps 8-15: dequantise
-constexpr int kIssueWarp = (kSmx + kDeq) / 32;  // warp 16: issues the TMA copies and the MMAs
-constexpr int kThreads = kSmx + kDeq + 32;
+constexpr int kIssueWarp = kSmx / 32;     // one thread of warp 8 also issues the TMA copies and the MMAs
+constexpr int kThreads = kSmx + kDeq;
 constexpr uint32_t kTmemCols = 256;     // S (two buffers): columns [0, 64) and [64, 128), O: columns [128, 256)
 constexpr uint32_t kColS = 0, kColO = 128;
 
@@ -248,8 +248,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   }
   // ---- the block's queries: row m = r * G + g, scaled by 1 / max|q|, split into fp16 hi + lo -----
   float qscale = 0.f;  // (softmax threads, their row) max|q| * sm_scale * log2(e) / alpha_k
-  if (tid < 512) {
-    constexpr int QT = 4, QD = kD / QT;  // QT threads stage a row, QD dims each
+  {
+    constexpr int QT = kThreads / 128, QD = kD / QT;  // QT threads stage a row, QD dims each
     const int m = tid / QT, part = tid % QT;
     const int d0 = part * QD, kb = d0 >> 6, c0 = (d0 & 63) >> 3;  // 64-column K-block, first 16-byte chunk
     const int r = m / G, g = m - r * G;
@@ -433,34 +433,29 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     PF_STAMP(j, 0);
     if (!smx) {
       if (j + 1 < n_tiles) {
-        const bool deq = warp < kIssueWarp;
         // K~ buffer (j+1) & 1, its norms and S buffer (j+1) & 1 were last used for tile j-1, whose
         // scores the softmax warps consumed before the block barrier that ended the previous iteration
-        if (deq) {
-          ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1));
-          PF_STAMP(j, 1);
-          dequant_tile(j + 1, tid - kSmx, kDeq, 0, 256);  // keys and norms
-          PF_STAMP(j, 2);
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
+        ok = bar_wait_bounded(bar_t0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1));
+        PF_STAMP(j, 1);
+        dequant_tile(j + 1, tid - kSmx, kDeq, 0, 256);  // keys and norms
+        PF_STAMP(j, 2);
         // S_{j+1} goes into the other S buffer as soon as its K~ is in place: the softmax warps
         // find it ready when they finish tile j
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        asm volatile("bar.sync 5, %0;" ::"n"(kDeq + 32) : "memory");
-        if (!deq) {
-          if (elect_one_sync()) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_s(j + 1);
-          }
-          PF_STAMP(j, 3);
-        } else {
-          // the values of tile j + 1 (only O += P V~ of the next iteration reads them): V~ buffer
-          // (j+1) & 1 was read by the MMAs of tile j-1
-          if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1)) && ok;
-          PF_STAMP(j, 4);
-          dequant_tile(j + 1, tid - kSmx, kDeq, 256, 512);
-          PF_STAMP(j, 5);
+        asm volatile("bar.sync 5, %0;" ::"n"(kDeq) : "memory");
+        const bool okw = __all_sync(0xffffffffu, ok);
+        if (okw && warp == kIssueWarp && elect_one_sync()) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(j + 1);
         }
+        PF_STAMP(j, 3);
+        // the values of tile j + 1 (only O += P V~ of the next iteration reads them): V~ buffer
+        // (j+1) & 1 was read by the MMAs of tile j-1
+        if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1)) && ok;
+        PF_STAMP(j, 4);
+        dequant_tile(j + 1, tid - kSmx, kDeq, 256, 512);
+        PF_STAMP(j, 5);
       }
     } else {
       ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1)));
