@@ -11,6 +11,11 @@
 //   S = Qhi K~^T + Qlo K~^T   (tcgen05.mma kind::f16, 128 x 64 x 16, fp32 in TMEM, two S buffers)
 //   tcgen05.ld S, x knorm, mask, lazy online softmax, P = p * vnorm as fp16 hi + lo   CUDA cores
 //   O += Plo V~ + Phi V~      (tcgen05.mma 128 x 128 x 16, V~ as an MN-major B operand)
+// The A operands of both products live in TENSOR MEMORY, not in shared memory: the block's queries
+// are written there once (tcgen05.st, two fp16 per 32-bit column), the probabilities once per tile by
+// the threads that computed them.  The loop is bound by shared-memory bandwidth (the tensor pipe
+// fetches its shared-memory operands again for every instruction, beside the dequantisation's own
+// loads and stores): with Q and P in shared memory the MMAs alone read 224 KB per tile, now 96 KB.
 // At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
 // layout of one dense partial per row; the merge kernel un-rotates and stores them.
 // Warps 0-7 own the S / O rows, two threads per row (softmax, rescale, epilogue); warps 8-15
@@ -46,27 +51,27 @@ constexpr int kD = 128;
 constexpr int kBN = 64;                 // tokens per tile
 constexpr int kSmx = 256;                 // warps 0-7: softmax (two threads per row)
 constexpr int kDeq = 256;                 // warps 8-15: dequantise
-constexpr int kIssueWarp = kSmx / 32;     // one thread of warp 8 also issues the TMA copies and the MMAs
 constexpr int kThreads = kSmx + kDeq;
-constexpr uint32_t kTmemCols = 256;     // S (two buffers): columns [0, 64) and [64, 128), O: columns [128, 256)
-constexpr uint32_t kColS = 0, kColO = 128;
+constexpr int kIssueWarp = kSmx / 32;     // one thread of warp 8 also issues the MMAs,
+constexpr int kCopyWarp = kThreads / 32 - 1;  // one of warp 15 the TMA copies (either job delays its warp)
+// tensor memory (all 512 columns: one CTA per SM): S (two buffers) [0, 64) and [64, 128), O [128, 256),
+// Q hi [256, 320) and lo [320, 384) (128 dims, two per column), P hi [384, 416) and lo [416, 448)
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 128, kColQ = 256, kColQlo = 320, kColP = 384, kColPlo = 416;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
-constexpr uint32_t kOffQhi = 0;                       // 2 K-blocks x [128 rows][128 B]
-constexpr uint32_t kOffQlo = 32768;
-constexpr uint32_t kOffK = 65536;                     // 2 buffers x 2 K-blocks x [64 tok][128 B]
+constexpr uint32_t kOffK = 0;                         // 2 buffers x 2 K-blocks x [64 tok][128 B]
 constexpr uint32_t kOffV = kOffK + 32768;             // 2 buffers x 2 MN-blocks x [64 tok][128 B]
-constexpr uint32_t kOffP = kOffV + 32768;             // [128 rows][128 B] fp16 hi part of p * vnorm
-constexpr uint32_t kOffPlo = kOffP + 16384;           // ... and its fp16 remainder
-constexpr uint32_t kOffStage = kOffPlo + 16384;       // 2 x (4 pages x 2048 B indices + 4 x 512 B norms)
+constexpr uint32_t kOffStage = kOffV + 32768;         // 2 x (4 pages x 2048 B indices + 4 x 512 B norms)
 constexpr uint32_t kStageBytes = 4 * 2048 + 4 * 512;
 // byte -> half2 tables of K and V, 16 copies of every entry side by side (lane pair p reads copy p:
 // lookups of different lane pairs never share a bank, at most two lanes collide)
 constexpr int kLutCopies = 16;
 constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // 2 tables x 256 entries x 16 copies x 4 B
 constexpr uint32_t kOffNorm = kOffLut + 2 * 256 * kLutCopies * 4;  // 2 buffers x (kn[64], vn[64], lg[64])
-constexpr uint32_t kOffXchg = kOffNorm + 2 * 3 * 64 * 4;     // [2 halves][128 rows] floats exchanged by a row's two threads
-constexpr uint32_t kSmemBytes = kOffXchg + 2 * 128 * 4;
+constexpr uint32_t kOffXchg = kOffNorm + 2 * 3 * 64 * 4;     // [4][128 rows] floats exchanged by the threads of a row
+constexpr uint32_t kSmemBytes = kOffXchg + 4 * 128 * 4;
+static_assert(2 * (kSmemBytes + 1024) > 227 * 1024, "one CTA per SM: it allocates the whole tensor memory");
 
 // instruction descriptors (kind::f16, fp16 operands, fp32 accumulator, M = 128)
 constexpr uint32_t kDescS = (1u << 4) | ((64u >> 3) << 17) | ((128u >> 4) << 24);                // N = 64, B K-major
@@ -85,12 +90,13 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t lbo) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+// D (tensor memory) (+)= A * B with the A operand (128 rows x 16 fp16 = 8 columns) read from tensor memory
+__device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t acc) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -148,6 +154,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// 8 consecutive 32-bit columns of this thread's TMEM lane (no wait: the caller waits once)
+__device__ __forceinline__ void tmem_st8_nowait(uint32_t taddr, const uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
@@ -246,62 +260,64 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       lut[i] = pack_h2(c_hi, c_lo);
     }
   }
-  // ---- the block's queries: row m = r * G + g, scaled by 1 / max|q|, split into fp16 hi + lo -----
-  float qscale = 0.f;  // (softmax threads, their row) max|q| * sm_scale * log2(e) / alpha_k
+  // ---- the block's queries: row m = r * G + g = tensor-memory lane m, scaled by 1 / max|q|, split into
+  //      fp16 hi + lo, two dims per 32-bit column.  A warp reaches lanes 32 * (warp % 4) ..., so thread
+  //      (warp, lane) stages dims [32 * (warp / 4), + 32) of row 32 * (warp % 4) + lane ----------------
+  const int row = 32 * (warp & 3) + lane;
+  const int my_r = row / G, my_g = row % G;
+  float* xchg = reinterpret_cast<float*>(sm + kOffXchg);
+  float qv[32];
   {
-    constexpr int QT = kThreads / 128, QD = kD / QT;  // QT threads stage a row, QD dims each
-    const int m = tid / QT, part = tid % QT;
-    const int d0 = part * QD, kb = d0 >> 6, c0 = (d0 & 63) >> 3;  // 64-column K-block, first 16-byte chunk
-    const int r = m / G, g = m - r * G;
-    float v[QD];
+    const int part = warp >> 2;
     float qmax = 0.f;
-    if (r < nrows) {
+    if (my_r < nrows) {
       const float4* src = reinterpret_cast<const float4*>(
-          p.q_rot + ((int64_t)(lr0 + r) * sh.Hq + kvh * G + g) * kD + d0);
+          p.q_rot + ((int64_t)(lr0 + my_r) * sh.Hq + kvh * G + my_g) * kD + 32 * part);
 #pragma unroll
-      for (int i = 0; i < QD / 4; ++i) {
+      for (int i = 0; i < 8; ++i) {
         const float4 x = src[i];
-        v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
+        qv[4 * i] = x.x; qv[4 * i + 1] = x.y; qv[4 * i + 2] = x.z; qv[4 * i + 3] = x.w;
       }
 #pragma unroll
-      for (int i = 0; i < QD; ++i) qmax = fmaxf(qmax, fabsf(v[i]));
+      for (int i = 0; i < 32; ++i) qmax = fmaxf(qmax, fabsf(qv[i]));
     } else {
 #pragma unroll
-      for (int i = 0; i < QD; ++i) v[i] = 0.f;
+      for (int i = 0; i < 32; ++i) qv[i] = 0.f;
     }
-#pragma unroll
-    for (int o = 1; o < QT; o <<= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, o));
+    xchg[part * 128 + row] = qmax;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();  // the tensor-memory address, the table and the partial maxima are in place
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s_tmem;
+  const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+  const float qmax = fmaxf(fmaxf(xchg[row], xchg[128 + row]), fmaxf(xchg[256 + row], xchg[384 + row]));
+  const float qscale = qmax * (a.scale_log2e / a.lut_scale_k);  // max|q| * sm_scale * log2(e) / alpha_k
+  {
+    const int part = warp >> 2;
     const float inv = qmax > 0.f ? 1.f / qmax : 0.f;
 #pragma unroll
-    for (int c = 0; c < QD / 8; ++c) {
-      uint32_t hi[4], lo[4];
+    for (int c = 0; c < 2; ++c) {  // 16 dims = 8 columns at a time
+      uint32_t hi[8], lo[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float x0 = v[8 * c + 2 * e] * inv, x1 = v[8 * c + 2 * e + 1] * inv;
+      for (int e = 0; e < 8; ++e) {
+        const float x0 = qv[16 * c + 2 * e] * inv, x1 = qv[16 * c + 2 * e + 1] * inv;
         const float h0 = __half2float(__float2half_rn(x0)), h1 = __half2float(__float2half_rn(x1));
         hi[e] = pack_h2(h0, h1);
         lo[e] = pack_h2(x0 - h0, x1 - h1);
       }
-      const uint32_t off = (uint32_t)kb * 16384u + swz(m, c0 + c);
-      *reinterpret_cast<uint4*>(sm + kOffQhi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-      if (!FAST) *reinterpret_cast<uint4*>(sm + kOffQlo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      tmem_st8_nowait(lane_base + kColQ + 16 * part + 8 * c, hi);
+      if (!FAST) tmem_st8_nowait(lane_base + kColQlo + 16 * part + 8 * c, lo);
     }
-    // hand qmax of row m to the threads that own TMEM lane m: through the P area (not in use yet)
-    if (part == 0) reinterpret_cast<float*>(sm + kOffP)[m] = qmax * (a.scale_log2e / a.lut_scale_k);
+    tmem_st_wait();
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  __syncthreads();  // Q is in tensor memory; the exchange area is free again
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem = s_tmem;
   // ---- softmax threads: warps 0-7; row = TMEM lane = 32 * (warp & 3) + lane, column half = warp >> 2
   const bool smx = tid < kSmx;
-  const int row = 32 * (warp & 3) + lane, hf = (warp >> 2) & 1;
-  if (smx) qscale = reinterpret_cast<const float*>(sm + kOffP)[row];
-  __syncthreads();  // the P area is reused below
-  const int my_r = row / G, my_g = row % G;
+  const int hf = (warp >> 2) & 1;
   const bool row_live = smx && my_r < nrows;
-  float* xchg = reinterpret_cast<float*>(sm + kOffXchg);
   // the two threads of a row sit in warps w and w + 4: a 64-thread named barrier per warp pair
   auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory"); };
   const int kv_lo = row_live ? p.kv_start[lr0 + my_r] : 0;
@@ -323,7 +339,11 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 #pragma unroll
     for (int pg = 0; pg < 4; ++pg) {
       const int pos = t0 + 16 * pg;
-      blk[pg] = pos < blk_hi ? __ldg(bt + (pos >> bs_shift)) : 0;  // out-of-range ids read zeros (TMA bounds)
+      // (a volatile load: the ids are used an iteration later, and an ordinary load gets moved down to
+      //  its use, where the copy-issuing warp then waits a global round trip in every iteration)
+      int id = 0;
+      if (pos < blk_hi) asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(id) : "l"(bt + (pos >> bs_shift)));
+      blk[pg] = id;  // out-of-range ids read zeros (TMA bounds)
     }
   };
   auto issue_tile = [&](int j, const int (&blks)[4]) {
@@ -374,9 +394,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   };
   // descriptors of the operand regions; a byte offset inside a region adds offset / 16 to the
   // address field (all regions lie below 256 KB, the sum never carries into the other fields)
-  const uint64_t d_qhi = desc_kmajor(base + kOffQhi), d_qlo = desc_kmajor(base + kOffQlo);
-  const uint64_t d_k = desc_kmajor(base + kOffK), d_p = desc_kmajor(base + kOffP);
-  const uint64_t d_plo = desc_kmajor(base + kOffPlo), d_v = desc_mnmajor(base + kOffV, 8192);
+  const uint64_t d_k = desc_kmajor(base + kOffK), d_v = desc_mnmajor(base + kOffV, 8192);
   auto issue_s = [&](int j) {  // S = Q K~^T of tile j (one thread)
     const uint64_t dk = d_k + (uint64_t)((j & 1) * (16384 >> 4));
 #pragma unroll
@@ -384,9 +402,9 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         const uint64_t db = dk + (uint64_t)((kb * 8192 + 32 * s) >> 4);
-        const uint64_t qo = (uint64_t)((kb * 16384 + 32 * s) >> 4);
-        if (!FAST) mma_f16(tmem + kColS + 64 * (j & 1), d_qlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
-        mma_f16(tmem + kColS + 64 * (j & 1), d_qhi + qo, db, kDescS, (FAST && !(kb | s)) ? 0u : 1u);
+        const uint32_t qo = (uint32_t)(32 * kb + 8 * s);  // dims 64 kb + 16 s ...: two per column
+        if (!FAST) mma_f16_ta(tmem + kColS + 64 * (j & 1), tmem + kColQlo + qo, db, kDescS, (kb | s) ? 1u : 0u);
+        mma_f16_ta(tmem + kColS + 64 * (j & 1), tmem + kColQ + qo, db, kDescS, (FAST && !(kb | s)) ? 0u : 1u);
       }
     mma_commit(bar_s0 + 8 * (j & 1));  // one barrier per S buffer: a waiter can never be two phases behind
   };
@@ -395,7 +413,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   bool o_zero = true;  // the O accumulator holds nothing yet (first PV overwrites)
   // ---- pipeline fill: tiles 0 and 1 in flight, tile 0 dequantised by everybody, S_0 issued ---------
   if (n_tiles > 0) {
-    if (warp == kIssueWarp && elect_one_sync()) {
+    if (warp == kCopyWarp && elect_one_sync()) {
       int b0[4], b1[4];
       load_blks(0, b0);
       if (n_tiles > 1) load_blks(1, b1);
@@ -414,8 +432,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     }
   }
 
-  int blk_next[4] = {0, 0, 0, 0};  // (warp 8) pages of the tile after next
-  if (warp == kIssueWarp && n_tiles > 2) load_blks(2, blk_next);
+  int blk_next[4] = {0, 0, 0, 0};  // (copy warp) pages of the tile after next
+  if (warp == kCopyWarp && n_tiles > 2) load_blks(2, blk_next);
   // ---- per tile: warps 0-7 turn S_j into P_j while warps 8-15 dequantise tile j+1 and issue S_{j+1};
   //      then one thread issues O += P_j V~_j --------------------------------------------------------------
   bool gave_up = n_tiles > 0 && s_info[3] != 0;  // a bounded wait ran out somewhere in the block
@@ -425,7 +443,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     // The packed stage of tile j was dequantised during the previous iteration: tile j + 2 goes into
     // it now, a whole iteration before its turn (its page ids were read an iteration ago; those of
     // tile j + 3 are read now).
-    if (warp == kIssueWarp) {
+    if (warp == kCopyWarp) {
       if (j + 2 < n_tiles && elect_one_sync()) issue_tile(j + 2, blk_next);
       __syncwarp();
       if (j + 3 < n_tiles) load_blks(j + 3, blk_next);
@@ -462,7 +480,6 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       PF_STAMP(j, 1);
       const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
-      const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
       // sc[i] = score of column i in the log2 domain (-inf = not visible).  Tiles strictly inside
       // the visible range of every row of the warp take the short path without per-element masks.
       float sc[32];
@@ -528,30 +545,34 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       float lsum = 0.f;
       const float4* vn4 = reinterpret_cast<const float4*>(ns + 64);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t h[4], lw[4];
-        const float4 va = vn4[2 * c], vb4 = vn4[2 * c + 1];
-        const float vv[8] = {va.x, va.y, va.z, va.w, vb4.x, vb4.y, vb4.z, vb4.w};
+      for (int c = 0; c < 2; ++c) {  // 16 tokens = 8 columns of P at a time
+        uint32_t h[8], lw[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int t = 8 * c + 2 * e;
-          const float e0 = ex2_approx(sc[t] - m_use), e1 = ex2_approx(sc[t + 1] - m_use);
-          lsum += e0 + e1;
-          // (a hidden column has e = 0; its value norm may be anything, so select instead of multiply)
-          const float v0 = (inner || sc[t] != -CUDART_INF_F) ? e0 * vv[2 * e] : 0.f;
-          const float v1 = (inner || sc[t + 1] != -CUDART_INF_F) ? e1 * vv[2 * e + 1] : 0.f;
-          const __half2 hp = __floats2half2_rn(v0, v1);
-          const float2 hf2 = __half22float2(hp);
-          h[e] = *reinterpret_cast<const uint32_t*>(&hp);
-          if (!FAST) lw[e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
+        for (int e4 = 0; e4 < 4; ++e4) {
+          const float4 va = vn4[4 * c + e4];
+          const float vv[4] = {va.x, va.y, va.z, va.w};
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int t = 16 * c + 4 * e4 + 2 * e;
+            const float e0 = ex2_approx(sc[t] - m_use), e1 = ex2_approx(sc[t + 1] - m_use);
+            lsum += e0 + e1;
+            // (a hidden column has e = 0; its value norm may be anything, so select instead of multiply)
+            const float v0 = (inner || sc[t] != -CUDART_INF_F) ? e0 * vv[2 * e] : 0.f;
+            const float v1 = (inner || sc[t + 1] != -CUDART_INF_F) ? e1 * vv[2 * e + 1] : 0.f;
+            const __half2 hp = __floats2half2_rn(v0, v1);
+            const float2 hf2 = __half22float2(hp);
+            h[2 * e4 + e] = *reinterpret_cast<const uint32_t*>(&hp);
+            if (!FAST) lw[2 * e4 + e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
+          }
         }
-        *reinterpret_cast<uint4*>(sm + kOffP + swz(row, 4 * hf + c)) = make_uint4(h[0], h[1], h[2], h[3]);
-        if (!FAST) *reinterpret_cast<uint4*>(sm + kOffPlo + swz(row, 4 * hf + c)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        tmem_st8_nowait(lane_base + kColP + 16 * hf + 8 * c, h);
+        if (!FAST) tmem_st8_nowait(lane_base + kColPlo + 16 * hf + 8 * c, lw);
       }
+      tmem_st_wait();
       l_run += lsum;  // (this thread's half of the row sum)
       PF_STAMP(j, 5);
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (!smx) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // (the dequantised values)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     gave_up = __syncthreads_or(!ok) != 0;  // (the flag travels with the barrier: no shared-memory read)
     PF_STAMP(j, 7);
@@ -562,8 +583,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 #pragma unroll
       for (int s = 0; s < 4; ++s) {
         const uint64_t dv = dvb + (uint64_t)((2048 * s) >> 4);
-        if (!FAST) mma_f16(tmem + kColO, d_plo + (uint64_t)((32 * s) >> 4), dv, kDescO, (!o_zero || s) ? 1u : 0u);
-        mma_f16(tmem + kColO, d_p + (uint64_t)((32 * s) >> 4), dv, kDescO, (FAST && o_zero && !s) ? 0u : 1u);
+        if (!FAST) mma_f16_ta(tmem + kColO, tmem + kColPlo + 8 * s, dv, kDescO, (!o_zero || s) ? 1u : 0u);
+        mma_f16_ta(tmem + kColO, tmem + kColP + 8 * s, dv, kDescO, (FAST && o_zero && !s) ? 0u : 1u);
       }
       mma_commit(bar_o);
     }
@@ -580,7 +601,6 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   const bool dead = s_info[3] != 0;
   if (smx) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
     xchg[hf * 128 + row] = l_run;  // the row sum = the two halves
     pair_sync();
     l_run += xchg[(hf ^ 1) * 128 + row];
