@@ -64,9 +64,10 @@ constexpr uint32_t kOffK = 0;                         // 2 buffers x 2 K-blocks 
 constexpr uint32_t kOffV = kOffK + 32768;             // 2 buffers x 2 MN-blocks x [64 tok][128 B]
 constexpr uint32_t kOffStage = kOffV + 32768;         // 2 x (4 pages x 2048 B indices + 4 x 512 B norms)
 constexpr uint32_t kStageBytes = 4 * 2048 + 4 * 512;
-// byte -> half2 tables of K and V, 16 copies of every entry side by side (lane pair p reads copy p:
-// lookups of different lane pairs never share a bank, at most two lanes collide)
-constexpr int kLutCopies = 16;
+// byte -> half2 tables of K and V, 32 copies of every entry side by side: lane l reads copy l, so a
+// warp's 32 lookups always hit 32 different banks (with 16 copies 43 % of the kernel's shared-memory
+// wavefronts were conflicts of these lookups)
+constexpr int kLutCopies = 32;
 constexpr uint32_t kOffLut = kOffStage + 2 * kStageBytes;   // 2 tables x 256 entries x 16 copies x 4 B
 constexpr uint32_t kOffNorm = kOffLut + 2 * 256 * kLutCopies * 4;  // 2 buffers x (kn[64], vn[64], lg[64])
 constexpr uint32_t kOffXchg = kOffNorm + 2 * 3 * 64 * 4;     // [4][128 rows] floats exchanged by the threads of a row
@@ -372,7 +373,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     for (int item = item_lo + t; item < item_hi; item += nt) {
       const int u = item >> 8, tok = (item >> 2) & 63, seg = item & 3;
       const uint4 pk = *reinterpret_cast<const uint4*>(stg + (tok >> 4) * 2048 + u * 1024 + (tok & 15) * 64 + seg * 16);
-      const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256 * kLutCopies + (lane >> 1);
+      const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256 * kLutCopies + lane;
       const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
       unsigned char* dst = sm + (u ? kOffV : kOffK) + kv_off + (seg >> 1) * 8192;
 #pragma unroll
