@@ -47,7 +47,9 @@ FALLBACK_HBM_GBS = 6650.0
 # the N = 1 workload.  A STORED figure from an ncu capture (the timed run cannot measure DRAM
 # traffic): it is reported together with the name of the capture it comes from and only while the
 # kernel build named there is the one that runs; otherwise `traffic` is null.
-NCU_TRAFFIC = {"bytes": None, "capture": None}
+NCU_TRAFFIC = {"bytes": 309819136,  # dram__bytes_read.sum 303 762 432 + dram__bytes_write.sum 6 056 704
+               "capture": "profiles/attention_mma_kernel_b64_ctx4096_ncu_full.md (attention kernel with the "
+                          "fused prologue, one launch, ncu --set full)"}
 
 
 def measured_peak_gbs():
@@ -301,10 +303,13 @@ def run_ours(args, rank, world, device):
     alg_bytes = batch * CTX * hkv * (D + 8)  # 136 B per token per KV head at D=128
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (avg["attention"] * 1e-3) / 1e9
+    # the stored capture is of the 8-heads-per-GPU layout with the prologue inside the kernel
+    traffic_known = (alg_bytes == 285212672 and world == 1 and not args.emulate_world and not args.separate_write
+                     and not os.environ.get("TQ4_NO_FUSED_PROLOGUE") and not args.row_bytes)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4),
-                "traffic": NCU_TRAFFIC["bytes"] if alg_bytes == 285212672 else None,
-                "traffic_source": NCU_TRAFFIC["capture"] if alg_bytes == 285212672 else None,
+                "traffic": NCU_TRAFFIC["bytes"] if traffic_known else None,
+                "traffic_source": NCU_TRAFFIC["capture"] if traffic_known else None,
                 "kernel": "paged TQ4 attention (streaming) kernel", "peak_kind": f"of {peak_kind}",
                 "algorithmic_bytes_per_launch": alg_bytes,
                 "kernel_ms": {k: (round(v, 5) if v is not None else None) for k, v in avg.items()},
