@@ -28,6 +28,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "tq4_attention.cuh"
 
@@ -156,6 +157,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 // 8 consecutive 32-bit columns of this thread's TMEM lane (no wait: the caller waits once)
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&v)[16]) {  // the caller waits
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+// wait for the loads in flight; the registers are named so that no use of them moves above the wait
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&v)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st8_nowait(uint32_t taddr, const uint32_t (&v)[8]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
@@ -293,7 +311,9 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   const uint32_t tmem = s_tmem;
   const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
   const float qmax = fmaxf(fmaxf(xchg[row], xchg[128 + row]), fmaxf(xchg[256 + row], xchg[384 + row]));
-  const float qscale = qmax * (a.scale_log2e / a.lut_scale_k);  // max|q| * sm_scale * log2(e) / alpha_k
+  // max|q| * sm_scale * log2(e) / alpha_k: the factor between a stored dot product and the score in
+  // the log2 domain (at least the smallest normal number, so that a hidden score, -inf, times it stays -inf)
+  const float qscale = fmaxf(qmax * (a.scale_log2e / a.lut_scale_k), 1.17549435e-38f);
   {
     const int part = warp >> 2;
     const float inv = qmax > 0.f ? 1.f / qmax : 0.f;
@@ -481,15 +501,23 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       PF_STAMP(j, 1);
       const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
-      // sc[i] = score of column i in the log2 domain (-inf = not visible).  Tiles strictly inside
-      // the visible range of every row of the warp take the short path without per-element masks.
+      // sc[i] = dot product of column i times its key norm (-inf = not visible); the score in the log2
+      // domain is sc[i] * qscale.  Tiles strictly inside the visible range of every row of the warp
+      // take the short path without per-element masks.
       float sc[32];
       float mt = -CUDART_INF_F;
       const bool inner = __all_sync(0xffffffffu, ok && row_live && t0 >= kv_lo && t0 + kBN <= kv_hi);
+      // 16 columns at a time (short register lifetimes); the second load is in flight while the first
+      // half is processed
+      uint32_t vbuf[2][16];
+      if (ok) {
+        tmem_ld16(lane_base + kColS + 64 * (j & 1) + 32 * hf, vbuf[0]);
+        tmem_ld16_nowait(lane_base + kColS + 64 * (j & 1) + 32 * hf + 16, vbuf[1]);
+      }
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {  // 16 columns at a time (short register lifetimes)
-        uint32_t v[16];
-        if (ok) tmem_ld16(lane_base + kColS + 64 * (j & 1) + 32 * hf + 16 * hh, v);
+      for (int hh = 0; hh < 2; ++hh) {
+        if (hh == 1) tmem_ld_wait16(vbuf[1]);
+        uint32_t (&v)[16] = vbuf[hh];
         const float4* kn4 = reinterpret_cast<const float4*>(ns + 16 * hh);
         const float4* lg4 = reinterpret_cast<const float4*>(ns + 128 + 16 * hh);
         if (inner) {
@@ -499,9 +527,9 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
             const float kk[4] = {kn.x, kn.y, kn.z, kn.w}, ll[4] = {lg.x, lg.y, lg.z, lg.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float s = (__uint_as_float(v[4 * i4 + e]) * kk[e]) * qscale;
+              const float s = __uint_as_float(v[4 * i4 + e]) * kk[e];
               sc[16 * hh + 4 * i4 + e] = s;
-              mt = fmaxf(mt, s + ll[e]);
+              mt = fmaxf(mt, fmaf(s, qscale, ll[e]));
             }
           }
         } else {
@@ -509,9 +537,9 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
           for (int i = 0; i < 16; ++i) {
             const int pos = t0 + 32 * hf + 16 * hh + i;
             const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
-            const float s = vis ? __uint_as_float(v[i]) * (qscale * ns[16 * hh + i]) : -CUDART_INF_F;
+            const float s = vis ? __uint_as_float(v[i]) * ns[16 * hh + i] : -CUDART_INF_F;
             sc[16 * hh + i] = s;
-            mt = fmaxf(mt, vis ? s + ns[128 + 16 * hh + i] : -CUDART_INF_F);
+            mt = fmaxf(mt, vis ? fmaf(s, qscale, ns[128 + 16 * hh + i]) : -CUDART_INF_F);
           }
         }
       }
@@ -542,33 +570,40 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
           }
         }
       }
-      const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
+      const float m_neg = m_run == -CUDART_INF_F ? 0.f : -m_run;
       float lsum = 0.f;
       const float4* vn4 = reinterpret_cast<const float4*>(ns + 64);
+      // (two instances of the loop: inside the visible range of every row of the warp there is nothing
+      //  to select, which saves two instructions per column)
+      auto exp_phase = [&](auto inner_tag) {
+        constexpr bool INNER = decltype(inner_tag)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {  // 16 tokens = 8 columns of P at a time
-        uint32_t h[8], lw[8];
+        for (int c = 0; c < 2; ++c) {  // 16 tokens = 8 columns of P at a time
+          uint32_t h[8], lw[8];
 #pragma unroll
-        for (int e4 = 0; e4 < 4; ++e4) {
-          const float4 va = vn4[4 * c + e4];
-          const float vv[4] = {va.x, va.y, va.z, va.w};
+          for (int e4 = 0; e4 < 4; ++e4) {
+            const float4 va = vn4[4 * c + e4];
+            const float vv[4] = {va.x, va.y, va.z, va.w};
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int t = 16 * c + 4 * e4 + 2 * e;
-            const float e0 = ex2_approx(sc[t] - m_use), e1 = ex2_approx(sc[t + 1] - m_use);
-            lsum += e0 + e1;
-            // (a hidden column has e = 0; its value norm may be anything, so select instead of multiply)
-            const float v0 = (inner || sc[t] != -CUDART_INF_F) ? e0 * vv[2 * e] : 0.f;
-            const float v1 = (inner || sc[t + 1] != -CUDART_INF_F) ? e1 * vv[2 * e + 1] : 0.f;
-            const __half2 hp = __floats2half2_rn(v0, v1);
-            const float2 hf2 = __half22float2(hp);
-            h[2 * e4 + e] = *reinterpret_cast<const uint32_t*>(&hp);
-            if (!FAST) lw[2 * e4 + e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
+            for (int e = 0; e < 2; ++e) {
+              const int t = 16 * c + 4 * e4 + 2 * e;
+              const float e0 = ex2_approx(fmaf(sc[t], qscale, m_neg)), e1 = ex2_approx(fmaf(sc[t + 1], qscale, m_neg));
+              lsum += e0 + e1;
+              // (a hidden column has e = 0; its value norm may be anything, so select instead of multiply)
+              const float v0 = (INNER || sc[t] != -CUDART_INF_F) ? e0 * vv[2 * e] : 0.f;
+              const float v1 = (INNER || sc[t + 1] != -CUDART_INF_F) ? e1 * vv[2 * e + 1] : 0.f;
+              const __half2 hp = __floats2half2_rn(v0, v1);
+              const float2 hf2 = __half22float2(hp);
+              h[2 * e4 + e] = *reinterpret_cast<const uint32_t*>(&hp);
+              if (!FAST) lw[2 * e4 + e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
+            }
           }
+          tmem_st8_nowait(lane_base + kColP + 16 * hf + 8 * c, h);
+          if (!FAST) tmem_st8_nowait(lane_base + kColPlo + 16 * hf + 8 * c, lw);
         }
-        tmem_st8_nowait(lane_base + kColP + 16 * hf + 8 * c, h);
-        if (!FAST) tmem_st8_nowait(lane_base + kColPlo + 16 * hf + 8 * c, lw);
-      }
+      };
+      if (inner) exp_phase(std::true_type{});
+      else exp_phase(std::false_type{});
       tmem_st_wait();
       l_run += lsum;  // (this thread's half of the row sum)
       PF_STAMP(j, 5);
