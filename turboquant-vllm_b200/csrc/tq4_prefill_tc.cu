@@ -18,11 +18,13 @@
 // loads and stores): with Q and P in shared memory the MMAs alone read 224 KB per tile, now 96 KB.
 // At the end the normalised rows (still rotated) and their log-sum-exp go to the scratch in the
 // layout of one dense partial per row; the merge kernel un-rotates and stores them.
-// Warps 0-7 own the S / O rows, two threads per row (softmax, rescale, epilogue); warps 8-15
-// dequantise the next tile into the other K~ / V~ buffer meanwhile (keys first, so that the next
-// scores can be issued early; then the values) and one thread of warp 8 issues the TMA copies and
-// the MMAs.  (A seventeenth warp for the issuing alone was tried: five warps on one scheduler cut
-// the register budget to 96 and the loop ran no faster.)  Every wait is bounded.
+// The first 4 * kTPR warps own the S / O rows, kTPR threads per row (softmax, rescale, epilogue; kTPR = 2:
+// with four threads per row the softmax part shortens but the 24 warps slow the dequantisation down
+// more); the next eight warps dequantise the following tile into the other K~ / V~ buffer meanwhile
+// (keys first, so that the next scores can be issued early; then the values).  One thread of the first
+// of them issues the MMAs; one thread of each of the last four issues the TMA copies of one page.
+// (A warp for the issuing alone was tried: five warps on one scheduler cut the register budget to 96
+// and the loop ran no faster.)  Every wait is bounded.
 #include <cuda.h>
 #include <math_constants.h>
 
@@ -40,8 +42,8 @@ __device__ long long g_ptrace[4][64][16];
 #define PF_STAMP(j, e)                                                                              \
   do {                                                                                              \
     if (blockIdx.x == 40 && blockIdx.y == 3 && lane == 0 && (j) < 64 &&                             \
-        (warp == 0 || warp == 4 || warp == 8 || warp == 15))                                        \
-      g_ptrace[warp == 0 ? 0 : warp == 4 ? 1 : warp == 8 ? 2 : 3][j][e] = clock64();                \
+        (warp == 0 || warp == 4 || warp == TQ4_PREFILL_TPR * 4 || warp == TQ4_PREFILL_TPR * 4 + 7))       \
+      g_ptrace[warp == 0 ? 0 : warp == 4 ? 1 : warp == TQ4_PREFILL_TPR * 4 ? 2 : 3][j][e] = clock64();  \
   } while (0)
 #else
 #define PF_STAMP(j, e) do {} while (0)
@@ -50,11 +52,17 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kBN = 64;                 // tokens per tile
-constexpr int kSmx = 256;                 // warps 0-7: softmax (two threads per row)
-constexpr int kDeq = 256;                 // warps 8-15: dequantise
+#ifndef TQ4_PREFILL_TPR
+#define TQ4_PREFILL_TPR 2
+#endif
+constexpr int kTPR = TQ4_PREFILL_TPR;     // softmax threads per row (2 or 4)
+constexpr int kCols = kBN / kTPR;         // score columns per softmax thread
+constexpr int kOCols = kD / kTPR;         // output columns per softmax thread
+constexpr int kSmx = 128 * kTPR;          // softmax warps 0 .. 4 kTPR - 1
+constexpr int kDeq = 256;                 // then eight warps that dequantise
 constexpr int kThreads = kSmx + kDeq;
 constexpr int kIssueWarp = kSmx / 32;     // one thread of warp 8 also issues the MMAs,
-constexpr int kCopyWarp = kThreads / 32 - 1;  // one of warp 15 the TMA copies (either job delays its warp)
+constexpr int kCopyWarp = kThreads / 32 - 1;  // the last four warps issue the TMA copies, one page each
 // tensor memory (all 512 columns: one CTA per SM): S (two buffers) [0, 64) and [64, 128), O [128, 256),
 // Q hi [256, 320) and lo [320, 384) (128 dims, two per column), P hi [384, 416) and lo [416, 448)
 constexpr uint32_t kTmemCols = 512;
@@ -286,7 +294,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   const int my_r = row / G, my_g = row % G;
   float* xchg = reinterpret_cast<float*>(sm + kOffXchg);
   float qv[32];
-  {
+  if (tid < 512) {  // (sixteen warps: four per lane quadrant, 32 dims each)
     const int part = warp >> 2;
     float qmax = 0.f;
     if (my_r < nrows) {
@@ -314,7 +322,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   // max|q| * sm_scale * log2(e) / alpha_k: the factor between a stored dot product and the score in
   // the log2 domain (at least the smallest normal number, so that a hidden score, -inf, times it stays -inf)
   const float qscale = fmaxf(qmax * (a.scale_log2e / a.lut_scale_k), 1.17549435e-38f);
-  {
+  if (tid < 512) {
     const int part = warp >> 2;
     const float inv = qmax > 0.f ? 1.f / qmax : 0.f;
 #pragma unroll
@@ -335,12 +343,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();  // Q is in tensor memory; the exchange area is free again
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  // ---- softmax threads: warps 0-7; row = TMEM lane = 32 * (warp & 3) + lane, column half = warp >> 2
+  // ---- softmax threads: row = TMEM lane = 32 * (warp & 3) + lane, column group = warp >> 2 -----------
   const bool smx = tid < kSmx;
-  const int hf = (warp >> 2) & 1;
+  const int qt = (warp >> 2) % kTPR;  // which kCols score columns / kOCols output columns of the row
   const bool row_live = smx && my_r < nrows;
-  // the two threads of a row sit in warps w and w + 4: a 64-thread named barrier per warp pair
-  auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory"); };
+  // the threads of a row sit in warps w, w + 4, ...: a named barrier per such group of warps
+  auto pair_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + (warp & 3)), "n"(32 * kTPR) : "memory"); };
   const int kv_lo = row_live ? p.kv_start[lr0 + my_r] : 0;
   const int kv_hi = row_live ? p.kv_end[lr0 + my_r] : 0;
   // keys the block needs: rows are in query order, ranges move forward with the row
@@ -360,11 +368,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
 #pragma unroll
     for (int pg = 0; pg < 4; ++pg) {
       const int pos = t0 + 16 * pg;
-      // (a volatile load: the ids are used an iteration later, and an ordinary load gets moved down to
-      //  its use, where the copy-issuing warp then waits a global round trip in every iteration)
-      int id = 0;
-      if (pos < blk_hi) asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(id) : "l"(bt + (pos >> bs_shift)));
-      blk[pg] = id;  // out-of-range ids read zeros (TMA bounds)
+      // A volatile load straight into its register, from a clamped address instead of under a
+      // condition: the ids are used an iteration later; an ordinary load gets moved down to its use, and
+      // a select after the load makes the warp wait a global round trip right here, in every iteration.
+      // (Pages past the block's last key are never issued, whatever id is read for them.)
+      const int pos_c = min(pos, max(blk_hi - 1, 0));
+      asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(blk[pg]) : "l"(bt + (pos_c >> bs_shift)));
     }
   };
   auto issue_tile = [&](int j, const int (&blks)[4]) {
@@ -391,7 +400,11 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
     const unsigned char* stg = sm + kOffStage + (j & 1) * kStageBytes;
     const uint32_t kv_off = (uint32_t)(j & 1) * 16384u;
     for (int item = item_lo + t; item < item_hi; item += nt) {
-      const int u = item >> 8, tok = (item >> 2) & 63, seg = item & 3;
+      // 32 consecutive items = 8 tokens x 4 segments; a quarter warp takes 4 tokens x the 2 segments of
+      // one K-block, so that its eight 16-byte stores below (chunk ^ (token & 7)) fall into eight
+      // different bank groups (token-major order made every store a two-way conflict)
+      const int r8 = item & 7, q4 = (item >> 3) & 3;
+      const int u = item >> 8, tok = ((item >> 5) & 7) * 8 + 4 * (q4 & 1) + (r8 & 3), seg = (r8 >> 2) + 2 * (q4 >> 1);
       const uint4 pk = *reinterpret_cast<const uint4*>(stg + (tok >> 4) * 2048 + u * 1024 + (tok & 15) * 64 + seg * 16);
       const uint32_t* lut = reinterpret_cast<const uint32_t*>(sm + kOffLut) + u * 256 * kLutCopies + lane;
       const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
@@ -411,6 +424,24 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       ns[t] = kn;
       ns[64 + t] = vn;
       ns[128 + t] = fmaxf(lg2_approx(vn), -30.f);
+    }
+  };
+  // one page of tile j by the calling thread; the thread with `first` also posts the byte count of
+  // the whole tile (the stage's barrier has one pending arrival, that one: bytes that land before it
+  // cannot complete the phase)
+  auto issue_page = [&](int j, int pg, int blk, bool first) {
+    const uint32_t st = base + kOffStage + (uint32_t)(j & 1) * kStageBytes, bar = bar_t0 + 8 * (j & 1);
+    const int t0 = t_first + j * kBN;
+    if (first) {
+      int npages = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) npages += (t0 + 16 * q < blk_hi) ? 1 : 0;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(npages * 2560) : "memory");
+    }
+    const int pos = t0 + 16 * pg;
+    if (pos < blk_hi) {
+      tma_load_4d(st + pg * 2048, &tm_idx, x_idx, pos & bs_mask, 0, blk, bar);
+      tma_load_4d(st + 8192 + pg * 512, &tm_norm, x_nrm, pos & bs_mask, 0, blk, bar);
     }
   };
   // descriptors of the operand regions; a byte offset inside a region adds offset / 16 to the
@@ -454,21 +485,13 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   }
 
   int blk_next[4] = {0, 0, 0, 0};  // (copy warp) pages of the tile after next
-  if (warp == kCopyWarp && n_tiles > 2) load_blks(2, blk_next);
+  if (warp >= kCopyWarp - 3 && n_tiles > 2) load_blks(2, blk_next);
   // ---- per tile: warps 0-7 turn S_j into P_j while warps 8-15 dequantise tile j+1 and issue S_{j+1};
   //      then one thread issues O += P_j V~_j --------------------------------------------------------------
   bool gave_up = n_tiles > 0 && s_info[3] != 0;  // a bounded wait ran out somewhere in the block
   for (int j = 0; j < n_tiles && !gave_up; ++j) {
     const int t0 = t_first + j * kBN;
     bool ok = true;
-    // The packed stage of tile j was dequantised during the previous iteration: tile j + 2 goes into
-    // it now, a whole iteration before its turn (its page ids were read an iteration ago; those of
-    // tile j + 3 are read now).
-    if (warp == kCopyWarp) {
-      if (j + 2 < n_tiles && elect_one_sync()) issue_tile(j + 2, blk_next);
-      __syncwarp();
-      if (j + 3 < n_tiles) load_blks(j + 3, blk_next);
-    }
     PF_STAMP(j, 0);
     if (!smx) {
       if (j + 1 < n_tiles) {
@@ -489,6 +512,17 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
           issue_s(j + 1);
         }
         PF_STAMP(j, 3);
+        // The packed stage of tile j was dequantised during the previous iteration: tile j + 2 goes into
+        // it, most of an iteration before its turn (its page ids were read an iteration ago; those of
+        // tile j + 3 are read now).  Issuing the eight copies takes the thread 1 000 - 2 000 cycles: here
+        // they delay only its warp's share of the values; before the keys they would delay S_{j+1}.
+        // Four warps issue one page each: a copy instruction costs its thread ~190 cycles.
+        if (warp >= kCopyWarp - 3) {
+          const int pg = warp - (kCopyWarp - 3);
+          if (j + 2 < n_tiles && elect_one_sync()) issue_page(j + 2, pg, blk_next[pg], pg == 0);
+          __syncwarp();
+          if (j + 3 < n_tiles) load_blks(j + 3, blk_next);
+        }
         // the values of tile j + 1 (only O += P V~ of the next iteration reads them): V~ buffer
         // (j+1) & 1 was read by the MMAs of tile j-1
         if (j >= 1) ok = bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1)) && ok;
@@ -500,23 +534,24 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1)));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       PF_STAMP(j, 1);
-      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + 32 * hf;
+      const float* ns = reinterpret_cast<const float*>(sm + kOffNorm) + (j & 1) * 192 + kCols * qt;
       // sc[i] = dot product of column i times its key norm (-inf = not visible); the score in the log2
       // domain is sc[i] * qscale.  Tiles strictly inside the visible range of every row of the warp
       // take the short path without per-element masks.
-      float sc[32];
+      float sc[kCols];
       float mt = -CUDART_INF_F;
       const bool inner = __all_sync(0xffffffffu, ok && row_live && t0 >= kv_lo && t0 + kBN <= kv_hi);
       // 16 columns at a time (short register lifetimes); the second load is in flight while the first
       // half is processed
-      uint32_t vbuf[2][16];
+      constexpr int NH = kCols / 16;
+      uint32_t vbuf[NH][16];
       if (ok) {
-        tmem_ld16(lane_base + kColS + 64 * (j & 1) + 32 * hf, vbuf[0]);
-        tmem_ld16_nowait(lane_base + kColS + 64 * (j & 1) + 32 * hf + 16, vbuf[1]);
+        tmem_ld16(lane_base + kColS + 64 * (j & 1) + kCols * qt, vbuf[0]);
+        if (NH == 2) tmem_ld16_nowait(lane_base + kColS + 64 * (j & 1) + kCols * qt + 16, vbuf[NH - 1]);
       }
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        if (hh == 1) tmem_ld_wait16(vbuf[1]);
+      for (int hh = 0; hh < NH; ++hh) {
+        if (hh == 1) tmem_ld_wait16(vbuf[NH - 1]);
         uint32_t (&v)[16] = vbuf[hh];
         const float4* kn4 = reinterpret_cast<const float4*>(ns + 16 * hh);
         const float4* lg4 = reinterpret_cast<const float4*>(ns + 128 + 16 * hh);
@@ -535,7 +570,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int pos = t0 + 32 * hf + 16 * hh + i;
+            const int pos = t0 + kCols * qt + 16 * hh + i;
             const bool vis = ok && row_live && pos >= kv_lo && pos < kv_hi;
             const float s = vis ? __uint_as_float(v[i]) * ns[16 * hh + i] : -CUDART_INF_F;
             sc[16 * hh + i] = s;
@@ -545,9 +580,10 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       }
       // the row's maximum over both halves (the decisions below must agree in its two threads)
       PF_STAMP(j, 2);
-      xchg[hf * 128 + row] = mt;
+      xchg[qt * 128 + row] = mt;
       pair_sync();
-      mt = fmaxf(mt, xchg[(hf ^ 1) * 128 + row]);
+#pragma unroll
+      for (int o = 1; o < kTPR; ++o) mt = fmaxf(mt, xchg[((qt + o) % kTPR) * 128 + row]);
       PF_STAMP(j, 3);
       // P and O are still in use by the MMAs of tile j-1
       if (j >= 1) ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_o, (uint32_t)((j - 1) & 1))) && ok;
@@ -561,12 +597,12 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         if (bump) { m_run = mt; l_run *= alpha; }
         if (!o_zero && ok) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {  // this thread's 64 of the row's 128 columns
+          for (int q = 0; q < kOCols / 16; ++q) {  // this thread's share of the row's 128 columns
             uint32_t v[16];
-            tmem_ld16(lane_base + kColO + 64 * hf + 16 * q, v);
+            tmem_ld16(lane_base + kColO + kOCols * qt + 16 * q, v);
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st16(lane_base + kColO + 64 * hf + 16 * q, v);
+            tmem_st16(lane_base + kColO + kOCols * qt + 16 * q, v);
           }
         }
       }
@@ -578,7 +614,7 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
       auto exp_phase = [&](auto inner_tag) {
         constexpr bool INNER = decltype(inner_tag)::value;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {  // 16 tokens = 8 columns of P at a time
+        for (int c = 0; c < kCols / 16; ++c) {  // 16 tokens = 8 columns of P at a time
           uint32_t h[8], lw[8];
 #pragma unroll
           for (int e4 = 0; e4 < 4; ++e4) {
@@ -598,8 +634,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
               if (!FAST) lw[2 * e4 + e] = pack_h2(v0 - hf2.x, v1 - hf2.y);  // the fp16 rounding of the weights is recovered by a second term
             }
           }
-          tmem_st8_nowait(lane_base + kColP + 16 * hf + 8 * c, h);
-          if (!FAST) tmem_st8_nowait(lane_base + kColPlo + 16 * hf + 8 * c, lw);
+          tmem_st8_nowait(lane_base + kColP + (kCols / 2) * qt + 8 * c, h);
+          if (!FAST) tmem_st8_nowait(lane_base + kColPlo + (kCols / 2) * qt + 8 * c, lw);
         }
       };
       if (inner) exp_phase(std::true_type{});
@@ -637,30 +673,31 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
   const bool dead = s_info[3] != 0;
   if (smx) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    xchg[hf * 128 + row] = l_run;  // the row sum = the two halves
+    xchg[qt * 128 + row] = l_run;  // the row sum = the shares of its threads
     pair_sync();
-    l_run += xchg[(hf ^ 1) * 128 + row];
+#pragma unroll
+    for (int o = 1; o < kTPR; ++o) l_run += xchg[((qt + o) % kTPR) * 128 + row];
     const bool have = !dead && !o_zero && l_run > 0.f;
     const float inv = have ? 1.f / (a.lut_scale_v * l_run) : 0.f;
     const int64_t vec = row_live ? (int64_t)(lr0 + my_r) * sh.Hq + kvh * G + my_g : 0;
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {  // this thread's 64 columns
+    for (int q = 0; q < kOCols / 32; ++q) {  // this thread's columns
       uint32_t v[32];
       if (!o_zero && !dead) {
-        tmem_ld32(lane_base + kColO + 64 * hf + 32 * q, v);
+        tmem_ld32(lane_base + kColO + kOCols * qt + 32 * q, v);
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0u;
       }
       if (row_live) {
-        float4* dst = reinterpret_cast<float4*>(p.part_o + vec * kD + 64 * hf + 32 * q);
+        float4* dst = reinterpret_cast<float4*>(p.part_o + vec * kD + kOCols * qt + 32 * q);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           dst[i] = make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
                                __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
       }
     }
-    if (row_live && hf == 0)
+    if (row_live && qt == 0)
       p.part_m[vec] = have ? (m_run + lg2_approx(l_run)) * 0.6931471805599453f : -CUDART_INF_F;
   }
   if (dead && tid == 0 && a.err_flag) atomicOr(a.err_flag, TQ4_DEV_TIMEOUT);
