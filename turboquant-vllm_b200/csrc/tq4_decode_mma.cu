@@ -257,7 +257,8 @@ struct MmaCfg {
 template <int D>
 struct RotCfg {
   static constexpr int KS = D / 16;                      // k-steps
-  static constexpr int NQ = D / 32;                      // tasks along N (4 n-blocks of 8 outputs each)
+  static constexpr int NBT = 2;                          // n-blocks (of 8 outputs) per task
+  static constexpr int NQ = D / (8 * NBT);               // tasks along N: small tasks spread evenly over 16 warps
   static constexpr int PITCH = 2 * D + (D == 96 ? 32 : 0);  // bytes per row of a Pi half (fp16)
   static constexpr bool XOR = D != 96;                   // 8-byte chunks XOR-swizzled by 4 * (row & 3)
   static constexpr int LO_BASE = D * PITCH;              // the lo array follows the hi array
@@ -473,7 +474,7 @@ __device__ __forceinline__ void load_q4(const void* q, int dtype, int64_t idx, b
 // They are handled in GROUPS of 16.  fused_prep_group (one warp per group) turns a group into the
 // A operand of the product -- 16 x D fp16 hi and lo tiles in the warp's (still idle) ring memory,
 // each vector scaled by a power of two into [1, 2) -- plus 16 bytes of bookkeeping per vector;
-// fused_mma_tasks multiplies (group, 32 output coordinates) tasks, handed out to all warps round
+// fused_mma_task multiplies (group, 16 output coordinates) tasks, handed out to all warps round
 // robin.  Both are short rolled loops: code that runs once per launch costs its instruction
 // fetches.  Lane (g, c) owns, per k-step s, the four contiguous elements 16 s + 4 c .. + 3 of
 // vectors g and g + 8 (the k order inside a step is a permutation applied to both operands).
@@ -606,7 +607,7 @@ __device__ __forceinline__ void fused_prep_group(const AttnArgs& a, const Compre
 }
 
 // One task: the 16 vectors of the group staged at `mem` times the output coordinates
-// [32 nq, 32 nq + 32) of Pi (hi / lo fp16 at `tab`), two n-blocks at a time.
+// [16 nq, 16 nq + 16) of Pi (hi / lo fp16 at `tab`).
 template <int D>
 __device__ __forceinline__ void fused_mma_task(const AttnArgs& a, const CompressArgs& w, const float* s_bounds,
                                                uint32_t tab, uint32_t mem, int nq, int lane) {
@@ -631,12 +632,12 @@ __device__ __forceinline__ void fused_mma_task(const AttnArgs& a, const Compress
   // chunk offset of k-step s is the same for all of them
   const uint32_t gx = R::XOR ? (uint32_t)(g & 3) : 0u;
   const uint32_t a_row = mem + g * R::PITCH + 8 * c;
-  // the four n-blocks of the task advance together, each with a main (hi * hi) and a correction
-  // (lo * hi + hi * lo) accumulator: eight independent chains of 8 / 16 dependent MMAs
-  const uint32_t b_row = tab + (nq * 32 + g) * R::PITCH + 8 * c;
-  float acc[4][4], cor[4][4];
+  // the n-blocks of the task advance together, each with a main (hi * hi) and a correction
+  // (lo * hi + hi * lo) accumulator: independent chains of 8 / 16 dependent MMAs
+  const uint32_t b_row = tab + (nq * 8 * R::NBT + g) * R::PITCH + 8 * c;
+  float acc[R::NBT][4], cor[R::NBT][4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+  for (int j = 0; j < R::NBT; ++j)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = cor[j][e] = 0.f;
 #pragma unroll 2
@@ -648,7 +649,7 @@ __device__ __forceinline__ void fused_mma_task(const AttnArgs& a, const Compress
     lds_words<8>(a_row + ko + GroupMem<D>::kHalf, al0);
     lds_words<8>(a_row + ko + GroupMem<D>::kHalf + 8 * R::PITCH, al1);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < R::NBT; ++j) {
       uint32_t bh[2], bl[2];
       lds_words<8>(b_row + ko + j * 8 * R::PITCH, bh);
       lds_words<8>(b_row + ko + j * 8 * R::PITCH + R::LO_BASE, bl);
@@ -658,14 +659,14 @@ __device__ __forceinline__ void fused_mma_task(const AttnArgs& a, const Compress
     }
   }
 #pragma unroll 1
-  for (int j = 0; j < 4; ++j) {
-    const int n0 = (nq * 4 + j) * 8 + 2 * c;  // C columns of this lane: coordinates n0 (even), n0 + 1
+  for (int j = 0; j < R::NBT; ++j) {
+    const int n0 = (nq * R::NBT + j) * 8 + 2 * c;  // C columns of this lane: coordinates n0 (even), n0 + 1
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       // (indexing the accumulators with the rolled j would spill them: select instead)
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj)
+      for (int jj = 0; jj < R::NBT; ++jj)
         if (jj == j) {
           y0 = (acc[jj][2 * hf] + cor[jj][2 * hf]) * inv_scale[hf];
           y1 = (acc[jj][2 * hf + 1] + cor[jj][2 * hf + 1]) * inv_scale[hf];
