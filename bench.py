@@ -47,9 +47,9 @@ FALLBACK_HBM_GBS = 6650.0
 # the N = 1 workload.  A STORED figure from an ncu capture (the timed run cannot measure DRAM
 # traffic): it is reported together with the name of the capture it comes from and only while the
 # kernel build named there is the one that runs; otherwise `traffic` is null.
-NCU_TRAFFIC = {"bytes": 309819136,  # dram__bytes_read.sum 303 762 432 + dram__bytes_write.sum 6 056 704
-               "capture": "profiles/attention_mma_kernel_b64_ctx4096_ncu_full.md (attention kernel with the "
-                          "fused prologue, one launch, ncu --set full)"}
+NCU_TRAFFIC = {"bytes": 308781824,  # dram__bytes_read.sum 304 016 384 + dram__bytes_write.sum 4 765 440
+               "capture": "profiles/attention_mma_kernel_b64_ctx4096_ncu_full.md (form A: attention kernel "
+                          "behind the prologue kernel, one launch, ncu --set full)"}
 
 
 def measured_peak_gbs():
@@ -303,9 +303,15 @@ def run_ours(args, rank, world, device):
     alg_bytes = batch * CTX * hkv * (D + 8)  # 136 B per token per KV head at D=128
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (avg["attention"] * 1e-3) / 1e9
-    # the stored capture is of the 8-heads-per-GPU layout with the prologue inside the kernel
+    # kernels per step: write + prologue + attention + combine as separate calls; prologue + attention +
+    # combine for up to 64 query rows; attention (prologue inside) + combine above that
+    forced = os.environ.get("TQ4_FUSED_PROLOGUE")
+    fused_step = (forced != "0" and not os.environ.get("TQ4_NO_FUSED_PROLOGUE")) and (forced == "1" or batch > 64) and batch <= 512
+    launches_per_step = 4 if args.separate_write else (2 if fused_step else 3)
+    # the stored capture is of the 8-heads-per-GPU layout with the prologue kernel in front (what the
+    # library picks at 64 query rows)
     traffic_known = (alg_bytes == 285212672 and world == 1 and not args.emulate_world and not args.separate_write
-                     and not os.environ.get("TQ4_NO_FUSED_PROLOGUE") and not args.row_bytes)
+                     and not fused_step and not args.row_bytes)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4),
                 "traffic": NCU_TRAFFIC["bytes"] if traffic_known else None,
@@ -414,7 +420,7 @@ def run_ours(args, rank, world, device):
         "compress_mtok_s": round(compress_mtok_s, 3),
         "compress_config": f"{nt} tokens x {hkv} KV heads, K and V, bf16 -> paged cache, one launch",
         "prefill": prefill,
-        "roofline": roofline, "e2e": e2e, "gpu_launches": (4 if args.separate_write else 3) * args.steps,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_bf16_baseline:

@@ -49,9 +49,19 @@ def _run(ops, mode, **kw):
         raise
 
 
+
+@pytest.fixture(params=["prologue_kernel", "fused_prologue"])
+def prologue(request, monkeypatch):
+    """Decode calls run both ways: tile plan, query rotation and the step's cache write in a prologue kernel
+    in front of the attention kernel, or inside it (the library picks by batch size; TQ4_FUSED_PROLOGUE
+    forces one)."""
+    monkeypatch.setenv("TQ4_FUSED_PROLOGUE", "1" if request.param == "fused_prologue" else "0")
+    return request.param
+
+
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("tag", ["k4v4", "k4v3", "d96", "d64g7", "k4v4h4"])
-def test_decode_golden(ops, golden, tag, mode):
+def test_decode_golden(ops, golden, tag, mode, prologue):
     """Decode against the output the reference's dequantize + fp32 SDPA produced."""
     g = golden("paged.npz")
     d, h_kv, h_q, kb, vb, bs = [int(x) for x in g[f"{tag}_meta"]]
@@ -81,7 +91,7 @@ def test_prefill_golden(ops, golden, tag, window, mode):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("seq_lens", [[1], [15], [16], [17], [47], [32, 17, 48], [0, 5, 0], [300, 1, 64, 129]])
-def test_decode_seq_len_edges(ops, seq_lens, mode):
+def test_decode_seq_len_edges(ops, seq_lens, mode, prologue):
     pr = Prims(128)
     p = pr.cuda()
     h_kv, h_q, d, bs = 8, 32, 128, 16
@@ -104,7 +114,7 @@ def test_decode_seq_len_edges(ops, seq_lens, mode):
     (24, 2, 128, 16, False), (4, 1, 128, 16, True), (8, 1, 64, 16, True), (4, 1, 128, 32, False),
     (4, 1, 128, 16, "dense"), (8, 2, 128, 16, "dense"), (8, 1, 64, 16, "dense"), (3, 3, 96, 16, "dense"),
 ])
-def test_decode_shapes(ops, hq, hkv, d, bs, padded, mode):
+def test_decode_shapes(ops, hq, hkv, d, bs, padded, mode, prologue):
     pr = Prims(d)
     p = pr.cuda()
     seq_lens = [70, 33, 129]
@@ -119,7 +129,7 @@ def test_decode_shapes(ops, hq, hkv, d, bs, padded, mode):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_decode_16bit_output_is_rounded_fp32(ops, dtype, mode):
+def test_decode_16bit_output_is_rounded_fp32(ops, dtype, mode, prologue):
     pr = Prims(128)
     p = pr.cuda()
     seq_lens = [200, 31]
@@ -179,7 +189,7 @@ def test_prefill_tensor_core_kernel(ops, hq, hkv, bs, vbits):
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_seq_len_beyond_block_table_row_is_cut_and_flagged(ops, mode):
+def test_seq_len_beyond_block_table_row_is_cut_and_flagged(ops, mode, prologue):
     """A seq_len that needs more pages than a block-table row holds is cut at the row's capacity and
     reported (TQ4_DEV_BAD_BLOCK); nothing is read past the row."""
     pr = Prims(128)
@@ -262,7 +272,7 @@ def test_int8_prefill_name_single_sequence(ops):
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_bad_block_id_sets_flag_not_fault(ops, mode):
+def test_bad_block_id_sets_flag_not_fault(ops, mode, prologue):
     pr = Prims(128)
     p = pr.cuda()
     case = build_paged_case([40], 8, 128, 16, pr, seed=3)
@@ -278,7 +288,7 @@ def test_bad_block_id_sets_flag_not_fault(ops, mode):
     assert torch.isfinite(out).all()
 
 
-def test_lse_and_combine_partials(ops):
+def test_lse_and_combine_partials(ops, prologue):
     """Split every sequence's keys over two 'shards', produce (o_rot, lse) per shard with the fused
     kernel, merge with tq4_combine_partials: equals the single-pass result and the oracle."""
     pr = Prims(96)
@@ -353,7 +363,7 @@ def test_decode_full_size_properties(ops, mode):
     (32, 8, 128, 16, 4, 4, torch.bfloat16), (8, 2, 64, 32, 4, 3, torch.float16),
     (12, 4, 96, 16, 4, 4, torch.float32), (8, 4, 256, 16, 4, 4, torch.bfloat16),
 ])
-def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, vbits, dtype, mode, monkeypatch):
+def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, vbits, dtype, mode, monkeypatch, prologue):
     """One decode step as a single call against tq4_write_paged + attention as two calls.
 
     Decode calls at head_dim <= 128 compress the new tokens inside the attention kernel, rotating on
@@ -418,9 +428,10 @@ def test_write_and_attention_equals_separate_calls(ops, hq, hkv, d, bs, kbits, v
         _check(out_b, ref)
 
 
-def test_fused_step_flags_a_slot_that_is_not_the_last_position(ops):
+def test_fused_step_flags_a_slot_that_is_not_the_last_position(ops, monkeypatch):
     """The one-call decode step orders the write of token i before the read of sequence i's last
     tile only; a slot elsewhere is still written, and reported through TQ4_DEV_WRITE_ORDER."""
+    monkeypatch.setenv("TQ4_FUSED_PROLOGUE", "1")
     from tests.helpers import index_mismatch
     from turboquant_vllm import _native as nv
 

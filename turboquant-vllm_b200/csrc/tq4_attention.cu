@@ -1145,9 +1145,17 @@ static int attention_impl(
   a.sh.span_ctas = use_mma ? ctas * a.sh.TPC : ctas;
   a.sh.part_tpc = part_tpc;
   cudaStream_t st = (cudaStream_t)stream;
-  static const bool no_fused = getenv("TQ4_NO_FUSED_PROLOGUE") != nullptr;
+  // Decode calls of up to kFusedMaxRows rows can plan, rotate and write inside the attention kernel
+  // (two launches per step) or in a prologue kernel in front of it (three).  Measured on B200, graph
+  // replays, 32 q / 8 kv heads, head_dim 128: the prologue kernel wins up to batch 64 x 4096 tokens
+  // (92.5 against 92.7 us there, 50.1 against 53.4 at batch 16), the fused form above it (155.7 against
+  // 160.4 us at batch 128, 173.9 against 177.4 at batch 256 x 2048).  TQ4_FUSED_PROLOGUE=1 / 0 forces it.
+  int force_fused = -1;
+  if (const char* e = getenv("TQ4_FUSED_PROLOGUE")) force_fused = atoi(e) != 0;
+  if (getenv("TQ4_NO_FUSED_PROLOGUE") != nullptr) force_fused = 0;
+  const bool want_fused = force_fused >= 0 ? force_fused != 0 : num_rows > kFusedMinRows;
   a.fused = use_mma && !use_prefill && query_start_loc == nullptr && num_rows <= kFusedMaxRows &&
-            head_dim <= 128 && !no_fused;
+            head_dim <= 128 && want_fused;
 
   for (int64_t r0 = 0; r0 < num_rows; r0 += kMaxRowsPerLaunch) {
     a.sh.rows = (int)((num_rows - r0) < kMaxRowsPerLaunch ? (num_rows - r0) : kMaxRowsPerLaunch);
