@@ -304,12 +304,12 @@ def run_ours(args, rank, world, device):
     peak, peak_kind = measured_peak_gbs()
     achieved = alg_bytes / (avg["attention"] * 1e-3) / 1e9
     # kernels per step: write + prologue + attention + combine as separate calls; prologue + attention +
-    # combine for up to 64 query rows; attention (prologue inside) + combine above that
+    # combine while rows x KV heads <= 512; attention (prologue inside) + combine above that
     forced = os.environ.get("TQ4_FUSED_PROLOGUE")
-    fused_step = (forced != "0" and not os.environ.get("TQ4_NO_FUSED_PROLOGUE")) and (forced == "1" or batch > 64) and batch <= 512
+    fused_step = (forced != "0" and not os.environ.get("TQ4_NO_FUSED_PROLOGUE")) and (forced == "1" or batch * hkv > 512) and batch <= 512
     launches_per_step = 4 if args.separate_write else (2 if fused_step else 3)
     # the stored capture is of the 8-heads-per-GPU layout with the prologue kernel in front (what the
-    # library picks at 64 query rows)
+    # library picks at 64 query rows x 8 KV heads)
     traffic_known = (alg_bytes == 285212672 and world == 1 and not args.emulate_world and not args.separate_write
                      and not fused_step and not args.row_bytes)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

@@ -194,8 +194,9 @@ int tq4_paged_attention(const void* q, int q_dtype, int64_t num_rows, int num_se
  * (cache_block_stride == block_size * cache_token_stride), which makes the flat slot
  * s = block * block_size + offset of slot_mapping address row s at cache + s * cache_token_stride.
  * n_tokens == 0 reduces to tq4_paged_attention, num_rows == 0 to tq4_write_paged.
- * Decode calls (query_start_loc == NULL) of 65 to 512 rows at head_dim <= 128 run as TWO launches
- * (smaller ones too with TQ4_FUSED_PROLOGUE=1 in the environment; =0 turns the form off): the
+ * Decode calls (query_start_loc == NULL) of up to 512 rows at head_dim <= 128 with more than 512
+ * (row, KV head) pairs run as TWO launches (smaller ones too with TQ4_FUSED_PROLOGUE=1 in the
+ * environment; =0 turns the form off): the
  * attention kernel plans its tiles, rotates the queries and compresses the new tokens itself, then
  * the merge kernel.  There token i must be the newest token of sequence i, i.e.
  * slot_mapping[i] addresses position seq_lens[i] - 1 through block_table (what a decode step of a

@@ -1147,13 +1147,15 @@ static int attention_impl(
   cudaStream_t st = (cudaStream_t)stream;
   // Decode calls of up to kFusedMaxRows rows can plan, rotate and write inside the attention kernel
   // (two launches per step) or in a prologue kernel in front of it (three).  Measured on B200, graph
-  // replays, 32 q / 8 kv heads, head_dim 128: the prologue kernel wins up to batch 64 x 4096 tokens
-  // (92.5 against 92.7 us there, 50.1 against 53.4 at batch 16), the fused form above it (155.7 against
-  // 160.4 us at batch 128, 173.9 against 177.4 at batch 256 x 2048).  TQ4_FUSED_PROLOGUE=1 / 0 forces it.
+  // replays, head_dim 128, GQA 4: the prologue kernel wins while rows x KV heads <= 512 (8 KV heads:
+  // 92.5 against 92.7 us at batch 64 x 4096, 50.1 against 53.4 at batch 16; 4 / 2 / 1 KV heads with
+  // batch 128 / 256 / 512: 93.9 against 94.9, 100.5 against 103.0, 123.6 against 132.9 us), the fused
+  // form above (8 KV heads: 155.7 against 160.4 us at batch 128, 173.9 against 177.4 at batch 256 x
+  // 2048).  TQ4_FUSED_PROLOGUE=1 / 0 forces it.
   int force_fused = -1;
   if (const char* e = getenv("TQ4_FUSED_PROLOGUE")) force_fused = atoi(e) != 0;
   if (getenv("TQ4_NO_FUSED_PROLOGUE") != nullptr) force_fused = 0;
-  const bool want_fused = force_fused >= 0 ? force_fused != 0 : num_rows > kFusedMinRows;
+  const bool want_fused = force_fused >= 0 ? force_fused != 0 : num_rows * num_kv_heads > kFusedMinRowHeads;
   a.fused = use_mma && !use_prefill && query_start_loc == nullptr && num_rows <= kFusedMaxRows &&
             head_dim <= 128 && want_fused;
 

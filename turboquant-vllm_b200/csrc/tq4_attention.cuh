@@ -25,7 +25,7 @@ constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace siz
 constexpr int kMaxSms = 160;               // tensor-core kernel: one CTA per SM, one span per warp phase
 constexpr int kMaxRowsPerLaunch = 4096;    // larger query batches are processed in pieces
 constexpr int kFusedMaxRows = 512;         // decode calls up to this size plan and rotate inside the attention kernel
-constexpr int kFusedMinRows = 64;          // ... and above this size (below it the separate prologue kernel is faster)
+constexpr int kFusedMinRowHeads = 512;     // ... when rows x KV heads exceeds this (else the separate prologue kernel is faster)
 
 struct AttnPlan {
   float* q_rot;      // [rows][Hq][D] fp32, q * Pi^T
