@@ -20,6 +20,9 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
   const AttnPlan& p = a.plan;
   __shared__ int s_part[32];
   __shared__ int s_total;
+  __shared__ int s_max_tiles;  // tiles of the longest row
+  if (threadIdx.x == 0) s_max_tiles = 0;
+  __syncthreads();
   const int rows = sh.rows;
   int* s_tiles = s_work;        // [rows] tile count, then exclusive prefix
   int* s_slots = s_work + rows; // [rows] slot count, then exclusive prefix
@@ -89,14 +92,16 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
     return base;
   };
 
-  int local = 0;
+  int local = 0, row_max = 0;
   for (int r = r_lo; r < r_hi; ++r) {
     int seq, start, end;
     row_range(r, seq, start, end);
     const int nt = end > start ? (end + kTileTokens - 1) / kTileTokens - start / kTileTokens : 0;
     s_tiles[r] = nt;
     local += nt;
+    row_max = max(row_max, nt);
   }
+  if (row_max > 0) atomicMax(&s_max_tiles, row_max);
   int run = block_exclusive_scan(local);
   for (int r = r_lo; r < r_hi; ++r) {
     const int nt = s_tiles[r];
@@ -104,7 +109,7 @@ __device__ void build_plan(const AttnArgs& a, int* s_work) {
     run += nt;
   }
   const int total = s_total;
-  const int tps = max(1, (total + sh.span_ctas - 1) / sh.span_ctas);
+  const int tps = tiles_per_span(total, sh.span_ctas, s_max_tiles);
   __syncthreads();
   local = 0;
   for (int r = r_lo; r < r_hi; ++r) {

@@ -25,6 +25,16 @@ constexpr int kMaxCtasPerSlice = 148 * 4;  // upper bound used for workspace siz
 constexpr int kMaxSms = 160;               // tensor-core kernel: one CTA per SM, one span per warp phase
 constexpr int kMaxRowsPerLaunch = 4096;    // larger query batches are processed in pieces
 constexpr int kFusedMaxRows = 512;         // decode calls up to this size plan and rotate inside the attention kernel
+// A row is cut into at most this many spans (= partials the merge kernel has to fold for it): a call of
+// a few long rows would otherwise hand the merge kernel hundreds of partials per row on a handful of
+// CTAs (batch 1 x 8192 tokens: merge 55 us against 16 us for the attention kernel itself).
+constexpr int kMaxSpansPerRow = 64;
+__host__ __device__ __forceinline__ int tiles_per_span(int total_tiles, int spans, int longest_row_tiles) {
+  const int even = (total_tiles + spans - 1) / spans;
+  const int capped = (longest_row_tiles + kMaxSpansPerRow - 1) / kMaxSpansPerRow;
+  const int t = even > capped ? even : capped;
+  return t > 1 ? t : 1;
+}
 constexpr int kFusedMinRowHeads = 512;     // ... when rows x KV heads exceeds this (else the separate prologue kernel is faster)
 
 struct AttnPlan {

@@ -392,14 +392,21 @@ __device__ __forceinline__ WarpPlan fused_plan(const AttnArgs& a, int warp, int 
     if (r < rows) decode_row_range(a, r, seq, start, end);
     return row_tiles(start, end);
   };
-  int local = 0;
+  int local = 0, longest = 0;
 #pragma unroll 4
-  for (int ch = 0; ch < n_chunks; ++ch) local += tiles_of(ch * 32 + lane);  // (independent loads, in flight together)
+  for (int ch = 0; ch < n_chunks; ++ch) {  // (independent loads, in flight together)
+    const int nt = tiles_of(ch * 32 + lane);
+    local += nt;
+    longest = max(longest, nt);
+  }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+  for (int o = 16; o > 0; o >>= 1) {
+    local += __shfl_xor_sync(0xffffffffu, local, o);
+    longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+  }
   WarpPlan wp;
   wp.total = local;
-  wp.tps = max(1, (wp.total + sh.span_ctas - 1) / sh.span_ctas);
+  wp.tps = tiles_per_span(wp.total, sh.span_ctas, longest);
   const int T_a = (int)min((long long)span_first * wp.tps, (long long)wp.total);
   const int T_b = (int)min((long long)wp.total, (long long)T_a + (long long)span_count * wp.tps);
   const long long T_w = (long long)span * wp.tps;  // first tile of the warp's own span
