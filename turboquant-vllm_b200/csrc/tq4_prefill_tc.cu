@@ -514,14 +514,13 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         PF_STAMP(j, 3);
         // The packed stage of tile j was dequantised during the previous iteration: tile j + 2 goes into
         // it, most of an iteration before its turn (its page ids were read an iteration ago; those of
-        // tile j + 3 are read now).  Issuing the eight copies takes the thread 1 000 - 2 000 cycles: here
+        // tile j + 3 are read after the values).  Issuing the eight copies takes the thread 1 000 - 2 000 cycles: here
         // they delay only its warp's share of the values; before the keys they would delay S_{j+1}.
         // Four warps issue one page each: a copy instruction costs its thread ~190 cycles.
         if (warp >= kCopyWarp - 3) {
           const int pg = warp - (kCopyWarp - 3);
           if (j + 2 < n_tiles && elect_one_sync()) issue_page(j + 2, pg, blk_next[pg], pg == 0);
           __syncwarp();
-          if (j + 3 < n_tiles) load_blks(j + 3, blk_next);
         }
         // the values of tile j + 1 (only O += P V~ of the next iteration reads them): V~ buffer
         // (j+1) & 1 was read by the MMAs of tile j-1
@@ -529,6 +528,8 @@ prefill_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_idx,
         PF_STAMP(j, 4);
         dequant_tile(j + 1, tid - kSmx, kDeq, 256, 512);
         PF_STAMP(j, 5);
+        // (page ids of the tile after that: issued here, they cost the warp nothing before the barrier)
+        if (warp >= kCopyWarp - 3 && j + 3 < n_tiles) load_blks(j + 3, blk_next);
       }
     } else {
       ok = __all_sync(0xffffffffu, bar_wait_bounded(bar_s0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1)));
