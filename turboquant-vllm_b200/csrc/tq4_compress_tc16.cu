@@ -35,6 +35,18 @@
 #include "tq4_common.cuh"
 
 namespace tq4 {
+#ifdef TQ4_TRACE
+// Tuning builds only (-DTQ4_TRACE): SM clock at points of the tile pipeline of CTA 0 (producer warp,
+// MMA warp, first warp of epilogue groups 0 and 1), read back with tq4_compress_trace_read.
+__device__ long long g_ctrace[4][32][8];
+#define CT_STAMP(role, i, e)                                                                   \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (i) < 32) g_ctrace[role][i][e] = clock64(); \
+  } while (0)
+#else
+#define CT_STAMP(role, i, e) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int kD = 128;
@@ -178,6 +190,21 @@ __device__ __forceinline__ int bucketize_reg(float y, const float (&b)[15]) {
   return (c1 ? 8 : 0) + (c2 ? 4 : 0) + (c3 ? 2 : 0) + (c4 ? 1 : 0);
 }
 
+// The same search with the two lower levels as table lookups through the warp shuffle: lane l holds
+// boundary l & 15 (`bval`; entry 15 = +inf), and __shfl_sync with a per-thread source lane is a
+// 16-entry lookup in one instruction.  Levels 1 and 2 compare against registers (b[7]; b[3] or b[11]);
+// 11 instructions per coordinate instead of 22, same comparisons, same result.  The shuffle unit
+// cannot take every coordinate (all of them through it: no faster than the register search), so the
+// epilogue sends every second one.
+__device__ __forceinline__ int bucketize_shfl(float y, float b7, float b3, float b11, float bval) {
+  const bool c1 = y > b7;
+  int idx = c1 ? 8 : 0;
+  idx += (y > (c1 ? b11 : b3)) ? 4 : 0;
+  idx += (y > __shfl_sync(0xffffffffu, bval, idx + 1)) ? 2 : 0;
+  idx += (y > __shfl_sync(0xffffffffu, bval, idx)) ? 1 : 0;
+  return idx;
+}
+
 struct Bars {
   uint64_t full[kStages];    // TMA -> consumers: the stage's tile has landed
   uint64_t empty[kStages];   // consumers -> TMA: MMAs (1 commit) and the norm readers (4 warps) are done with it
@@ -197,6 +224,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
   __shared__ int s_dead;
   __shared__ float s_bounds[2][16];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (warp == 0) CT_STAMP(0, 31, 6);  // kernel entry
   const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   unsigned char* sm = smem_raw + (base - smem_addr(smem_raw));
   volatile int* dead = &s_dead;
@@ -263,6 +291,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = s_tmem;
+  if (warp == 0) CT_STAMP(0, 31, 7);  // set-up done (Pi converted, tensor memory allocated)
 
   const int64_t rows_per_src = a.n_tokens * a.num_heads;
   const int64_t tiles_per_src = (rows_per_src + kRows - 1) / kRows;
@@ -278,6 +307,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       // (passes at once the first time round; warp-uniform so that the election below is well formed)
       ok = __all_sync(0xffffffffu, bar_wait_bounded(smem_addr(&s_bars.empty[st]), par ^ 1u, dead));
       if (!ok) break;
+      CT_STAMP(0, i, 0);
       if (elect_one_sync()) {
         const int64_t tile = blockIdx.x + i * gridDim.x;
         const int s_ = (int)(tile / tiles_per_src);
@@ -300,6 +330,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
                           bar_wait_bounded(smem_addr(&s_bars.tempty[acc]), (uint32_t)((i / kAccs) & 1) ^ 1u, dead));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      CT_STAMP(1, i, 0);
       if (elect_one_sync()) {
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * kD;
         const uint32_t a0 = base + kOffA + st * kTileBytes;
@@ -318,6 +349,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
         mma_commit(smem_addr(&s_bars.tfull[acc]));  // the accumulator is complete
       }
       __syncwarp();
+      CT_STAMP(1, i, 1);
     }
   } else {
     // ================= epilogue groups =================
@@ -333,6 +365,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       const bool live = in_src < rows_per_src;
       ok = __all_sync(0xffffffffu, bar_wait_bounded(smem_addr(&s_bars.full[st]), (uint32_t)((i / kStages) & 1), dead));
       if (!ok) break;
+      if (quarter == 0 && grp < 2) CT_STAMP(2 + grp, i, 0);
       // ---- norm, in the summation order of the FMA kernels: p[l] over k = l, l+32, l+64, l+96,
       //      then the butterfly tree 16, 8, 4, 2, 1 --------------------------------------------------
       float nrm = 0.f;
@@ -360,6 +393,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
         nrm = sqrtf(p[0]);
       }
       __syncwarp();
+      if (quarter == 0 && grp < 2) CT_STAMP(2 + grp, i, 1);
       if (lane == 0) bar_arrive(smem_addr(&s_bars.empty[st]));  // this warp is done with the staged rows
       // one IEEE division per row; Y_raw * (1 / den) is within an ulp of Y_raw / den
       const float scale = (1.f / (nrm + 1e-10f)) * (1.f / F::kScale);
@@ -388,11 +422,13 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       float b[15];
 #pragma unroll
       for (int bi = 0; bi < 15; ++bi) b[bi] = s_bounds[src][bi];
+      const float bval = s_bounds[src][lane & 15];  // (entry 15 is +inf)
       const bool wide = dst_idx != nullptr && ((uintptr_t)dst_idx & 15) == 0;  // else rows are 4-byte aligned
 
       ok = __all_sync(0xffffffffu, bar_wait_bounded(smem_addr(&s_bars.tfull[acc]), (uint32_t)((i / kAccs) & 1), dead));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (quarter == 0 && grp < 2) CT_STAMP(2 + grp, i, 2);
       // four chunks of 32 coordinates -> 16 bytes each; the loop stays rolled so that its body (32
       // register searches) fits the instruction cache
 #pragma unroll 1
@@ -406,7 +442,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int ie = bucketize_reg(__uint_as_float(v[8 * w + 2 * e]) * scale, b);
-            const int io = bucketize_reg(__uint_as_float(v[8 * w + 2 * e + 1]) * scale, b);
+            const int io = bucketize_shfl(__uint_as_float(v[8 * w + 2 * e + 1]) * scale, b[7], b[3], b[11], bval);
             word[w] |= (uint32_t)((ie << 4) | io) << (8 * e);
           }
         }
@@ -421,6 +457,7 @@ compress_tc16_kernel(const CompressArgs a, const __grid_constant__ CUtensorMap t
       __syncwarp();
       if (lane == 0) bar_arrive(smem_addr(&s_bars.tempty[acc]));  // the accumulator may be overwritten
       if (dst_norm) *dst_norm = nrm;
+      if (quarter == 0 && grp < 2) CT_STAMP(2 + grp, i, 3);
     }
   }
   if (!ok) {
@@ -502,3 +539,9 @@ int launch_compress_tc16(const CompressArgs& a, int dtype, cudaStream_t st) {
 }
 
 }  // namespace tq4
+
+#ifdef TQ4_TRACE
+extern "C" int tq4_compress_trace_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, tq4::g_ctrace, sizeof(long long) * 4 * 32 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -2,11 +2,13 @@
 
     python turboquant-vllm_b200/kernel_timeline.py decode     # paged decode step, batch 64 x 4096 tokens
     python turboquant-vllm_b200/kernel_timeline.py prefill    # tcgen05 chunked prefill, 8 x 2048 on 8192
+    python turboquant-vllm_b200/kernel_timeline.py compress   # tcgen05 cache write, 16 384 tokens x 8 heads
 
 Builds `turboquant_vllm/lib/libtq4_sm100a_trace.so`: the same sources with `-DTQ4_TRACE`, which compiles
 time stamps into `attention_mma_kernel` (`%globaltimer` at its phases, lane 0 of every warp of every
-CTA) and `prefill_tc_kernel` (SM clock at points of the tile loop, four warps of one CTA) and exports
-the two functions that read them back.  The shipped library has neither.  The workloads are the ones
+CTA), `prefill_tc_kernel` (SM clock at points of the tile loop, four warps of one CTA) and
+`compress_tc16_kernel` (SM clock at the hand-overs of its tile pipeline, four warps of CTA 0) and
+exports the functions that read them back.  The shipped library has neither.  The workloads are the ones
 `bench.py` times; the decode timeline is taken with the prologue inside the attention kernel
 (`TQ4_FUSED_PROLOGUE=1`), the form whose single kernel shows every phase of a step.
 """
@@ -57,7 +59,7 @@ def _load(kind: str):
     from turboquant_vllm import _native as nv
 
     nv._LIB_PATH = build_trace_library()
-    reader = "tq4_trace_read" if kind == "decode" else "tq4_prefill_trace_read"
+    reader = {"decode": "tq4_trace_read", "prefill": "tq4_prefill_trace_read", "compress": "tq4_compress_trace_read"}[kind]
     nv._SIGNATURES[reader] = (ctypes.c_int, [ctypes.c_void_p])
     return nv, reader
 
@@ -131,7 +133,44 @@ def prefill_timeline() -> None:
         print(f"   {'next top':32s} {m[9]:8.0f}")
 
 
+def compress_timeline() -> None:
+    nv, reader = _load("compress")
+    import torch
+
+    from turboquant_vllm.kernels import ops
+    from turboquant_vllm.quantizer import TurboQuantMSE
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nt, hkv, d, bs = 16384, 8, 128, 16
+    rot, even, odd, kc, kb = TurboQuantMSE(d, 4, seed=42).device_primitives(dev)
+    g = torch.Generator(device=dev).manual_seed(3)
+    k = torch.randn(nt, hkv, d, device=dev, generator=g).bfloat16()
+    v = torch.randn(nt, hkv, d, device=dev, generator=g).bfloat16()
+    cache = torch.zeros(nt // bs, bs, hkv * 256, dtype=torch.uint8, device=dev)
+    slots = torch.randperm(nt, device=dev, generator=g)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        e0.record()
+        ops.tq4_write_paged(k, v, cache, slots, even, odd, kb, kb)
+        e1.record()
+    torch.cuda.synchronize()
+    print(f"write of {nt} tokens x {hkv} heads, K and V: {e0.elapsed_time(e1) * 1e3:.1f} us on the traced build")
+    buf = np.zeros(4 * 32 * 8, dtype=np.int64)
+    assert getattr(nv.lib(), reader)(buf.ctypes.data) == 0
+    t = buf.reshape(4, 32, 8).astype(np.float64)
+    t0 = t[0, 31, 6]
+    print(f"CTA 0, SM cycles since kernel entry; set-up (Pi converted, tensor memory allocated) done at {t[0, 31, 7] - t0:.0f}")
+    print("tile | stage free, copy issued | rows landed + accumulator free, MMAs issued | group: rows landed, norm done, "
+          "product ready, tile stored")
+    for i in range(14):
+        p, m, e = t[0, i] - t0, t[1, i] - t0, t[2 + (i & 1) if (i % 4) < 2 else 0, i] - t0
+        ep = "  ".join(f"{x:7.0f}" for x in e[:4]) if (i % 4) < 2 else "(group not traced)"
+        print(f"{i:4d} | {p[0]:7.0f} | {m[0]:7.0f} {m[1]:7.0f} | {ep}")
+
+
 if __name__ == "__main__":
-    if len(sys.argv) != 2 or sys.argv[1] not in ("decode", "prefill"):
+    modes = {"decode": decode_timeline, "prefill": prefill_timeline, "compress": compress_timeline}
+    if len(sys.argv) != 2 or sys.argv[1] not in modes:
         raise SystemExit(__doc__)
-    decode_timeline() if sys.argv[1] == "decode" else prefill_timeline()
+    modes[sys.argv[1]]()
