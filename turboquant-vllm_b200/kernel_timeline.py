@@ -164,8 +164,8 @@ def compress_timeline() -> None:
     print("tile | stage free, copy issued | rows landed + accumulator free, MMAs issued | group: rows landed, norm done, "
           "product ready, tile stored")
     for i in range(14):
-        p, m, e = t[0, i] - t0, t[1, i] - t0, t[2 + (i & 1) if (i % 4) < 2 else 0, i] - t0
-        ep = "  ".join(f"{x:7.0f}" for x in e[:4]) if (i % 4) < 2 else "(group not traced)"
+        p, m, e = t[0, i] - t0, t[1, i] - t0, t[2 + (i & 1), i] - t0
+        ep = "  ".join(f"{x:7.0f}" for x in e[:4]) if abs(e[0]) < 1e9 else "(group not traced)"
         print(f"{i:4d} | {p[0]:7.0f} | {m[0]:7.0f} {m[1]:7.0f} | {ep}")
 
 
