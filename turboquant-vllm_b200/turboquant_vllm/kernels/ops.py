@@ -366,7 +366,10 @@ def tq4_write_and_attention(
 ) -> torch.Tensor:
     """One decode step of a layer: :func:`tq4_write_paged` of the new tokens, then
     :func:`paged_tq4_attention`, in three launches (the cache write rides in the kernel that rotates
-    the queries and plans the tiles).  Same results, bit for bit, as the two calls in sequence."""
+    the queries and plans the tiles) or, for decode calls with more than 512 (row, KV head) pairs, in
+    two (that work happens inside the attention kernel; token i must then be the newest token of
+    sequence i).  In the three-launch form the results equal the two calls in sequence bit for bit; in
+    the two-launch form the norms do and the indices agree within the write path's 1e-4 bound."""
     return paged_tq4_attention(
         q, kv_cache, block_table, seq_lens, k_centroids, v_centroids, rotation, num_kv_heads,
         block_size, sm_scale,

@@ -485,8 +485,9 @@ class TQ4AttentionImpl(FlashAttentionImpl):
         return output
 
     def _fused_decode_path(self, query, key, value, kv_cache, attn_metadata, output):
-        """Uniform single-token decode in three launches: the cache write of the new tokens rides in
-        the kernel that rotates the queries and plans the tiles, then attention and the merge."""
+        """Uniform single-token decode in one library call: the cache write of the new tokens rides in
+        the kernel that rotates the queries and plans the tiles (three launches), or all of that
+        happens inside the attention kernel (two launches; the library picks by batch size)."""
         write = None
         if key is not None and value is not None:
             write = (key, value, attn_metadata.slot_mapping)
