@@ -1,4 +1,4 @@
-"""Timelines of the two attention kernels from a tuning build of the library (B200).
+"""Timelines of the attention and cache-write kernels from a tuning build of the library (B200).
 
     python turboquant-vllm_b200/kernel_timeline.py decode     # paged decode step, batch 64 x 4096 tokens
     python turboquant-vllm_b200/kernel_timeline.py prefill    # tcgen05 chunked prefill, 8 x 2048 on 8192
